@@ -1,0 +1,25 @@
+"""CPU oracle for the Monarch-Muon optimizer step.
+
+TEST INFRASTRUCTURE ONLY.  Nothing in the shipped package imports this
+directory; it exists so the CUDA path can be checked against an independent
+CPU restatement of the reference algorithm.  Only the test-suite, the smoke
+entry and the benchmark's CPU-baseline / reference arm may import it.
+
+Modules
+-------
+muon_oracle   heavy-ball momentum, batched quintic Newton-Schulz, the Muon
+              weight update and the embedded AdamW, restated from
+              pretrain/src/models/monarch/monarch_muon.py and its bf16 twin
+              membench/src/models/monarch/monarch_muon.py.
+fp8_oracle    the two FP8 (E4M3, groups of 128) optimizer-state codecs:
+              plain absmax (pretrain/third_party/coat/optimizer/
+              triton_kernels.py:34-36,51-63) and COAT dynamic-range expansion
+              (pretrain/src/models/monarch/coat_state_muon.py:22-91).
+
+Parity pin: the restatement is checked in tests/test_oracle_golden.py against
+vectors produced by importing and running the reference's own Python on CPU
+(tests/golden/make_golden.py).  The expansion codec could not be executed on
+CPU (its Triton kernel needs libdevice.pow), so that codec is
+"parity unpinned": it follows the reference source line by line but no
+reference output exists to compare with.
+"""
