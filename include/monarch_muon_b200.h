@@ -1,0 +1,180 @@
+/*
+ * monarch_muon_b200.h - C ABI of libmonarch_muon_b200.so
+ *
+ * The hot path of the Monarch-Muon optimizer step for NVIDIA B200 (sm_100a):
+ * heavy-ball momentum with FP8 (E4M3, groups of 128) optimizer state, batched
+ * quintic Newton-Schulz on bf16 blocks (tcgen05 tensor cores, TMEM, TMA), the
+ * Muon weight update and the embedded AdamW.
+ *
+ * Conventions
+ *   - Every pointer named *_dev or documented "device" is a CUDA device
+ *     pointer on the current device; tables (`const mmb_*_seg*`) are HOST
+ *     arrays that the call copies into kernel parameters.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default
+ *     stream).  Calls only enqueue work; none synchronises the device.
+ *   - Return value 0 = success.  Negative = error; mmb_last_error() returns a
+ *     description (thread local).  Nothing throws, aborts or exits.
+ *   - The caller owns all memory.  The library allocates nothing on the
+ *     device except inside mmb_device_status_create().
+ *   - Citations name the reference file (path within the reference project)
+ *     and lines whose behaviour the entry point replaces.
+ */
+#ifndef MONARCH_MUON_B200_H
+#define MONARCH_MUON_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MMB_OK 0
+#define MMB_ERR_INVALID (-1) /* bad argument                                 */
+#define MMB_ERR_CUDA (-2)    /* a CUDA runtime/driver call failed            */
+#define MMB_ERR_DEVICE (-3)  /* a kernel reported a problem (status word)    */
+#define MMB_ERR_UNSUPPORTED (-4)
+
+/* element types */
+#define MMB_BF16 0
+#define MMB_F32 1
+
+/* momentum state formats */
+#define MMB_STATE_FP8_ABSMAX 0 /* E4M3 codes + one fp32 scale per 128          */
+#define MMB_STATE_FP8_EXPAND 1 /* E4M3 codes + scale, expand, sqrt_minmax      */
+#define MMB_STATE_BF16 2       /* plain buffer, two roundings per step         */
+#define MMB_STATE_F32 3
+
+/* division used by the FP8 quantiser: IEEE round-to-nearest (matches a CPU
+ * restatement bit for bit) or the GPU's approximate full-range division that
+ * the reference's Triton build emits for `/`. */
+#define MMB_DIV_IEEE 0
+#define MMB_DIV_FULL 1
+
+/* Newton-Schulz GEMM back ends */
+#define MMB_NS_TCGEN05 0 /* tcgen05.mma + TMEM + TMA (the product)             */
+#define MMB_NS_SIMT 1    /* plain CUDA-core tiles; slow, for cross-checking    */
+
+int mmb_version(void);
+const char* mmb_last_error(void);
+
+/* ------------------------------------------------------------------------
+ * Heavy-ball momentum with optimizer-state codec, fused:
+ *   dequantise -> m = beta*m (rounded) -> m = m + grad_scale*g (rounded)
+ *   -> requantise; also writes bf16(m) for Newton-Schulz and the per-block
+ *   sum of squares of bf16(m).
+ * Replaces: momentum update   pretrain/src/models/monarch/monarch_muon.py:146-148
+ *                             membench/src/models/monarch/monarch_muon.py:150-151
+ *           cat + bf16 cast   membench/.../monarch_muon.py:161-163
+ *           FP8 state codec   pretrain/src/models/monarch/coat_state_muon.py:22-114
+ *                             (expansion) and pretrain/third_party/coat/optimizer/
+ *                             triton_kernels.py:34-36,51-63 (absmax)
+ *           Frobenius norm    monarch_muon.py:38
+ * One segment = one parameter tensor of nblocks blocks of block_elems
+ * elements.  Groups of 128 restart at each segment; a tail group is masked.
+ * ---------------------------------------------------------------------- */
+typedef struct mmb_momentum_seg {
+  const void* grad;     /* device, grad_dtype, [numel]                        */
+  void* state;          /* device: E4M3 codes (uint8) or the bf16/fp32 buffer */
+  float* scale;         /* device, [ceil(numel/128)]       (FP8 formats)      */
+  float* expand;        /* device, [ceil(numel/128)]       (FP8_EXPAND only)  */
+  float* sqrt_minmax;   /* device, [ceil(numel/128)]       (FP8_EXPAND only)  */
+  void* m_bf16;         /* device, bf16 [numel], may be NULL                  */
+  int64_t numel;        /* nblocks * block_elems                              */
+  int64_t block_elems;  /* rows*cols of one block                             */
+  int64_t first_block;  /* index of this segment's first block in block_sumsq */
+} mmb_momentum_seg;
+
+/* Number of floats of scratch (per-chunk partial sums) the call below needs. */
+int64_t mmb_momentum_scratch_floats(const mmb_momentum_seg* segs, int nseg);
+
+int mmb_momentum_step(const mmb_momentum_seg* segs, int nseg, int grad_dtype, int state_format,
+                      int div_mode, float beta, float grad_scale, int expand_min,
+                      float* block_sumsq_dev, /* [total blocks] or NULL           */
+                      float* scratch_dev, int64_t scratch_floats, void* stream);
+
+/* Stand-alone codecs on one flat fp32 tensor (first-step quantise, state_dict
+ * export, tests).  Replace coat_state_muon.py:94-114 (dequantize, quantize_). */
+int mmb_fp8_quantize(const float* value_dev, uint8_t* codes_dev, float* scale_dev, float* expand_dev,
+                     float* sqrt_minmax_dev, int64_t numel, int state_format, int is_signed,
+                     int div_mode, int expand_min, void* stream);
+int mmb_fp8_dequantize(const uint8_t* codes_dev, const float* scale_dev, const float* expand_dev,
+                       const float* sqrt_minmax_dev, float* out_dev, int64_t numel, int state_format,
+                       int is_signed, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Batched quintic Newton-Schulz on `batch` bf16 blocks of rows x cols.
+ * Replaces _newton_schulz_batched, monarch_muon.py:36-50 (bf16 twin:
+ * membench/.../monarch_muon.py:36-50 with the cast at :161-166):
+ *   X = B / (||B||_F + 1e-7); 5 x { A = X X^T; X = aX + (bA + cA^2) X }
+ * computed on the stored orientation (tall blocks are never transposed in
+ * memory).  The norm prescale is applied inside the first iteration's
+ * epilogues, bA + cA^2 is formed in one epilogue, aX + PX in another.
+ *   x_dev            bf16 [batch, rows, cols], input (momentum); also used as
+ *                    scratch unless `out_dev` differs - see below
+ *   out_dev          bf16 [batch, rows, cols]; may equal x_dev
+ *   block_sumsq_dev  fp32 [batch] sum of squares per block, or NULL to have
+ *                    the call compute it from x_dev
+ *   workspace_dev    mmb_ns_workspace_bytes() bytes, 1024-byte aligned
+ *   status_dev       int32 word from mmb_device_status_create(), or NULL
+ * ---------------------------------------------------------------------- */
+int64_t mmb_ns_workspace_bytes(int batch, int rows, int cols);
+int mmb_newton_schulz(const void* x_dev, void* out_dev, const float* block_sumsq_dev, int batch,
+                      int rows, int cols, void* workspace_dev, int64_t workspace_bytes, int backend,
+                      int32_t* status_dev, void* stream);
+
+/* One batched GEMM of the family Newton-Schulz is built from (exposed for
+ * tests and profiling):
+ *   D[b] = sigma_b * (alpha * opA[b] . opB[b]^T + gamma * C[b])
+ * opA is M x K, opB is N x K.  a_kmajor=1: A stored [batch][M][K] (K
+ * contiguous); a_kmajor=0: stored [batch][K][M].  Same for B with N.
+ * C, D: bf16 [batch][M][N].  sigma_b = inv_norm[b]^sigma_pow (pow 0: 1). */
+int mmb_gemm_bf16(const void* a_dev, const void* b_dev, const void* c_dev, void* d_dev, int batch,
+                  int M, int N, int K, int a_kmajor, int b_kmajor, float alpha, float gamma,
+                  const float* inv_norm_dev, int sigma_pow, int backend, int32_t* status_dev,
+                  void* stream);
+
+/* ------------------------------------------------------------------------
+ * Muon weight update, W <- W + alpha * O with alpha = -lr*sqrt(rows/cols).
+ * Replaces monarch_muon.py:160-165 (membench :167-170).
+ * ---------------------------------------------------------------------- */
+typedef struct mmb_update_seg {
+  void* weight;       /* device, weight_dtype, [numel]      */
+  const void* ortho;  /* device, bf16, [numel]              */
+  int64_t numel;
+} mmb_update_seg;
+
+int mmb_muon_update(const mmb_update_seg* segs, int nseg, int weight_dtype, float alpha, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Decoupled AdamW over a list of tensors, one launch per <=128 tensors.
+ * Replaces _adamw_step, monarch_muon.py:171-201 (membench :176-208): weight
+ * decay multiplies the parameter first; eps is added after sqrt(v)/sqrt(bc2);
+ * every intermediate is rounded to the tensor dtype like the reference's
+ * separate torch ops.  `step` is the already-incremented count.
+ * ---------------------------------------------------------------------- */
+typedef struct mmb_adamw_seg {
+  void* param;        /* device, dtype */
+  const void* grad;   /* device, dtype */
+  void* exp_avg;      /* device, dtype */
+  void* exp_avg_sq;   /* device, dtype */
+  int64_t numel;
+  int32_t step;       /* per tensor (the pretrain twin counts per parameter) */
+  int32_t pad_;
+} mmb_adamw_seg;
+
+int mmb_adamw_step(const mmb_adamw_seg* segs, int nseg, int dtype, float lr, float beta1, float beta2,
+                   float weight_decay, float eps, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Device status word.  Kernels never trap: a bounded wait that expires or a
+ * failed self-check stores a non-zero code here and the kernel returns.
+ * mmb_device_status_read synchronises `stream` and returns the word.
+ * ---------------------------------------------------------------------- */
+int mmb_device_status_create(int32_t** status_dev_out);
+int mmb_device_status_destroy(int32_t* status_dev);
+int mmb_device_status_read(int32_t* status_dev, int32_t* host_out, int reset, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MONARCH_MUON_B200_H */

@@ -1,0 +1,129 @@
+"""ctypes binding of libmonarch_muon_b200.so (the C ABI in include/monarch_muon_b200.h).
+
+There is no fallback: if the library is missing it is built with nvcc, and if
+that fails, or no CUDA device is present when a kernel is requested, the call
+raises.  Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+import torch
+
+from . import build as _build
+
+BF16, F32 = 0, 1
+STATE_FP8_ABSMAX, STATE_FP8_EXPAND, STATE_BF16, STATE_F32 = 0, 1, 2, 3
+DIV_IEEE, DIV_FULL = 0, 1
+NS_TCGEN05, NS_SIMT = 0, 1
+
+
+class MomentumSeg(C.Structure):
+    _fields_ = [("grad", C.c_void_p), ("state", C.c_void_p), ("scale", C.c_void_p), ("expand", C.c_void_p),
+                ("sqrt_minmax", C.c_void_p), ("m_bf16", C.c_void_p), ("numel", C.c_int64),
+                ("block_elems", C.c_int64), ("first_block", C.c_int64)]
+
+
+class UpdateSeg(C.Structure):
+    _fields_ = [("weight", C.c_void_p), ("ortho", C.c_void_p), ("numel", C.c_int64)]
+
+
+class AdamWSeg(C.Structure):
+    _fields_ = [("param", C.c_void_p), ("grad", C.c_void_p), ("exp_avg", C.c_void_p), ("exp_avg_sq", C.c_void_p),
+                ("numel", C.c_int64), ("step", C.c_int32), ("pad_", C.c_int32)]
+
+
+# every symbol include/monarch_muon_b200.h declares: name -> (restype, argtypes)
+_vp, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
+SYMBOLS = {
+    "mmb_version": (_i, []),
+    "mmb_last_error": (C.c_char_p, []),
+    "mmb_momentum_scratch_floats": (_i64, [C.POINTER(MomentumSeg), _i]),
+    "mmb_momentum_step": (_i, [C.POINTER(MomentumSeg), _i, _i, _i, _i, _f, _f, _i, _vp, _vp, _i64, _vp]),
+    "mmb_fp8_quantize": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp]),
+    "mmb_fp8_dequantize": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _vp]),
+    "mmb_ns_workspace_bytes": (_i64, [_i, _i, _i]),
+    "mmb_newton_schulz": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i64, _i, _vp, _vp]),
+    "mmb_gemm_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _i, _i, _vp, _vp]),
+    "mmb_muon_update": (_i, [C.POINTER(UpdateSeg), _i, _i, _f, _vp]),
+    "mmb_adamw_step": (_i, [C.POINTER(AdamWSeg), _i, _i, _f, _f, _f, _f, _f, _vp]),
+    "mmb_device_status_create": (_i, [C.POINTER(_vp)]),
+    "mmb_device_status_destroy": (_i, [_vp]),
+    "mmb_device_status_read": (_i, [_vp, C.POINTER(C.c_int32), _i, _vp]),
+}
+
+_lock = threading.Lock()
+_lib = None
+
+
+def load():
+    """Load (building first if needed) the shared library; raises on failure."""
+    global _lib
+    with _lock:
+        if _lib is None:
+            path = _build.LIB_PATH
+            if not os.path.exists(path) or os.environ.get("MMB_REBUILD") == "1":
+                path = _build.build()
+            lib = C.CDLL(path)
+            for name, (res, args) in SYMBOLS.items():
+                fn = getattr(lib, name)          # AttributeError if the symbol is missing
+                fn.restype = res
+                fn.argtypes = args
+            _lib = lib
+    return _lib
+
+
+def check(rc: int, what: str = "") -> None:
+    if rc != 0:
+        msg = load().mmb_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"libmonarch_muon_b200 {what} failed ({rc}): {msg}")
+
+
+def require_cuda(*tensors) -> None:
+    if not torch.cuda.is_available():
+        raise RuntimeError("monarch_muon_b200 needs a CUDA device (B200, sm_100a); there is no CPU path")
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("monarch_muon_b200: tensor is not on a CUDA device; there is no CPU path")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.bfloat16:
+        return BF16
+    if dt == torch.float32:
+        return F32
+    raise TypeError(f"monarch_muon_b200 supports bfloat16 and float32 tensors, got {dt}")
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+_status_words: dict = {}
+
+
+def status_word(device: torch.device) -> int:
+    """Per-device status word that kernels write when a bounded wait expires."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status_words:
+        out = C.c_void_p()
+        with torch.cuda.device(idx):
+            check(load().mmb_device_status_create(C.byref(out)), "device_status_create")
+        _status_words[idx] = out.value
+    return _status_words[idx]
+
+
+def read_status(device: torch.device, reset: bool = True) -> int:
+    """Synchronise the current stream and return the device status word (0 = fine)."""
+    host = C.c_int32(0)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    with torch.cuda.device(idx):
+        check(load().mmb_device_status_read(status_word(device), C.byref(host), int(reset), stream_ptr()),
+              "device_status_read")
+    return host.value

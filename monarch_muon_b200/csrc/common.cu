@@ -1,0 +1,69 @@
+// Error reporting, device queries and the device status word.
+#include "common.cuh"
+
+#include <cstring>
+
+namespace mmb {
+
+char* error_buffer() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int sm_count() {
+  static thread_local int cached_dev = -1;
+  static thread_local int cached_sms = 0;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (dev != cached_dev) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached_dev = dev;
+    cached_sms = sms;
+  }
+  return cached_sms;
+}
+
+}  // namespace mmb
+
+extern "C" {
+
+int mmb_version(void) { return 100; }
+
+const char* mmb_last_error(void) { return mmb::error_buffer(); }
+
+int mmb_device_status_create(int32_t** status_dev_out) {
+  using namespace mmb;
+  MMB_REQUIRE(status_dev_out != nullptr, "mmb_device_status_create: null output");
+  int32_t* p = nullptr;
+  MMB_CUDA_CHECK(cudaMalloc(&p, 4 * sizeof(int32_t)));
+  MMB_CUDA_CHECK(cudaMemset(p, 0, 4 * sizeof(int32_t)));
+  *status_dev_out = p;
+  return MMB_OK;
+}
+
+int mmb_device_status_destroy(int32_t* status_dev) {
+  using namespace mmb;
+  if (status_dev != nullptr) MMB_CUDA_CHECK(cudaFree(status_dev));
+  return MMB_OK;
+}
+
+int mmb_device_status_read(int32_t* status_dev, int32_t* host_out, int reset, void* stream) {
+  using namespace mmb;
+  MMB_REQUIRE(status_dev != nullptr && host_out != nullptr, "mmb_device_status_read: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MMB_CUDA_CHECK(cudaMemcpyAsync(host_out, status_dev, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+  if (reset) MMB_CUDA_CHECK(cudaMemsetAsync(status_dev, 0, 4 * sizeof(int32_t), st));
+  MMB_CUDA_CHECK(cudaStreamSynchronize(st));
+  return MMB_OK;
+}
+
+}  // extern "C"

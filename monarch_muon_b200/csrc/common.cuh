@@ -1,0 +1,47 @@
+// Shared host/device helpers for libmonarch_muon_b200.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/monarch_muon_b200.h"
+
+namespace mmb {
+
+// Thread-local message behind mmb_last_error().
+char* error_buffer();
+int fail(int code, const char* fmt, ...);
+
+#define MMB_CUDA_CHECK(expr)                                                                  \
+  do {                                                                                        \
+    cudaError_t _e = (expr);                                                                  \
+    if (_e != cudaSuccess)                                                                    \
+      return ::mmb::fail(MMB_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
+                         __FILE__, __LINE__);                                                 \
+  } while (0)
+
+#define MMB_REQUIRE(cond, ...)                                   \
+  do {                                                           \
+    if (!(cond)) return ::mmb::fail(MMB_ERR_INVALID, __VA_ARGS__); \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+// Device status codes stored by kernels (first writer wins).
+enum : int32_t {
+  STATUS_OK = 0,
+  STATUS_WAIT_PRODUCER_EMPTY = 0x101,  // TMA producer waited too long for a free stage
+  STATUS_WAIT_MMA_FULL = 0x102,        // MMA issuer waited too long for operands
+  STATUS_WAIT_MMA_TMEM_EMPTY = 0x103,  // MMA issuer waited too long for a drained accumulator
+  STATUS_WAIT_EPI_TMEM_FULL = 0x104,   // epilogue waited too long for an accumulator
+};
+
+}  // namespace mmb

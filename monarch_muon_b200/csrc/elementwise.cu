@@ -1,0 +1,297 @@
+// Bandwidth-bound multi-tensor kernels: the Muon weight update and the
+// embedded AdamW.  Both take a table of tensors as kernel parameters and walk
+// it with a grid-stride loop over 16-byte vectors, so one launch covers many
+// parameter tensors without staging a pointer table in device memory.
+#include "common.cuh"
+
+namespace mmb {
+namespace {
+
+constexpr int THREADS = 256;
+constexpr int MAX_SEG = 128;
+constexpr int VEC = 8;  // elements per thread per step
+
+template <typename T>
+__device__ __forceinline__ float ld(const T* p);
+template <>
+__device__ __forceinline__ float ld<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <>
+__device__ __forceinline__ float ld<float>(const float* p) { return *p; }
+template <typename T>
+__device__ __forceinline__ void st(T* p, float v);
+template <>
+__device__ __forceinline__ void st<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ void st<float>(float* p, float v) { *p = v; }
+
+// Round to the tensor's storage type and come back: models one torch op.
+template <typename T>
+__device__ __forceinline__ float rd(float v);
+template <>
+__device__ __forceinline__ float rd<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+template <>
+__device__ __forceinline__ float rd<float>(float v) { return v; }
+
+template <typename T>
+__device__ __forceinline__ void load_vec(const T* p, bool vec, int n, float* out);
+template <>
+__device__ __forceinline__ void load_vec<__nv_bfloat16>(const __nv_bfloat16* p, bool vec, int n, float* out) {
+  if (vec) {
+    uint4 v = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __bfloat1622float2(h[i]);
+      out[2 * i] = f.x;
+      out[2 * i + 1] = f.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) out[i] = i < n ? __bfloat162float(p[i]) : 0.0f;
+  }
+}
+template <>
+__device__ __forceinline__ void load_vec<float>(const float* p, bool vec, int n, float* out) {
+  if (vec) {
+    float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+    out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) out[i] = i < n ? p[i] : 0.0f;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T* p, bool vec, int n, const float* in);
+template <>
+__device__ __forceinline__ void store_vec<__nv_bfloat16>(__nv_bfloat16* p, bool vec, int n, const float* in) {
+  if (vec) {
+    uint4 v;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(in[2 * i], in[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = v;
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i)
+      if (i < n) p[i] = __float2bfloat16_rn(in[i]);
+  }
+}
+template <>
+__device__ __forceinline__ void store_vec<float>(float* p, bool vec, int n, const float* in) {
+  if (vec) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(in[0], in[1], in[2], in[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(in[4], in[5], in[6], in[7]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i)
+      if (i < n) p[i] = in[i];
+  }
+}
+
+// A table entry: tensors of one segment and where its vectors start in the
+// launch-wide numbering.
+struct UpdSeg {
+  void* weight;
+  const __nv_bfloat16* ortho;
+  long long numel;
+  int vec_ok;
+};
+struct UpdTable {
+  UpdSeg seg[MAX_SEG];
+  long long vec_start[MAX_SEG + 1];
+  int nseg;
+};
+
+template <typename Tab>
+__device__ __forceinline__ int find_segment(const Tab& tab, long long v) {
+  int lo = 0, hi = tab.nseg;
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (tab.vec_start[mid] <= v) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// W <- W + alpha*O, one fused multiply-add then one rounding to W's type, as
+// torch's add_(other, alpha=) kernel does on a GPU.
+template <typename WT>
+__global__ void __launch_bounds__(THREADS)
+muon_update_kernel(const __grid_constant__ UpdTable tab, float alpha) {
+  const long long total = tab.vec_start[tab.nseg];
+  const long long stride = static_cast<long long>(gridDim.x) * THREADS;
+  for (long long v = static_cast<long long>(blockIdx.x) * THREADS + threadIdx.x; v < total; v += stride) {
+    const int s = find_segment(tab, v);
+    const UpdSeg& sg = tab.seg[s];
+    const long long at = (v - tab.vec_start[s]) * VEC;
+    const long long rem = sg.numel - at;
+    const int n = rem >= VEC ? VEC : static_cast<int>(rem);
+    const bool vec = sg.vec_ok && n == VEC;
+    float w[VEC], o[VEC];
+    WT* wp = static_cast<WT*>(sg.weight) + at;
+    load_vec<WT>(wp, vec, n, w);
+    load_vec<__nv_bfloat16>(sg.ortho + at, vec, n, o);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) w[i] = fmaf(alpha, o[i], w[i]);
+    store_vec<WT>(wp, vec, n, w);
+  }
+}
+
+struct AdamSeg {
+  void* param;
+  const void* grad;
+  void* exp_avg;
+  void* exp_avg_sq;
+  long long numel;
+  float bc2_sqrt;    // sqrt(1 - beta2^step)
+  float step_size;   // lr / (1 - beta1^step)
+  int vec_ok;
+  int pad_;
+};
+struct AdamTable {
+  AdamSeg seg[MAX_SEG];
+  long long vec_start[MAX_SEG + 1];
+  int nseg;
+};
+
+// The reference issues one torch op per line (pretrain/src/models/monarch/
+// monarch_muon.py:191-201); each op rounds to the tensor dtype, so `rd` is
+// applied after every one of them.
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+adamw_kernel(const __grid_constant__ AdamTable tab, float decay, float beta1, float one_m_beta1, float beta2,
+             float one_m_beta2, float eps) {
+  const long long total = tab.vec_start[tab.nseg];
+  const long long stride = static_cast<long long>(gridDim.x) * THREADS;
+  for (long long v = static_cast<long long>(blockIdx.x) * THREADS + threadIdx.x; v < total; v += stride) {
+    const int s = find_segment(tab, v);
+    const AdamSeg& sg = tab.seg[s];
+    const long long at = (v - tab.vec_start[s]) * VEC;
+    const long long rem = sg.numel - at;
+    const int n = rem >= VEC ? VEC : static_cast<int>(rem);
+    const bool vec = sg.vec_ok && n == VEC;
+    T* pp = static_cast<T*>(sg.param) + at;
+    T* mp = static_cast<T*>(sg.exp_avg) + at;
+    T* vp = static_cast<T*>(sg.exp_avg_sq) + at;
+    float p[VEC], g[VEC], m[VEC], q[VEC];
+    load_vec<T>(pp, vec, n, p);
+    load_vec<T>(static_cast<const T*>(sg.grad) + at, vec, n, g);
+    load_vec<T>(mp, vec, n, m);
+    load_vec<T>(vp, vec, n, q);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      float pi = p[i];
+      if (decay != 1.0f) pi = rd<T>(__fmul_rn(pi, decay));                      // p.mul_(1 - lr*wd)
+      float mi = rd<T>(__fmul_rn(m[i], beta1));                                 // exp_avg.mul_(beta1)
+      mi = rd<T>(fmaf(one_m_beta1, g[i], mi));                                  // .add_(grad, alpha=1-beta1)
+      float vi = rd<T>(__fmul_rn(q[i], beta2));                                 // exp_avg_sq.mul_(beta2)
+      vi = rd<T>(fmaf(__fmul_rn(one_m_beta2, g[i]), g[i], vi));                 // .addcmul_(grad, grad, value=1-beta2)
+      float d = rd<T>(__fsqrt_rn(vi));                                          // exp_avg_sq.sqrt()
+      d = rd<T>(__fdiv_rn(d, sg.bc2_sqrt));                                     // / sqrt(bc2)
+      d = rd<T>(__fadd_rn(d, eps));                                             // .add_(eps)
+      pi = rd<T>(fmaf(-sg.step_size, __fdiv_rn(mi, d), pi));                    // p.addcdiv_(m, denom, value=-lr/bc1)
+      p[i] = pi; m[i] = mi; q[i] = vi;
+    }
+    store_vec<T>(pp, vec, n, p);
+    store_vec<T>(mp, vec, n, m);
+    store_vec<T>(vp, vec, n, q);
+  }
+}
+
+int grid_for(long long total_vecs, int sms) {
+  long long want = (total_vecs + THREADS - 1) / THREADS;
+  long long cap = static_cast<long long>(sms) * 8 * 4;
+  long long g = want < cap ? want : cap;
+  return static_cast<int>(g < 1 ? 1 : g);
+}
+
+}  // namespace
+}  // namespace mmb
+
+extern "C" {
+
+int mmb_muon_update(const mmb_update_seg* segs, int nseg, int weight_dtype, float alpha, void* stream) {
+  using namespace mmb;
+  MMB_REQUIRE(nseg >= 0 && (nseg == 0 || segs != nullptr), "mmb_muon_update: bad segment table");
+  MMB_REQUIRE(weight_dtype == MMB_BF16 || weight_dtype == MMB_F32, "mmb_muon_update: weight_dtype %d", weight_dtype);
+  if (nseg == 0) return MMB_OK;
+  const int sms = sm_count();
+  if (sms <= 0) return fail(MMB_ERR_CUDA, "mmb_muon_update: no CUDA device");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (int base = 0; base < nseg; base += MAX_SEG) {
+    UpdTable tab;
+    tab.nseg = (nseg - base) < MAX_SEG ? (nseg - base) : MAX_SEG;
+    long long vecs = 0;
+    for (int i = 0; i < tab.nseg; ++i) {
+      const mmb_update_seg& s = segs[base + i];
+      MMB_REQUIRE(s.numel > 0 && s.weight && s.ortho, "mmb_muon_update: segment %d empty", base + i);
+      tab.seg[i].weight = s.weight;
+      tab.seg[i].ortho = static_cast<const __nv_bfloat16*>(s.ortho);
+      tab.seg[i].numel = s.numel;
+      tab.seg[i].vec_ok = aligned16(s.ortho) &&
+                          ((reinterpret_cast<uintptr_t>(s.weight) & (weight_dtype == MMB_F32 ? 31u : 15u)) == 0);
+      tab.vec_start[i] = vecs;
+      vecs += (s.numel + VEC - 1) / VEC;
+    }
+    tab.vec_start[tab.nseg] = vecs;
+    const int grid = grid_for(vecs, sms);
+    if (weight_dtype == MMB_BF16)
+      muon_update_kernel<__nv_bfloat16><<<grid, THREADS, 0, st>>>(tab, alpha);
+    else
+      muon_update_kernel<float><<<grid, THREADS, 0, st>>>(tab, alpha);
+    MMB_CUDA_CHECK(cudaGetLastError());
+  }
+  return MMB_OK;
+}
+
+int mmb_adamw_step(const mmb_adamw_seg* segs, int nseg, int dtype, float lr, float beta1, float beta2,
+                   float weight_decay, float eps, void* stream) {
+  using namespace mmb;
+  MMB_REQUIRE(nseg >= 0 && (nseg == 0 || segs != nullptr), "mmb_adamw_step: bad segment table");
+  MMB_REQUIRE(dtype == MMB_BF16 || dtype == MMB_F32, "mmb_adamw_step: dtype %d", dtype);
+  if (nseg == 0) return MMB_OK;
+  const int sms = sm_count();
+  if (sms <= 0) return fail(MMB_ERR_CUDA, "mmb_adamw_step: no CUDA device");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // scalars are formed in double like the reference's Python floats, then
+  // narrowed once to the fp32 the element-wise arithmetic runs in
+  const double b1 = beta1, b2 = beta2, lrd = lr, wd = weight_decay;
+  const float decay = weight_decay > 0.0f ? static_cast<float>(1.0 - lrd * wd) : 1.0f;
+  const uintptr_t amask = dtype == MMB_F32 ? 31u : 15u;
+  for (int base = 0; base < nseg; base += MAX_SEG) {
+    AdamTable tab;
+    tab.nseg = (nseg - base) < MAX_SEG ? (nseg - base) : MAX_SEG;
+    long long vecs = 0;
+    for (int i = 0; i < tab.nseg; ++i) {
+      const mmb_adamw_seg& s = segs[base + i];
+      MMB_REQUIRE(s.numel > 0 && s.param && s.grad && s.exp_avg && s.exp_avg_sq, "mmb_adamw_step: segment %d empty",
+                  base + i);
+      MMB_REQUIRE(s.step >= 1, "mmb_adamw_step: segment %d has step %d (must be >= 1)", base + i, s.step);
+      AdamSeg& d = tab.seg[i];
+      d.param = s.param;
+      d.grad = s.grad;
+      d.exp_avg = s.exp_avg;
+      d.exp_avg_sq = s.exp_avg_sq;
+      d.numel = s.numel;
+      double bc1 = 1.0 - pow(b1, static_cast<double>(s.step));
+      double bc2 = 1.0 - pow(b2, static_cast<double>(s.step));
+      d.bc2_sqrt = static_cast<float>(sqrt(bc2));
+      d.step_size = static_cast<float>(lrd / bc1);
+      d.vec_ok = (((reinterpret_cast<uintptr_t>(s.param) | reinterpret_cast<uintptr_t>(s.grad) |
+                    reinterpret_cast<uintptr_t>(s.exp_avg) | reinterpret_cast<uintptr_t>(s.exp_avg_sq)) & amask) == 0);
+      tab.vec_start[i] = vecs;
+      vecs += (s.numel + VEC - 1) / VEC;
+    }
+    tab.vec_start[tab.nseg] = vecs;
+    const int grid = grid_for(vecs, sms);
+    const float omb1 = static_cast<float>(1.0 - b1), omb2 = static_cast<float>(1.0 - b2);
+    if (dtype == MMB_BF16)
+      adamw_kernel<__nv_bfloat16><<<grid, THREADS, 0, st>>>(tab, decay, beta1, omb1, beta2, omb2, eps);
+    else
+      adamw_kernel<float><<<grid, THREADS, 0, st>>>(tab, decay, beta1, omb1, beta2, omb2, eps);
+    MMB_CUDA_CHECK(cudaGetLastError());
+  }
+  return MMB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,479 @@
+// Batched bf16 GEMM for Newton-Schulz on sm_100a: TMA -> shared memory ->
+// tcgen05.mma -> TMEM -> fused epilogue.
+//
+//   D[b] = sigma_b * (alpha * opA[b] . opB[b]^T + gamma * C[b])
+//
+// opA is M x K, opB is N x K; each may be stored K-major ([rows][K], K
+// contiguous) or MN-major ([K][rows], rows contiguous), so that X X^T, X^T X,
+// P X and Y P all run on the matrices as stored and nothing is ever
+// transposed in memory.
+//
+// CTA = 192 threads, persistent over output tiles of 128 x BN:
+//   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of a
+//               128x64 A tile and a BNx64 B tile (128-byte swizzle) per stage
+//               into a ring of STAGES buffers, arming the stage's mbarrier
+//               with the byte count.  No cluster multicast anywhere.
+//   warp 1      MMA issuer: one lane issues four tcgen05.mma (K=16 each) per
+//               stage into one of two TMEM accumulators (128 lanes x BN fp32
+//               columns each), then tcgen05.commit to free the stage; after
+//               the last K tile, tcgen05.commit hands the accumulator over.
+//   warps 2-5   epilogue: tcgen05.ld 32 columns at a time (each warp owns the
+//               32 TMEM lanes its warp-id allows), apply alpha/gamma/sigma,
+//               round to bf16, store.  The double-buffered accumulator lets
+//               the epilogue of tile i overlap the main loop of tile i+1.
+//
+// Every mbarrier wait is bounded (about two seconds of wall clock): on expiry
+// the waiting role stores a code in the device status word, raises a CTA-wide
+// abort flag and all roles leave their loops; the CTA then lets outstanding
+// bulk copies land, frees its TMEM and returns.  Nothing traps.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace mmb {
+namespace tc {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int A_TILE_BYTES = BM * BK * 2;
+constexpr int CHUNK_BYTES = 64 * BK * 2;  // one 64-wide MN-major chunk
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+template <int BN>
+struct Cfg {
+  static constexpr int B_TILE_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct GemmArgs {
+  int M, N, K, batch;
+  int tiles_m, tiles_n;
+  long long total_tiles;
+  const __nv_bfloat16* C;
+  __nv_bfloat16* D;
+  float alpha, gamma;
+  const float* inv_norm;
+  int sigma_pow;
+  int32_t* status;
+};
+
+// ------------------------------------------------------------------ PTX glue
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done;
+}
+// Bounded wait.  Returns false when the CTA is aborting (this wait expired or
+// another role's did).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                          int32_t code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        if (status != nullptr) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle.
+//   bits  0-13  start address >> 4
+//   bits 16-29  leading-dimension byte offset >> 4
+//   bits 32-45  stride-dimension byte offset >> 4
+//   bits 46-47  descriptor version (1 on sm_100)
+//   bits 61-63  swizzle mode (2 = 128 bytes)
+// K-major tile ([rows][64] bf16, 128 bytes per row): 8-row groups are 1024
+// bytes apart (stride offset); the leading offset is unused (1).
+// MN-major tile ([64 k][64 rows] chunks of 8 KiB): the 8-k groups of one
+// chunk are 1024 bytes apart (stride offset) and the 64-row chunks are 8 KiB
+// apart (leading offset).
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, bool k_major) {
+  const uint64_t lbo = k_major ? 1ull : static_cast<uint64_t>(CHUNK_BYTES >> 4);
+  const uint64_t sbo = 1024ull >> 4;
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (lbo << 16) | (sbo << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B.
+//   bits 4-5 D format (1 = f32); 7-9 A format (1 = bf16); 10-12 B format;
+//   bit 15 / 16: A / B is MN-major; bits 17-22 N>>3; bits 24-28 M>>4.
+template <int BN, bool A_KMAJOR, bool B_KMAJOR>
+__device__ __forceinline__ constexpr uint32_t make_idesc() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((A_KMAJOR ? 0u : 1u) << 15) | ((B_KMAJOR ? 0u : 1u) << 16) |
+         (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void tile_coords(long long t, const GemmArgs& a, int& b, int& m0, int& n0) {
+  const int per = a.tiles_m * a.tiles_n;
+  b = static_cast<int>(t / per);
+  const int r = static_cast<int>(t - static_cast<long long>(b) * per);
+  m0 = (r / a.tiles_n) * BM;
+  n0 = (r % a.tiles_n);
+}
+
+// -------------------------------------------------------------------- kernel
+template <int BN, bool A_KMAJOR, bool B_KMAJOR>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const GemmArgs args) {
+  using C = Cfg<BN>;
+  constexpr int STAGES = C::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
+  uint8_t* tiles_ptr = smem_raw + (tiles_addr - raw_addr);
+  // barrier block after the tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles_ptr + STAGES * C::STAGE_BYTES);
+  const uint32_t bars_addr = tiles_addr + STAGES * C::STAGE_BYTES;
+  const uint32_t full_bar = bars_addr;                      // STAGES
+  const uint32_t empty_bar = bars_addr + 8 * STAGES;        // STAGES
+  const uint32_t tmem_full_bar = bars_addr + 16 * STAGES;   // 2
+  const uint32_t tmem_empty_bar = tmem_full_bar + 16;       // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_k_tiles = (args.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(empty_bar + 8 * s, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tmem_full_bar + 8 * i, 1);
+      mbar_init(tmem_empty_bar + 8 * i, 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(static_cast<uint32_t>(C::TMEM_COLS))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; ok && t < args.total_tiles; t += gridDim.x) {
+        int b, m0, nt;
+        tile_coords(t, args, b, m0, nt);
+        const int n0 = nt * BN;
+        for (int kt = 0; kt < num_k_tiles; ++kt) {
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, args.status, STATUS_WAIT_PRODUCER_EMPTY)) {
+            ok = false;
+            break;
+          }
+          const uint32_t fb = full_bar + 8 * stage;
+          mbar_expect_tx(fb, C::STAGE_BYTES);
+          const uint32_t sa = tiles_addr + stage * C::STAGE_BYTES;
+          const uint32_t sb = sa + A_TILE_BYTES;
+          const int k0 = kt * BK;
+          if (A_KMAJOR) {
+            tma_load_3d(sa, &tmap_a, fb, k0, m0, b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_3d(sa + c * CHUNK_BYTES, &tmap_a, fb, m0 + 64 * c, k0, b);
+          }
+          if (B_KMAJOR) {
+            tma_load_3d(sb, &tmap_b, fb, k0, n0, b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * CHUNK_BYTES, &tmap_b, fb, n0 + 64 * c, k0, b);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // --------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc<BN, A_KMAJOR, B_KMAJOR>();
+      constexpr uint32_t a_step = A_KMAJOR ? (UMMA_K * 2) >> 4 : (UMMA_K * 128) >> 4;  // descriptor units of 16 B
+      constexpr uint32_t b_step = B_KMAJOR ? (UMMA_K * 2) >> 4 : (UMMA_K * 128) >> 4;
+      uint32_t stage = 0, phase = 0;
+      uint32_t local = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; ok && t < args.total_tiles; t += gridDim.x, ++local) {
+        const uint32_t acc = local & 1u;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        if (!mbar_wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, args.status, STATUS_WAIT_MMA_TMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kt = 0; kt < num_k_tiles; ++kt) {
+          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, args.status, STATUS_WAIT_MMA_FULL)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t sa = tiles_addr + stage * C::STAGE_BYTES;
+          const uint64_t adesc = make_desc(sa, A_KMAJOR);
+          const uint64_t bdesc = make_desc(sa + A_TILE_BYTES, B_KMAJOR);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            tcgen05_mma_f16(d_tmem, adesc + k * a_step, bdesc + k * b_step, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          tcgen05_commit(empty_bar + 8 * stage);  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tcgen05_commit(tmem_full_bar + 8 * acc);  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32) are this warp's
+    uint32_t local = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; ok && t < args.total_tiles; t += gridDim.x, ++local) {
+      int b, m0, nt;
+      tile_coords(t, args, b, m0, nt);
+      const int n0 = nt * BN;
+      const uint32_t acc = local & 1u;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag, args.status, STATUS_WAIT_EPI_TMEM_FULL)) {
+        ok = false;
+        break;
+      }
+      tcgen05_fence_after();
+      float sigma = 1.0f;
+      if (args.sigma_pow > 0) {
+        const float s = args.inv_norm[b];
+        sigma = args.sigma_pow == 2 ? s * s : s;
+      }
+      const float sa = sigma * args.alpha, sg = sigma * args.gamma;
+      const int row = m0 + quarter * 32 + lane;
+      const bool row_ok = row < args.M;
+      const long long row_off = (static_cast<long long>(b) * args.M + row) * args.N;
+      const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tcgen05_ld_32x32b_x32(t_base + c * 32, v);
+        tcgen05_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row_ok && col0 < args.N) {
+          const int nvec = (args.N - col0) >= 32 ? 4 : (args.N - col0) / 8;  // 16-byte vectors of 8 bf16
+          const __nv_bfloat16* cp = args.C != nullptr ? args.C + row_off + col0 : nullptr;
+          __nv_bfloat16* dp = args.D + row_off + col0;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (q < nvec) {
+              float addend[8];
+              if (cp != nullptr) {
+                uint4 cv = *reinterpret_cast<const uint4*>(cp + 8 * q);
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&cv);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  float2 f = __bfloat1622float2(h[i]);
+                  addend[2 * i] = f.x;
+                  addend[2 * i + 1] = f.y;
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) addend[i] = 0.0f;
+              }
+              uint4 ov;
+              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                float x0 = fmaf(sa, __uint_as_float(v[8 * q + 2 * i]), sg * addend[2 * i]);
+                float x1 = fmaf(sa, __uint_as_float(v[8 * q + 2 * i + 1]), sg * addend[2 * i + 1]);
+                oh[i] = __floats2bfloat162_rn(x0, x1);
+              }
+              *reinterpret_cast<uint4*>(dp + 8 * q) = ov;
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar + 8 * acc);
+    }
+  }
+
+  // ------------------------------------------------------------- teardown
+  __syncthreads();
+  if (*abort_flag) {
+    // let bulk copies that were already issued land before shared memory is released
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(C::TMEM_COLS))
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Tensor map over a bf16 array [batch][outer][inner] (inner contiguous) with a
+// box of {64, box_outer, 1} and 128-byte swizzle; out-of-range elements read 0.
+int make_map(CUtensorMap* map, const void* base, int batch, int outer, int inner, int box_outer) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return fail(MMB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer), static_cast<cuuint64_t>(batch)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(inner) * 2ull, static_cast<cuuint64_t>(inner) * outer * 2ull};
+  cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(box_outer), 1u};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(MMB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for [%d][%d][%d] box %d", static_cast<int>(r), batch,
+                outer, inner, box_outer);
+  return MMB_OK;
+}
+
+template <int BN, bool AK, bool BK_>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, int grid, cudaStream_t st) {
+  auto kern = gemm_kernel<BN, AK, BK_>;
+  MMB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES));
+  kern<<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, st>>>(ta, tb, args);
+  MMB_CUDA_CHECK(cudaGetLastError());
+  return MMB_OK;
+}
+
+template <int BN>
+int launch_major(bool ak, bool bk, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, int grid,
+                 cudaStream_t st) {
+  if (ak && bk) return launch<BN, true, true>(ta, tb, args, grid, st);
+  if (ak && !bk) return launch<BN, true, false>(ta, tb, args, grid, st);
+  if (!ak && bk) return launch<BN, false, true>(ta, tb, args, grid, st);
+  return launch<BN, false, false>(ta, tb, args, grid, st);
+}
+
+}  // namespace tc
+
+int gemm_tcgen05(const void* a, const void* b, const void* c, void* d, int batch, int M, int N, int K, int a_kmajor,
+                 int b_kmajor, float alpha, float gamma, const float* inv_norm, int sigma_pow, int32_t* status,
+                 cudaStream_t st) {
+  using namespace tc;
+  MMB_REQUIRE(M % 8 == 0 && N % 8 == 0 && K % 8 == 0, "tcgen05 GEMM needs M, N, K multiples of 8 (got %d %d %d)", M, N, K);
+  MMB_REQUIRE(aligned16(a) && aligned16(b) && aligned16(d) && (c == nullptr || aligned16(c)),
+              "tcgen05 GEMM needs 16-byte aligned operands");
+  const int bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  CUtensorMap ta, tb;
+  int rc;
+  // K-major: [batch][rows][K], box {64 k, rows}; MN-major: [batch][K][rows], box {64 rows, 64 k}
+  rc = a_kmajor ? make_map(&ta, a, batch, M, K, BM) : make_map(&ta, a, batch, K, M, BK);
+  if (rc != MMB_OK) return rc;
+  rc = b_kmajor ? make_map(&tb, b, batch, N, K, bn) : make_map(&tb, b, batch, K, N, BK);
+  if (rc != MMB_OK) return rc;
+  GemmArgs args;
+  args.M = M; args.N = N; args.K = K; args.batch = batch;
+  args.tiles_m = (M + BM - 1) / BM;
+  args.tiles_n = (N + bn - 1) / bn;
+  args.total_tiles = static_cast<long long>(batch) * args.tiles_m * args.tiles_n;
+  args.C = static_cast<const __nv_bfloat16*>(c);
+  args.D = static_cast<__nv_bfloat16*>(d);
+  args.alpha = alpha; args.gamma = gamma;
+  args.inv_norm = inv_norm; args.sigma_pow = inv_norm != nullptr ? sigma_pow : 0;
+  args.status = status;
+  const int sms = sm_count();
+  if (sms <= 0) return fail(MMB_ERR_CUDA, "tcgen05 GEMM: no CUDA device");
+  const int grid = static_cast<int>(args.total_tiles < sms ? args.total_tiles : sms);
+  if (grid == 0) return MMB_OK;
+  if (bn == 256) return launch_major<256>(a_kmajor != 0, b_kmajor != 0, ta, tb, args, grid, st);
+  if (bn == 128) return launch_major<128>(a_kmajor != 0, b_kmajor != 0, ta, tb, args, grid, st);
+  return launch_major<64>(a_kmajor != 0, b_kmajor != 0, ta, tb, args, grid, st);
+}
+
+}  // namespace mmb

@@ -1,0 +1,671 @@
+// Heavy-ball momentum fused with the optimizer-state codec.
+//
+// One streaming pass per step: read the stored state (E4M3 codes + per-group
+// fp32 scale, or a plain bf16/fp32 buffer) and the gradient, form
+// m = round(beta*m) then m = round(m + g) - two roundings, like the
+// reference's mul_ followed by add_ (pretrain/src/models/monarch/
+// monarch_muon.py:148) - requantise, and emit what Newton-Schulz needs: the
+// bf16 copy of m and per-block sums of squares.
+//
+// Work decomposition.  A group is 128 contiguous elements and is handled by 8
+// lanes x 16 elements, so the group maximum is three xor-shuffles and every
+// global access is a 16-byte vector.  A warp walks a "unit" of 4096 elements
+// of one block and leaves one partial sum of squares; a second tiny kernel
+// adds a block's partials in a fixed order, which keeps the norm - and so the
+// whole step - bit-reproducible from run to run (no float atomics).
+//
+// HBM traffic per element with the absmax codec and bf16 gradients:
+// 1 (code in) + 2 (grad) + 1 (code out) + 2 (bf16 m) + 8/128 (scale in/out)
+// = 6.0625 bytes; the kernel is bandwidth bound.
+#include "common.cuh"
+
+namespace mmb {
+namespace {
+
+constexpr int GROUP = 128;
+constexpr int LANES_PER_GROUP = 8;
+constexpr int ELEMS_PER_LANE = 16;
+constexpr int UNIT = 4096;  // elements per warp work unit = one partial sum
+constexpr int MAX_SEG = 96;
+constexpr int THREADS = 256;
+
+struct SegDev {
+  const void* grad;
+  void* state;
+  float* scale;
+  float* expand;
+  float* sqrt_mm;
+  __nv_bfloat16* m_out;
+  long long numel;
+  long long block_elems;   // multiple of 128, or == numel
+  long long partial_base;  // first partial of this segment in the scratch
+  long long first_block;
+  int cpb;                 // units (= partials) per block
+  int vec_ok;              // all pointers 16-byte aligned
+};
+
+struct SegTable {
+  SegDev seg[MAX_SEG];
+  long long unit_start[MAX_SEG + 1];
+  int nseg;
+};
+
+// ---------------------------------------------------------------- arithmetic
+template <int DIV>
+__device__ __forceinline__ float fdiv(float a, float b) {
+  if (DIV == MMB_DIV_IEEE) return __fdiv_rn(a, b);
+  float r;
+  asm("div.full.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+
+template <int DIV>
+__device__ __forceinline__ float fsqrt(float a) {
+  if (DIV == MMB_DIV_IEEE) return __fsqrt_rn(a);
+  float r;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));
+  return r;
+}
+
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t pair) {
+  __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(pair), __NV_E4M3);
+  return __half22float2(*reinterpret_cast<__half2*>(&h));
+}
+
+__device__ __forceinline__ uint16_t float2_to_e4m3x2(float lo, float hi) {
+  return static_cast<uint16_t>(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
+}
+
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__device__ __forceinline__ float group_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+  return v;
+}
+__device__ __forceinline__ float group_min(float v) {
+  v = fminf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  v = fminf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+  v = fminf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+  return v;
+}
+__device__ __forceinline__ int group_or(int v) {
+  v |= __shfl_xor_sync(0xffffffffu, v, 1);
+  v |= __shfl_xor_sync(0xffffffffu, v, 2);
+  v |= __shfl_xor_sync(0xffffffffu, v, 4);
+  return v;
+}
+
+// COAT dynamic-range expansion, per group (pretrain/src/models/monarch/
+// coat_state_muon.py:56-86).  Inputs are the group's reduced statistics.
+struct ExpandParams {
+  float scale, expand, sqrt_mm;
+};
+
+template <int DIV>
+__device__ __forceinline__ ExpandParams expand_group_params(float absmax, float absmin_nz, bool any_nz,
+                                                            float expand_min) {
+  const float eps = 1e-30f;
+  absmax = fmaxf(absmax, eps);
+  float absmin = any_nz ? fmaxf(absmin_nz, eps) : eps;
+  const float one_eps = 1.0f + eps;  // == 1.0f
+  float ratio = fmaxf(fdiv<DIV>(absmax, absmin), one_eps);
+  const float ratio_upper = 448.0f * 448.0f / 2.0f;
+  float log_ratio = log2f(ratio);
+  float safe_log = log_ratio > eps ? log_ratio : 1.0f;
+  float raw = fdiv<DIV>(floorf(fdiv<DIV>(log2f(ratio_upper), safe_log) * expand_min), expand_min);
+  float min_expand = fdiv<DIV>(1.0f, expand_min);
+  ExpandParams p;
+  p.expand = (ratio <= one_eps) ? 1.0f : fmaxf(raw, min_expand);
+  p.sqrt_mm = fmaxf(fsqrt<DIV>(absmax) * fsqrt<DIV>(absmin), eps);
+  float scale_base = fmaxf(fdiv<DIV>(absmax, p.sqrt_mm), eps);
+  p.scale = fmaxf(fdiv<DIV>(powf(scale_base, p.expand), 448.0f), eps);
+  return p;
+}
+
+template <int DIV>
+__device__ __forceinline__ float expand_normalize(float m, bool valid, const ExpandParams& p, bool is_signed) {
+  const float eps = 1e-30f;
+  float a = fabsf(m);
+  float base = fmaxf(fdiv<DIV>(a, p.sqrt_mm), eps);
+  float pw = powf(base, p.expand);
+  float sgn = (m >= 0.0f) ? 1.0f : -1.0f;
+  float n = (valid && a > 0.0f) ? (is_signed ? sgn * pw : pw) : 0.0f;
+  return fdiv<DIV>(n, p.scale);
+}
+
+template <int DIV>
+__device__ __forceinline__ float expand_decode(float raw, float s, float expand, float sqrt_mm, bool is_signed) {
+  const float eps = 1e-30f;
+  expand = fmaxf(expand, eps);
+  sqrt_mm = fmaxf(sqrt_mm, eps);
+  float scaled = raw * s;
+  if (!is_signed) scaled = fmaxf(scaled, 0.0f);
+  float a = fabsf(scaled);
+  float sgn = (scaled >= 0.0f) ? 1.0f : -1.0f;
+  float pw = powf(fmaxf(a, eps), fdiv<DIV>(1.0f, expand));
+  return a > 0.0f ? sgn * pw * sqrt_mm : 0.0f;
+}
+
+// ------------------------------------------------------------------- loaders
+template <typename T>
+struct Elem;
+template <>
+struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ void load16(const void* base, long long at, bool vec, int n, float* out) {
+    const __nv_bfloat16* p = static_cast<const __nv_bfloat16*>(base) + at;
+    if (vec) {
+      uint4 v[2];
+      v[0] = __ldcs(reinterpret_cast<const uint4*>(p));
+      v[1] = __ldcs(reinterpret_cast<const uint4*>(p) + 1);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float2 f = __bfloat1622float2(h[i]);
+        out[2 * i] = f.x;
+        out[2 * i + 1] = f.y;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) out[i] = i < n ? __bfloat162float(p[i]) : 0.0f;
+    }
+  }
+  static __device__ __forceinline__ void store16(void* base, long long at, bool vec, int n, const float* in) {
+    __nv_bfloat16* p = static_cast<__nv_bfloat16*>(base) + at;
+    if (vec) {
+      uint4 v[2];
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) h[i] = __floats2bfloat162_rn(in[2 * i], in[2 * i + 1]);
+      reinterpret_cast<uint4*>(p)[0] = v[0];
+      reinterpret_cast<uint4*>(p)[1] = v[1];
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if (i < n) p[i] = __float2bfloat16_rn(in[i]);
+    }
+  }
+};
+template <>
+struct Elem<float> {
+  static __device__ __forceinline__ void load16(const void* base, long long at, bool vec, int n, float* out) {
+    const float* p = static_cast<const float*>(base) + at;
+    if (vec) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float4 f = __ldcs(reinterpret_cast<const float4*>(p) + i);
+        out[4 * i] = f.x;
+        out[4 * i + 1] = f.y;
+        out[4 * i + 2] = f.z;
+        out[4 * i + 3] = f.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) out[i] = i < n ? p[i] : 0.0f;
+    }
+  }
+  static __device__ __forceinline__ void store16(void* base, long long at, bool vec, int n, const float* in) {
+    float* p = static_cast<float*>(base) + at;
+    if (vec) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        reinterpret_cast<float4*>(p)[i] = make_float4(in[4 * i], in[4 * i + 1], in[4 * i + 2], in[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if (i < n) p[i] = in[i];
+    }
+  }
+};
+
+__device__ __forceinline__ void load_codes16(const uint8_t* p, bool vec, int n, float* out) {
+  if (vec) {
+    uint4 v = *reinterpret_cast<const uint4*>(p);
+    const uint16_t* h = reinterpret_cast<const uint16_t*>(&v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float2 f = e4m3x2_to_float2(h[i]);
+      out[2 * i] = f.x;
+      out[2 * i + 1] = f.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) out[i] = i < n ? e4m3x2_to_float2(p[i]).x : 0.0f;
+  }
+}
+
+__device__ __forceinline__ void store_codes16(uint8_t* p, bool vec, int n, const float* q) {
+  if (vec) {
+    uint4 v;
+    uint16_t* h = reinterpret_cast<uint16_t*>(&v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) h[i] = float2_to_e4m3x2(q[2 * i], q[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = v;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (i < n) p[i] = static_cast<uint8_t>(float2_to_e4m3x2(q[i], 0.0f) & 0xff);
+  }
+}
+
+// -------------------------------------------------------------- fused kernel
+template <int FORMAT, typename GradT, int DIV>
+__global__ void __launch_bounds__(THREADS)
+momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_scale, float expand_min,
+                float* __restrict__ partials) {
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & (LANES_PER_GROUP - 1);
+  const int grp_in_warp = lane >> 3;
+  const long long warp_global = static_cast<long long>(blockIdx.x) * (THREADS / 32) + (threadIdx.x >> 5);
+  const long long nwarps = static_cast<long long>(gridDim.x) * (THREADS / 32);
+  const long long total_units = tab.unit_start[tab.nseg];
+
+  for (long long u = warp_global; u < total_units; u += nwarps) {
+    int lo = 0, hi = tab.nseg;  // last segment with unit_start <= u
+    while (hi - lo > 1) {
+      int mid = (lo + hi) >> 1;
+      if (tab.unit_start[mid] <= u) lo = mid; else hi = mid;
+    }
+    const SegDev& sg = tab.seg[lo];
+    const long long local = u - tab.unit_start[lo];
+    const long long blk = local / sg.cpb;
+    const int chunk = static_cast<int>(local - blk * sg.cpb);
+    const long long e0 = blk * sg.block_elems + static_cast<long long>(chunk) * UNIT;
+    long long e1 = e0 + UNIT;
+    const long long blk_end = (blk + 1) * sg.block_elems;
+    if (e1 > blk_end) e1 = blk_end;
+    if (e1 > sg.numel) e1 = sg.numel;
+    const int ngroups = static_cast<int>((e1 - e0 + GROUP - 1) / GROUP);
+    float ss = 0.0f;
+
+    for (int g0 = 0; g0 < ngroups; g0 += 4) {
+      const int gi = g0 + grp_in_warp;
+      const bool active = gi < ngroups;
+      const long long gstart = e0 + static_cast<long long>(gi) * GROUP;  // first element of the group
+      const long long at = gstart + sub * ELEMS_PER_LANE;
+      int n = 0;  // valid elements of this lane
+      if (active) {
+        long long rem = sg.numel - at;
+        n = rem >= ELEMS_PER_LANE ? ELEMS_PER_LANE : (rem > 0 ? static_cast<int>(rem) : 0);
+      }
+      const bool vec = sg.vec_ok && n == ELEMS_PER_LANE;
+      const long long gidx = gstart / GROUP;  // group index within the tensor
+
+      float m[ELEMS_PER_LANE];
+      float g[ELEMS_PER_LANE];
+#pragma unroll
+      for (int i = 0; i < ELEMS_PER_LANE; ++i) { m[i] = 0.0f; g[i] = 0.0f; }
+
+      if (n > 0) {
+        Elem<GradT>::load16(sg.grad, at, vec, n, g);
+        if (FORMAT == MMB_STATE_FP8_ABSMAX) {
+          load_codes16(static_cast<const uint8_t*>(sg.state) + at, vec, n, m);
+          const float s = sg.scale[gidx];
+#pragma unroll
+          for (int i = 0; i < ELEMS_PER_LANE; ++i) m[i] = __fmul_rn(m[i], s);
+        } else if (FORMAT == MMB_STATE_FP8_EXPAND) {
+          load_codes16(static_cast<const uint8_t*>(sg.state) + at, vec, n, m);
+          const float s = sg.scale[gidx], ex = sg.expand[gidx], sq = sg.sqrt_mm[gidx];
+#pragma unroll
+          for (int i = 0; i < ELEMS_PER_LANE; ++i) m[i] = expand_decode<DIV>(m[i], s, ex, sq, true);
+        } else if (FORMAT == MMB_STATE_BF16) {
+          Elem<__nv_bfloat16>::load16(sg.state, at, vec, n, m);
+        } else {
+          Elem<float>::load16(sg.state, at, vec, n, m);
+        }
+      }
+
+      // heavy ball: two roundings in the state's arithmetic type
+      float amax = 0.0f, amin = 3.4028235e38f;
+      int any_nz = 0;
+#pragma unroll
+      for (int i = 0; i < ELEMS_PER_LANE; ++i) {
+        float gi_f = __fmul_rn(g[i], grad_scale);
+        float t = __fmul_rn(beta, m[i]);
+        if (FORMAT == MMB_STATE_BF16) t = bf16_round(t);
+        t = __fadd_rn(t, gi_f);
+        if (FORMAT == MMB_STATE_BF16) t = bf16_round(t);
+        if (i >= n) t = 0.0f;
+        m[i] = t;
+        float a = fabsf(t);
+        amax = fmaxf(amax, a);
+        if (FORMAT == MMB_STATE_FP8_EXPAND && a > 0.0f) { amin = fminf(amin, a); any_nz = 1; }
+      }
+
+      if (FORMAT == MMB_STATE_FP8_ABSMAX) {
+        amax = group_max(amax);
+        const float s_new = fdiv<DIV>(__fadd_rn(amax, 1e-20f), 448.0f);
+        float q[ELEMS_PER_LANE];
+#pragma unroll
+        for (int i = 0; i < ELEMS_PER_LANE; ++i) q[i] = fdiv<DIV>(m[i], s_new);
+        if (n > 0) {
+          store_codes16(static_cast<uint8_t*>(sg.state) + at, vec, n, q);
+          if (sub == 0) sg.scale[gidx] = s_new;
+        }
+      } else if (FORMAT == MMB_STATE_FP8_EXPAND) {
+        amax = group_max(amax);
+        amin = group_min(amin);
+        any_nz = group_or(any_nz);
+        const ExpandParams p = expand_group_params<DIV>(amax, amin, any_nz != 0, expand_min);
+        float q[ELEMS_PER_LANE];
+#pragma unroll
+        for (int i = 0; i < ELEMS_PER_LANE; ++i) q[i] = expand_normalize<DIV>(m[i], i < n, p, true);
+        if (n > 0) {
+          store_codes16(static_cast<uint8_t*>(sg.state) + at, vec, n, q);
+          if (sub == 0) { sg.scale[gidx] = p.scale; sg.expand[gidx] = p.expand; sg.sqrt_mm[gidx] = p.sqrt_mm; }
+        }
+      } else if (FORMAT == MMB_STATE_BF16) {
+        if (n > 0) Elem<__nv_bfloat16>::store16(sg.state, at, vec, n, m);
+      } else {
+        if (n > 0) Elem<float>::store16(sg.state, at, vec, n, m);
+      }
+
+      // what Newton-Schulz reads, and its squared norm
+#pragma unroll
+      for (int i = 0; i < ELEMS_PER_LANE; ++i) {
+        float r = bf16_round(m[i]);
+        ss = fmaf(r, r, ss);
+      }
+      if (n > 0 && sg.m_out != nullptr && static_cast<void*>(sg.m_out) != sg.state)
+        Elem<__nv_bfloat16>::store16(sg.m_out, at, vec, n, m);
+    }
+
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0 && partials != nullptr) partials[sg.partial_base + blk * sg.cpb + chunk] = ss;
+  }
+}
+
+// Sum each block's partials in a fixed order (lane-strided, then a tree).
+__global__ void __launch_bounds__(THREADS)
+block_sumsq_kernel(const __grid_constant__ SegTable tab, const float* __restrict__ partials,
+                   float* __restrict__ block_sumsq) {
+  const int lane = threadIdx.x & 31;
+  const long long warp_global = static_cast<long long>(blockIdx.x) * (THREADS / 32) + (threadIdx.x >> 5);
+  const long long nwarps = static_cast<long long>(gridDim.x) * (THREADS / 32);
+  for (int s = 0; s < tab.nseg; ++s) {
+    const SegDev& sg = tab.seg[s];
+    const long long nblk = sg.numel / sg.block_elems;
+    for (long long b = warp_global; b < nblk; b += nwarps) {
+      const float* p = partials + sg.partial_base + b * sg.cpb;
+      float acc = 0.0f;
+      for (int i = lane; i < sg.cpb; i += 32) acc += p[i];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane == 0) block_sumsq[sg.first_block + b] = acc;
+    }
+  }
+}
+
+// ------------------------------------------------------- stand-alone codecs
+// One warp per group of 128 (4 elements per lane); not performance critical:
+// used for first-step state creation, state_dict export and tests.
+template <int FORMAT, int DIV>
+__global__ void __launch_bounds__(THREADS)
+quantize_kernel(const float* __restrict__ value, uint8_t* __restrict__ codes, float* __restrict__ scale,
+                float* __restrict__ expand, float* __restrict__ sqrt_mm, long long numel, int is_signed,
+                float expand_min) {
+  const int lane = threadIdx.x & 31;
+  const long long ngroups = (numel + GROUP - 1) / GROUP;
+  const long long warp_global = static_cast<long long>(blockIdx.x) * (THREADS / 32) + (threadIdx.x >> 5);
+  const long long nwarps = static_cast<long long>(gridDim.x) * (THREADS / 32);
+  for (long long gidx = warp_global; gidx < ngroups; gidx += nwarps) {
+    float m[4];
+    bool ok[4];
+    float amax = 0.0f, amin = 3.4028235e38f;
+    int any_nz = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      long long at = gidx * GROUP + lane * 4 + i;
+      ok[i] = at < numel;
+      m[i] = ok[i] ? value[at] : 0.0f;
+      float a = fabsf(m[i]);
+      amax = fmaxf(amax, a);
+      if (ok[i] && a > 0.0f) { amin = fminf(amin, a); any_nz = 1; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      amin = fminf(amin, __shfl_xor_sync(0xffffffffu, amin, o));
+      any_nz |= __shfl_xor_sync(0xffffffffu, any_nz, o);
+    }
+    float q[4];
+    if (FORMAT == MMB_STATE_FP8_ABSMAX) {
+      const float s = fdiv<DIV>(__fadd_rn(amax, 1e-20f), 448.0f);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) q[i] = fdiv<DIV>(m[i], s);
+      if (lane == 0) scale[gidx] = s;
+    } else {
+      const ExpandParams p = expand_group_params<DIV>(amax, amin, any_nz != 0, expand_min);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) q[i] = expand_normalize<DIV>(m[i], ok[i], p, is_signed != 0);
+      if (lane == 0) { scale[gidx] = p.scale; expand[gidx] = p.expand; sqrt_mm[gidx] = p.sqrt_mm; }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      long long at = gidx * GROUP + lane * 4 + i;
+      if (ok[i]) codes[at] = static_cast<uint8_t>(float2_to_e4m3x2(q[i], 0.0f) & 0xff);
+    }
+  }
+}
+
+template <int FORMAT, int DIV>
+__global__ void __launch_bounds__(THREADS)
+dequantize_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ scale,
+                  const float* __restrict__ expand, const float* __restrict__ sqrt_mm, float* __restrict__ out,
+                  long long numel, int is_signed) {
+  const long long stride = static_cast<long long>(gridDim.x) * THREADS;
+  for (long long at = static_cast<long long>(blockIdx.x) * THREADS + threadIdx.x; at < numel; at += stride) {
+    const long long gidx = at / GROUP;
+    const float raw = e4m3x2_to_float2(codes[at]).x;
+    if (FORMAT == MMB_STATE_FP8_ABSMAX)
+      out[at] = __fmul_rn(raw, scale[gidx]);
+    else
+      out[at] = expand_decode<DIV>(raw, scale[gidx], expand[gidx], sqrt_mm[gidx], is_signed != 0);
+  }
+}
+
+// ------------------------------------------------------------------- host
+struct Plan {
+  long long cpb;          // partials per block
+  long long nblocks;
+  long long block_elems;  // effective (== numel when blocks do not hold whole groups)
+};
+
+Plan plan_segment(const mmb_momentum_seg& s) {
+  Plan p;
+  p.block_elems = s.block_elems;
+  if (p.block_elems <= 0 || p.block_elems % GROUP != 0 || s.numel % p.block_elems != 0) p.block_elems = s.numel;
+  p.nblocks = s.numel / p.block_elems;
+  p.cpb = (p.block_elems + UNIT - 1) / UNIT;
+  return p;
+}
+
+template <int FORMAT, typename GradT>
+void launch_momentum(int div_mode, const SegTable& tab, int grid, float beta, float grad_scale, float expand_min,
+                     float* partials, cudaStream_t st) {
+  if (div_mode == MMB_DIV_IEEE)
+    momentum_kernel<FORMAT, GradT, MMB_DIV_IEEE><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
+  else
+    momentum_kernel<FORMAT, GradT, MMB_DIV_FULL><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
+}
+
+template <typename GradT>
+void launch_momentum_format(int format, int div_mode, const SegTable& tab, int grid, float beta, float grad_scale,
+                            float expand_min, float* partials, cudaStream_t st) {
+  switch (format) {
+    case MMB_STATE_FP8_ABSMAX:
+      launch_momentum<MMB_STATE_FP8_ABSMAX, GradT>(div_mode, tab, grid, beta, grad_scale, expand_min, partials, st);
+      break;
+    case MMB_STATE_FP8_EXPAND:
+      launch_momentum<MMB_STATE_FP8_EXPAND, GradT>(div_mode, tab, grid, beta, grad_scale, expand_min, partials, st);
+      break;
+    case MMB_STATE_BF16:
+      launch_momentum<MMB_STATE_BF16, GradT>(MMB_DIV_IEEE, tab, grid, beta, grad_scale, expand_min, partials, st);
+      break;
+    default:
+      launch_momentum<MMB_STATE_F32, GradT>(MMB_DIV_IEEE, tab, grid, beta, grad_scale, expand_min, partials, st);
+      break;
+  }
+}
+
+}  // namespace
+
+int momentum_step_impl(const mmb_momentum_seg* segs, int nseg, int grad_dtype, int state_format, int div_mode,
+                       float beta, float grad_scale, int expand_min, float* block_sumsq_dev, float* scratch_dev,
+                       int64_t scratch_floats, void* stream) {
+  MMB_REQUIRE(nseg >= 0 && (nseg == 0 || segs != nullptr), "mmb_momentum_step: bad segment table");
+  MMB_REQUIRE(grad_dtype == MMB_BF16 || grad_dtype == MMB_F32, "mmb_momentum_step: grad_dtype %d", grad_dtype);
+  MMB_REQUIRE(state_format >= MMB_STATE_FP8_ABSMAX && state_format <= MMB_STATE_F32,
+              "mmb_momentum_step: state_format %d", state_format);
+  MMB_REQUIRE(div_mode == MMB_DIV_IEEE || div_mode == MMB_DIV_FULL, "mmb_momentum_step: div_mode %d", div_mode);
+  if (nseg == 0) return MMB_OK;
+  const int64_t need = mmb_momentum_scratch_floats(segs, nseg);
+  if (block_sumsq_dev != nullptr)
+    MMB_REQUIRE(scratch_dev != nullptr && scratch_floats >= need,
+                "mmb_momentum_step: scratch of %lld floats needed, %lld given", (long long)need,
+                (long long)scratch_floats);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int sms = sm_count();
+  if (sms <= 0) return fail(MMB_ERR_CUDA, "mmb_momentum_step: no CUDA device");
+  float* partials = block_sumsq_dev != nullptr ? scratch_dev : nullptr;
+
+  long long partial_base = 0;
+  for (int base = 0; base < nseg; base += MAX_SEG) {
+    SegTable tab;
+    tab.nseg = (nseg - base) < MAX_SEG ? (nseg - base) : MAX_SEG;
+    long long units = 0;
+    for (int i = 0; i < tab.nseg; ++i) {
+      const mmb_momentum_seg& s = segs[base + i];
+      MMB_REQUIRE(s.numel > 0 && s.grad != nullptr && s.state != nullptr, "mmb_momentum_step: segment %d empty",
+                  base + i);
+      if (state_format == MMB_STATE_FP8_ABSMAX || state_format == MMB_STATE_FP8_EXPAND)
+        MMB_REQUIRE(s.scale != nullptr, "mmb_momentum_step: segment %d has no scale array", base + i);
+      if (state_format == MMB_STATE_FP8_EXPAND)
+        MMB_REQUIRE(s.expand != nullptr && s.sqrt_minmax != nullptr,
+                    "mmb_momentum_step: segment %d lacks expand/sqrt_minmax", base + i);
+      const Plan p = plan_segment(s);
+      if (block_sumsq_dev != nullptr)
+        MMB_REQUIRE(p.block_elems == s.block_elems,
+                    "mmb_momentum_step: block_elems %lld of segment %d must be a multiple of 128 dividing numel "
+                    "when block sums are requested", (long long)s.block_elems, base + i);
+      SegDev& d = tab.seg[i];
+      d.grad = s.grad;
+      d.state = s.state;
+      d.scale = s.scale;
+      d.expand = s.expand;
+      d.sqrt_mm = s.sqrt_minmax;
+      d.m_out = static_cast<__nv_bfloat16*>(s.m_bf16);
+      d.numel = s.numel;
+      d.block_elems = p.block_elems;
+      d.partial_base = partial_base;
+      d.first_block = s.first_block;
+      d.cpb = static_cast<int>(p.cpb);
+      d.vec_ok = aligned16(s.grad) && aligned16(s.state) && (s.m_bf16 == nullptr || aligned16(s.m_bf16));
+      tab.unit_start[i] = units;
+      units += p.nblocks * p.cpb;
+      partial_base += p.nblocks * p.cpb;
+    }
+    tab.unit_start[tab.nseg] = units;
+    const long long warps_per_cta = THREADS / 32;
+    long long want = (units + warps_per_cta - 1) / warps_per_cta;
+    long long cap = static_cast<long long>(sms) * 8 * 4;  // a few waves of 8 resident CTAs per SM
+    int grid = static_cast<int>(want < cap ? want : cap);
+    if (grid < 1) grid = 1;
+    if (grad_dtype == MMB_BF16)
+      launch_momentum_format<__nv_bfloat16>(state_format, div_mode, tab, grid, beta, grad_scale,
+                                            static_cast<float>(expand_min), partials, st);
+    else
+      launch_momentum_format<float>(state_format, div_mode, tab, grid, beta, grad_scale,
+                                    static_cast<float>(expand_min), partials, st);
+    MMB_CUDA_CHECK(cudaGetLastError());
+    if (block_sumsq_dev != nullptr) {
+      long long nblk = 0;
+      for (int i = 0; i < tab.nseg; ++i) nblk += tab.seg[i].numel / tab.seg[i].block_elems;
+      long long g2 = (nblk + warps_per_cta - 1) / warps_per_cta;
+      if (g2 > sms * 4) g2 = sms * 4;
+      if (g2 < 1) g2 = 1;
+      block_sumsq_kernel<<<static_cast<int>(g2), THREADS, 0, st>>>(tab, partials, block_sumsq_dev);
+      MMB_CUDA_CHECK(cudaGetLastError());
+    }
+  }
+  return MMB_OK;
+}
+
+}  // namespace mmb
+
+extern "C" {
+
+int64_t mmb_momentum_scratch_floats(const mmb_momentum_seg* segs, int nseg) {
+  int64_t total = 0;
+  for (int i = 0; i < nseg; ++i) {
+    if (segs[i].numel <= 0) continue;
+    mmb::Plan p = mmb::plan_segment(segs[i]);
+    total += p.nblocks * p.cpb;
+  }
+  return total;
+}
+
+int mmb_momentum_step(const mmb_momentum_seg* segs, int nseg, int grad_dtype, int state_format, int div_mode,
+                      float beta, float grad_scale, int expand_min, float* block_sumsq_dev, float* scratch_dev,
+                      int64_t scratch_floats, void* stream) {
+  return mmb::momentum_step_impl(segs, nseg, grad_dtype, state_format, div_mode, beta, grad_scale, expand_min,
+                                 block_sumsq_dev, scratch_dev, scratch_floats, stream);
+}
+
+int mmb_fp8_quantize(const float* value_dev, uint8_t* codes_dev, float* scale_dev, float* expand_dev,
+                     float* sqrt_minmax_dev, int64_t numel, int state_format, int is_signed, int div_mode,
+                     int expand_min, void* stream) {
+  using namespace mmb;
+  MMB_REQUIRE(state_format == MMB_STATE_FP8_ABSMAX || state_format == MMB_STATE_FP8_EXPAND,
+              "mmb_fp8_quantize: state_format %d", state_format);
+  MMB_REQUIRE(numel >= 0 && (numel == 0 || (value_dev && codes_dev && scale_dev)), "mmb_fp8_quantize: null pointer");
+  if (state_format == MMB_STATE_FP8_EXPAND)
+    MMB_REQUIRE(numel == 0 || (expand_dev && sqrt_minmax_dev), "mmb_fp8_quantize: expansion arrays missing");
+  if (numel == 0) return MMB_OK;
+  const int sms = sm_count();
+  if (sms <= 0) return fail(MMB_ERR_CUDA, "mmb_fp8_quantize: no CUDA device");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  long long groups = (numel + GROUP - 1) / GROUP;
+  long long want = (groups + THREADS / 32 - 1) / (THREADS / 32);
+  int grid = static_cast<int>(want < sms * 32LL ? want : sms * 32LL);
+  const float em = static_cast<float>(expand_min);
+#define MMB_Q(F, D) \
+  quantize_kernel<F, D><<<grid, THREADS, 0, st>>>(value_dev, codes_dev, scale_dev, expand_dev, sqrt_minmax_dev, numel, is_signed, em)
+  if (state_format == MMB_STATE_FP8_ABSMAX) {
+    if (div_mode == MMB_DIV_IEEE) MMB_Q(MMB_STATE_FP8_ABSMAX, MMB_DIV_IEEE); else MMB_Q(MMB_STATE_FP8_ABSMAX, MMB_DIV_FULL);
+  } else {
+    if (div_mode == MMB_DIV_IEEE) MMB_Q(MMB_STATE_FP8_EXPAND, MMB_DIV_IEEE); else MMB_Q(MMB_STATE_FP8_EXPAND, MMB_DIV_FULL);
+  }
+#undef MMB_Q
+  MMB_CUDA_CHECK(cudaGetLastError());
+  return MMB_OK;
+}
+
+int mmb_fp8_dequantize(const uint8_t* codes_dev, const float* scale_dev, const float* expand_dev,
+                       const float* sqrt_minmax_dev, float* out_dev, int64_t numel, int state_format, int is_signed,
+                       void* stream) {
+  using namespace mmb;
+  MMB_REQUIRE(state_format == MMB_STATE_FP8_ABSMAX || state_format == MMB_STATE_FP8_EXPAND,
+              "mmb_fp8_dequantize: state_format %d", state_format);
+  MMB_REQUIRE(numel >= 0 && (numel == 0 || (codes_dev && scale_dev && out_dev)), "mmb_fp8_dequantize: null pointer");
+  if (state_format == MMB_STATE_FP8_EXPAND)
+    MMB_REQUIRE(numel == 0 || (expand_dev && sqrt_minmax_dev), "mmb_fp8_dequantize: expansion arrays missing");
+  if (numel == 0) return MMB_OK;
+  const int sms = sm_count();
+  if (sms <= 0) return fail(MMB_ERR_CUDA, "mmb_fp8_dequantize: no CUDA device");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  long long want = (numel + THREADS - 1) / THREADS;
+  int grid = static_cast<int>(want < sms * 32LL ? want : sms * 32LL);
+  if (state_format == MMB_STATE_FP8_ABSMAX)
+    dequantize_kernel<MMB_STATE_FP8_ABSMAX, MMB_DIV_IEEE><<<grid, THREADS, 0, st>>>(codes_dev, scale_dev, expand_dev,
+                                                                                  sqrt_minmax_dev, out_dev, numel, is_signed);
+  else
+    dequantize_kernel<MMB_STATE_FP8_EXPAND, MMB_DIV_IEEE><<<grid, THREADS, 0, st>>>(codes_dev, scale_dev, expand_dev,
+                                                                                  sqrt_minmax_dev, out_dev, numel, is_signed);
+  MMB_CUDA_CHECK(cudaGetLastError());
+  return MMB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,98 @@
+"""Batched Newton-Schulz and the GEMM family it is built from (CUDA only).
+
+`newton_schulz_batched` mirrors the reference function of the same role,
+_newton_schulz_batched (pretrain/src/models/monarch/monarch_muon.py:36-50; the
+bf16 path of membench/src/models/monarch/monarch_muon.py:161-166): input a
+(batch, rows, cols) stack, output the same shape, Frobenius normalisation with
+eps on the norm, five quintic iterations, tall blocks handled without a
+transpose in memory.  Arithmetic is bf16 operands with fp32 accumulation on
+the tcgen05 tensor cores.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+_workspaces: dict = {}
+
+
+def _workspace(nbytes: int, device: torch.device) -> torch.Tensor:
+    """Grow-only per-device scratch (A, P and two X buffers); 1 KiB aligned by
+    the caching allocator's 512-byte granularity plus an explicit offset."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes + 1024:
+        _workspaces.pop(key, None)
+        buf = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    off = (-buf.data_ptr()) % 1024
+    return buf[off:off + nbytes]
+
+
+def release_workspaces() -> None:
+    _workspaces.clear()
+
+
+def newton_schulz_batched(stack: torch.Tensor, *, out: torch.Tensor | None = None,
+                          block_sumsq: torch.Tensor | None = None, backend: int = _lib.NS_TCGEN05,
+                          max_batch: int | None = None) -> torch.Tensor:
+    """Orthogonalise every (rows, cols) block of a bf16 CUDA stack.
+
+    out          optional destination (may be `stack` itself)
+    block_sumsq  optional fp32 [batch] sums of squares (otherwise computed)
+    max_batch    process the stack in slices of at most this many blocks to
+                 bound the workspace (default: whole stack)
+    """
+    _lib.require_cuda(stack)
+    if stack.dim() != 3:
+        raise ValueError("newton_schulz_batched expects (batch, rows, cols)")
+    if stack.dtype != torch.bfloat16:
+        raise TypeError("newton_schulz_batched computes in bfloat16; cast the stack first")
+    if not stack.is_contiguous():
+        raise ValueError("newton_schulz_batched expects a contiguous stack")
+    if out is None:
+        out = torch.empty_like(stack)
+    elif out.shape != stack.shape or out.dtype != stack.dtype or not out.is_contiguous():
+        raise ValueError("out must match the stack")
+    batch, rows, cols = stack.shape
+    if batch == 0:
+        return out
+    lib = _lib.load()
+    step = batch if not max_batch else min(batch, max_batch)
+    status = _lib.status_word(stack.device)
+    with torch.cuda.device(stack.device):
+        ws = _workspace(lib.mmb_ns_workspace_bytes(step, rows, cols), stack.device)
+        for b0 in range(0, batch, step):
+            nb = min(step, batch - b0)
+            ss = None if block_sumsq is None else block_sumsq[b0:b0 + nb]
+            _lib.check(lib.mmb_newton_schulz(stack[b0:b0 + nb].data_ptr(), out[b0:b0 + nb].data_ptr(), _lib.ptr(ss),
+                                             nb, rows, cols, ws.data_ptr(), ws.numel(), backend, status,
+                                             _lib.stream_ptr()), "newton_schulz")
+    return out
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, c: torch.Tensor | None = None, a_kmajor: bool = True,
+              b_kmajor: bool = True, alpha: float = 1.0, gamma: float = 0.0,
+              inv_norm: torch.Tensor | None = None, sigma_pow: int = 0,
+              backend: int = _lib.NS_TCGEN05) -> torch.Tensor:
+    """D[b] = sigma_b * (alpha * opA[b] @ opB[b]^T + gamma * C[b]) on bf16 stacks.
+
+    a is (batch, M, K) when a_kmajor else (batch, K, M); b likewise with N.
+    """
+    _lib.require_cuda(a, b)
+    batch = a.shape[0]
+    M, K = (a.shape[1], a.shape[2]) if a_kmajor else (a.shape[2], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[2]) if b_kmajor else (b.shape[2], b.shape[1])
+    if K != Kb or b.shape[0] != batch:
+        raise ValueError("operand shapes do not agree")
+    for t in (a, b, c):
+        if t is not None and (t.dtype != torch.bfloat16 or not t.is_contiguous()):
+            raise TypeError("gemm_bf16 expects contiguous bfloat16 tensors")
+    d = torch.empty(batch, M, N, dtype=torch.bfloat16, device=a.device)
+    lib = _lib.load()
+    with torch.cuda.device(a.device):
+        _lib.check(lib.mmb_gemm_bf16(a.data_ptr(), b.data_ptr(), _lib.ptr(c), d.data_ptr(), batch, M, N, K,
+                                     int(a_kmajor), int(b_kmajor), alpha, gamma, _lib.ptr(inv_norm), sigma_pow,
+                                     backend, _lib.status_word(a.device), _lib.stream_ptr()), "gemm_bf16")
+    return d

@@ -1,0 +1,344 @@
+"""MonarchMuonOptimizer for B200: the reference optimizer's API over CUDA kernels.
+
+Drop-in for the reference class of the same name
+(pretrain/src/models/monarch/monarch_muon.py:57-201; bf16 twin in
+membench/src/models/monarch/monarch_muon.py): same constructor, same two
+param groups (`update_type` "muon" for the 3-D Monarch factors, "adamw" for
+everything else), `group["lr"]` read at call time so LR schedulers work,
+parameters without a gradient skipped, state created lazily on the first
+step, standard `state_dict` / `load_state_dict` / step hooks.
+
+What differs is where the arithmetic runs.  A step is a handful of launches:
+
+  1. one fused momentum kernel over every Muon tensor (heavy ball + optional
+     FP8 state codec + bf16 copy for Newton-Schulz + per-block sums of
+     squares);
+  2. per block shape, 15 tcgen05 GEMM launches (5 x Gram / Poly / Apply) on
+     the momentum arena of that shape - the reference's torch.cat is gone
+     because momentum lives in one arena per shape;
+  3. one update launch per shape, one AdamW launch per <=128 tensors.
+
+There is no CPU path: tensors must live on a CUDA device.
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+
+import torch
+
+from . import _lib, fp8_state
+from .newton_schulz import newton_schulz_batched
+
+_STATE_FORMATS = ("param", "fp8_absmax", "fp8_expand")
+
+
+class _ShapeGroup:
+    """All Muon tensors of one (dtype, rows, cols), their arena slices and tables."""
+
+    def __init__(self, dtype, rows, cols):
+        self.dtype, self.rows, self.cols = dtype, rows, cols
+        self.params: list = []
+        self.block_start: list[int] = []      # first block of each tensor inside the group arena
+        self.nblocks = 0
+        self.m_arena = None                   # bf16 [nblocks, rows, cols]: Newton-Schulz input
+        self.ortho = None                     # bf16 [nblocks, rows, cols]: Newton-Schulz output
+        self.first_block_global = 0           # index of the group's first block in block_sumsq
+
+
+class MonarchMuonOptimizer(torch.optim.Optimizer):
+    """Muon (batched Newton-Schulz on 3-D Monarch factors) + AdamW in one optimizer.
+
+    Parameters (reference signature, monarch_muon.py:78-90)
+    ----------
+    muon_params, adamw_params : iterables of parameters
+    lr, momentum, adamw_betas, adamw_weight_decay, adamw_eps : as upstream
+
+    Extra keyword-only knobs (defaults reproduce the reference's behaviour)
+    ----------
+    state_format : "param" keeps `momentum_buffer` in the parameter dtype like
+        the reference; "fp8_absmax" / "fp8_expand" store it as E4M3 codes with
+        per-128-group side arrays (absmax scale, or COAT range expansion).
+    fp8_div : "ieee" or "full" - division used by the FP8 quantiser.
+    ns_backend : "tcgen05" (tensor cores) or "simt" (cross-check kernel).
+    ns_max_batch : slice Newton-Schulz into at most this many blocks per call
+        to bound its workspace.
+    """
+
+    def __init__(self, muon_params, adamw_params, *, lr: float = 5e-3, momentum: float = 0.95,
+                 adamw_betas: tuple[float, float] = (0.9, 0.95), adamw_weight_decay: float = 0.1,
+                 adamw_eps: float = 1e-8, state_format: str = "param", fp8_div: str = "ieee",
+                 ns_backend: str = "tcgen05", ns_max_batch: int | None = 256, expand_min: int = 16):
+        if state_format not in _STATE_FORMATS:
+            raise ValueError(f"state_format must be one of {_STATE_FORMATS}")
+        muon_params = list(muon_params)
+        adamw_params = list(adamw_params)
+        defaults = dict(lr=lr)
+        param_groups = [
+            {"params": muon_params, "update_type": "muon", "momentum": momentum},
+            {"params": adamw_params, "update_type": "adamw", "betas": adamw_betas,
+             "weight_decay": adamw_weight_decay, "eps": adamw_eps},
+        ]
+        super().__init__(param_groups, defaults)
+        self.state_format = state_format
+        self.fp8_div = {"ieee": _lib.DIV_IEEE, "full": _lib.DIV_FULL}[fp8_div]
+        self.ns_backend = {"tcgen05": _lib.NS_TCGEN05, "simt": _lib.NS_SIMT}[ns_backend]
+        self.ns_max_batch = ns_max_batch
+        self.expand_min = expand_min
+        self.grad_scale = 1.0            # multiplies Muon gradients inside the momentum kernel
+        self._plans: dict = {}           # id(group) -> plan
+        _lib.load()                      # fail now, not at the first step, if the library is missing
+
+    # ------------------------------------------------------------------ public
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for group in self.param_groups:
+            lr = group["lr"]
+            if group["update_type"] == "muon":
+                self._muon_step(group, lr)
+            else:
+                self._adamw_step(group, lr)
+        return loss
+
+    def block_sumsq(self, group_index: int = 0):
+        """fp32 sums of squares of bf16(momentum) per block from the last step (device tensor)."""
+        plan = self._plans.get(id(self.param_groups[group_index]))
+        return None if plan is None else plan["block_sumsq"]
+
+    # ------------------------------------------------------------ Muon: plan
+    def _fp8(self) -> bool:
+        return self.state_format != "param"
+
+    def _build_plan(self, group):
+        params = group["params"]
+        if not params:
+            return None
+        dev = params[0].device
+        shapes: "OrderedDict[tuple, _ShapeGroup]" = OrderedDict()
+        for p in params:
+            _lib.require_cuda(p)
+            if p.dim() != 3:
+                raise ValueError("Muon parameters must be 3-D (nblocks, rows, cols) Monarch factors")
+            if p.device != dev:
+                raise ValueError("all Muon parameters must live on one device")
+            _lib.dtype_code(p.dtype)
+            key = (p.dtype, p.shape[1], p.shape[2])
+            sg = shapes.get(key)
+            if sg is None:
+                sg = shapes[key] = _ShapeGroup(*key)
+            sg.params.append(p)
+            sg.block_start.append(sg.nblocks)
+            sg.nblocks += p.shape[0]
+        plan = {"device": dev, "shapes": shapes, "params": list(params), "entry": {}}
+        total_blocks = 0
+        mplan = fp8_state.MomentumPlan(dev)
+        for sg in shapes.values():
+            sg.first_block_global = total_blocks
+            total_blocks += sg.nblocks
+            sg.m_arena = torch.zeros(sg.nblocks, sg.rows, sg.cols, dtype=torch.bfloat16, device=dev)
+            blk = sg.rows * sg.cols
+            in_place_state = self.state_format == "param" and sg.dtype == torch.bfloat16
+            # Newton-Schulz may overwrite its input unless that input is the state itself
+            sg.ortho = torch.empty_like(sg.m_arena) if in_place_state else sg.m_arena
+            sg.fp32_state = None
+            sg.codes = sg.scale = sg.expand = sg.sqrt_mm = None
+            if self.state_format == "param" and sg.dtype == torch.float32:
+                sg.fp32_state = torch.zeros(sg.nblocks, sg.rows, sg.cols, dtype=torch.float32, device=dev)
+            if self._fp8():
+                sg.codes = torch.zeros(sg.nblocks, sg.rows, sg.cols, dtype=torch.uint8, device=dev)
+                ngroups = sum(fp8_state.groups_of(p.numel()) for p in sg.params)
+                sg.scale = torch.zeros(ngroups, dtype=torch.float32, device=dev)
+                if self.state_format == "fp8_expand":
+                    sg.expand = torch.ones(ngroups, dtype=torch.float32, device=dev)
+                    sg.sqrt_mm = torch.ones(ngroups, dtype=torch.float32, device=dev)
+            g_at = 0
+            for p, b0 in zip(sg.params, sg.block_start):
+                nb = p.shape[0]
+                m_view = sg.m_arena[b0:b0 + nb]
+                ng = fp8_state.groups_of(p.numel())
+                views = {}
+                if self._fp8():
+                    state_t = sg.codes[b0:b0 + nb]
+                    views["momentum_buffer"] = state_t.view(torch.float8_e4m3fn)
+                    views["scale_momentum_buffer"] = sg.scale[g_at:g_at + ng]
+                    if sg.expand is not None:
+                        views["expand_momentum_buffer"] = sg.expand[g_at:g_at + ng]
+                        views["sqrt_minmax_momentum_buffer"] = sg.sqrt_mm[g_at:g_at + ng]
+                elif sg.fp32_state is not None:
+                    state_t = sg.fp32_state[b0:b0 + nb]
+                    views["momentum_buffer"] = state_t
+                else:
+                    state_t = m_view
+                    views["momentum_buffer"] = m_view
+                idx = len(mplan.entries)
+                mplan.add(state=state_t, m_bf16=m_view, numel=p.numel(), block_elems=blk,
+                          scale=views.get("scale_momentum_buffer"), expand=views.get("expand_momentum_buffer"),
+                          sqrt_minmax=views.get("sqrt_minmax_momentum_buffer"))
+                # block sums are indexed globally over all shape groups
+                mplan.entries[idx]["first_block"] = sg.first_block_global + b0
+                plan["entry"][id(p)] = (idx, sg, b0, views)
+                g_at += ng
+        plan["momentum"] = mplan
+        plan["block_sumsq"] = torch.zeros(total_blocks, dtype=torch.float32, device=dev)
+        plan["scratch"] = None
+        return plan
+
+    def _plan_for(self, group):
+        plan = self._plans.get(id(group))
+        if plan is None or len(plan["params"]) != len(group["params"]) or \
+                any(a is not b for a, b in zip(plan["params"], group["params"])):
+            plan = self._build_plan(group)
+            self._plans[id(group)] = plan
+        return plan
+
+    def _state_code(self, sg) -> int:
+        if self.state_format == "fp8_absmax":
+            return _lib.STATE_FP8_ABSMAX
+        if self.state_format == "fp8_expand":
+            return _lib.STATE_FP8_EXPAND
+        return _lib.STATE_BF16 if sg.dtype == torch.bfloat16 else _lib.STATE_F32
+
+    # ------------------------------------------------------------ Muon: step
+    def _muon_step(self, group, lr: float) -> None:
+        live = [p for p in group["params"] if p.grad is not None]
+        if not live:
+            return
+        plan = self._plan_for(group)
+        dev = plan["device"]
+        lib = _lib.load()
+        with torch.cuda.device(dev):
+            # register state lazily, like _get_momentum_buffer (monarch_muon.py:133-137)
+            for p in live:
+                st = self.state[p]
+                if "momentum_buffer" not in st:
+                    st.update(plan["entry"][id(p)][3])
+            # 1. momentum (+codec, +bf16 copy, +block norms): one table per (grad dtype, state format)
+            buckets: "OrderedDict[tuple, list]" = OrderedDict()
+            for p in live:
+                idx, sg, _, _ = plan["entry"][id(p)]
+                g = p.grad
+                if g.shape != p.shape:
+                    raise ValueError("gradient shape differs from its parameter")
+                if not g.is_contiguous():
+                    g = g.contiguous()
+                buckets.setdefault((g.dtype, self._state_code(sg)), []).append((idx, g))
+            mplan = plan["momentum"]
+            for (gdtype, scode), items in buckets.items():
+                segs = mplan.table([g for _, g in items], [i for i, _ in items])
+                need = fp8_state.scratch_floats(segs, len(items))
+                if plan["scratch"] is None or plan["scratch"].numel() < need:
+                    plan["scratch"] = torch.empty(need, dtype=torch.float32, device=dev)
+                fp8_state.momentum_step(segs, len(items), grad_dtype=gdtype, state_format=scode,
+                                        beta=group["momentum"], grad_scale=self.grad_scale,
+                                        div_mode=self.fp8_div, expand_min=self.expand_min,
+                                        block_sumsq=plan["block_sumsq"], scratch=plan["scratch"])
+            # 2. Newton-Schulz and 3. update, per shape and per run of consecutive live tensors
+            for sg in plan["shapes"].values():
+                alpha = -lr * (sg.rows / sg.cols) ** 0.5
+                runs: list[list] = []
+                prev_live = False
+                for p, b0 in zip(sg.params, sg.block_start):
+                    if p.grad is None:
+                        prev_live = False
+                        continue
+                    if not prev_live:
+                        runs.append([])
+                    runs[-1].append((p, b0))
+                    prev_live = True
+                for run in runs:
+                    b0 = run[0][1]
+                    b1 = run[-1][1] + run[-1][0].shape[0]
+                    ss = plan["block_sumsq"][sg.first_block_global + b0: sg.first_block_global + b1]
+                    newton_schulz_batched(sg.m_arena[b0:b1], out=sg.ortho[b0:b1], block_sumsq=ss,
+                                          backend=self.ns_backend, max_batch=self.ns_max_batch)
+                    segs = (_lib.UpdateSeg * len(run))()
+                    for k, (p, pb0) in enumerate(run):
+                        if not p.data.is_contiguous():
+                            raise ValueError("Muon parameters must be contiguous")
+                        segs[k].weight = p.data.data_ptr()
+                        segs[k].ortho = sg.ortho[pb0:pb0 + p.shape[0]].data_ptr()
+                        segs[k].numel = p.numel()
+                    _lib.check(lib.mmb_muon_update(segs, len(run), _lib.dtype_code(sg.dtype), alpha,
+                                                   _lib.stream_ptr()), "muon_update")
+
+    # ----------------------------------------------------------------- AdamW
+    def _adamw_step(self, group, lr: float) -> None:
+        beta1, beta2 = group["betas"]
+        by_dtype: "OrderedDict[torch.dtype, list]" = OrderedDict()
+        for p in group["params"]:
+            if p.grad is None:
+                continue
+            _lib.require_cuda(p)
+            state = self.state[p]
+            if len(state) == 0:
+                state["step"] = 0
+                state["exp_avg"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+                state["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+            state["step"] += 1
+            g = p.grad
+            if g.dtype != p.dtype:
+                g = g.to(p.dtype)
+            if not g.is_contiguous():
+                g = g.contiguous()
+            if not p.data.is_contiguous():
+                raise ValueError("AdamW parameters must be contiguous")
+            by_dtype.setdefault(p.dtype, []).append((p, g, state))
+        if not by_dtype:
+            return
+        lib = _lib.load()
+        for dtype, items in by_dtype.items():
+            segs = (_lib.AdamWSeg * len(items))()
+            for k, (p, g, state) in enumerate(items):
+                segs[k].param = p.data.data_ptr()
+                segs[k].grad = g.data_ptr()
+                segs[k].exp_avg = state["exp_avg"].data_ptr()
+                segs[k].exp_avg_sq = state["exp_avg_sq"].data_ptr()
+                segs[k].numel = p.numel()
+                segs[k].step = state["step"]
+            with torch.cuda.device(items[0][0].device):
+                _lib.check(lib.mmb_adamw_step(segs, len(items), _lib.dtype_code(dtype), lr, beta1, beta2,
+                                              group["weight_decay"], group["eps"], _lib.stream_ptr()), "adamw_step")
+
+    # ----------------------------------------------------------- checkpoints
+    _MANAGED = ("momentum_buffer", "scale_momentum_buffer", "expand_momentum_buffer",
+                "sqrt_minmax_momentum_buffer")
+
+    def load_state_dict(self, state_dict):
+        """Restore a reference-shaped state dict.  torch casts floating state to
+        the parameter dtype, which would squash fp32 scale arrays and FP8 codes
+        (coat_state_muon.py:141-151 works around the same thing), so the Muon
+        state is taken out first and copied into the arenas afterwards."""
+        saved_ids = [i for g in state_dict["param_groups"] for i in g["params"]]
+        params = [p for g in self.param_groups for p in g["params"]]
+        if len(saved_ids) != len(params):
+            raise ValueError("loaded state dict has a different number of parameters")
+        stripped_state = {}
+        managed = {}
+        for pid, entry in state_dict["state"].items():
+            keep = {k: v for k, v in entry.items() if k not in self._MANAGED}
+            mine = {k: v for k, v in entry.items() if k in self._MANAGED}
+            if keep:
+                stripped_state[pid] = keep
+            if mine:
+                managed[pid] = mine
+        super().load_state_dict({"state": stripped_state, "param_groups": state_dict["param_groups"]})
+        by_id = dict(zip(saved_ids, params))
+        muon_group = self.param_groups[0]
+        plan = self._plan_for(muon_group) if muon_group["params"] else None
+        for pid, mine in managed.items():
+            p = by_id[pid]
+            _, _, _, views = plan["entry"][id(p)]
+            for k, v in mine.items():
+                if k not in views:
+                    raise ValueError(f"state '{k}' does not fit state_format={self.state_format}")
+                dst = views[k]
+                src = v.to(dst.device)
+                if dst.dtype == torch.float8_e4m3fn:
+                    src = src.to(torch.float8_e4m3fn) if src.dtype != torch.float8_e4m3fn else src
+                    dst.view(torch.uint8).copy_(src.view(torch.uint8).reshape(dst.shape))
+                else:
+                    dst.copy_(src.to(dst.dtype).reshape(dst.shape))
+            self.state[p].update(views)
