@@ -1,0 +1,315 @@
+#!/usr/bin/env python
+"""Benchmark of the Monarch-Muon optimizer step on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--nblocks 4]
+
+Workload (N = 1): the full optimizer step at the 6.89B-dense-reference size
+with 4-block Monarch factors: 448 Muon tensors (1408 blocks 1024x1024, 256
+blocks 2752x1024, 128 blocks 1024x2752 = 2,558,525,440 elements) with FP8
+(E4M3 absmax) momentum state, batched Newton-Schulz and the weight update, plus
+the AdamW group (embedding, LM head, 65 norm vectors; vocab 50257).  Weights
+N(0, 0.02) and gradients N(0, 1e-3) are seeded synthetic bf16 tensors - there is
+no dataset on this path.
+
+One JSON line is printed by rank 0.  `value` is device-timed milliseconds per
+step with gradients already in HBM; `e2e` repeats the measurement through the
+public `optimizer.step()` with every gradient copied from pinned host memory
+inside the timed region and the per-block momentum norms read back.
+
+`--impl reference` times the CPU restatement of the reference step (oracle/,
+torch CPU kernels on all host threads) on a bounded sample of blocks and scales
+it to the full step by block and element counts.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from monarch_muon_b200 import shapes as S  # noqa: E402
+
+METRIC = "monarch_muon_opt_step_ms_6.89B_ref_nb4"
+H100_PUBLISHED_MS = 304.4      # README.md:16 of the reference, one H100, bf16 state
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"],
+                    bf16_tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+# ----------------------------------------------------------------- clock sampler
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows: list[list[str]] = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            if len(r) < 8:
+                continue
+            try:
+                sm.append(float(r[0]))
+                smax = float(r[1])
+            except ValueError:
+                continue
+            for name, v in zip(names, r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------ the workload
+def build_workload(device, nblocks: int, seed: int = 1234, shard=None):
+    """Parameters and gradients of the 6.89B-reference model's optimizer step.
+    `shard=(rank, world)` keeps every world-th tensor's blocks split evenly: each
+    rank owns 1/world of the blocks of every tensor (used for N > 1)."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    m = S.MODEL_689B
+    muon_shapes = S.llama_monarch_muon_shapes(m["d_model"], m["n_layers"], m["intermediate"], nblocks)
+    adamw_shapes = S.llama_adamw_shapes(m["d_model"], m["n_layers"], m["vocab"])
+    muon, adamw = [], []
+    for s in muon_shapes:
+        w = torch.empty(s, dtype=torch.bfloat16, device=device).normal_(0.0, 0.02, generator=gen)
+        muon.append(torch.nn.Parameter(w))
+    for s in adamw_shapes:
+        w = torch.empty(s, dtype=torch.bfloat16, device=device).normal_(0.0, 0.02, generator=gen)
+        adamw.append(torch.nn.Parameter(w))
+    for p in muon + adamw:
+        p.grad = torch.empty_like(p).normal_(0.0, 1e-3, generator=gen)
+    return muon, adamw
+
+
+def workload_counts(nblocks: int):
+    m = S.MODEL_689B
+    shp = S.llama_monarch_muon_shapes(m["d_model"], m["n_layers"], m["intermediate"], nblocks)
+    flops = sum(s[0] * S.ns_flops(s[1], s[2]) for s in shp)
+    muon_elems = sum(s[0] * s[1] * s[2] for s in shp)
+    adamw_elems = sum(int(torch.Size(s).numel()) for s in S.llama_adamw_shapes(m["d_model"], m["n_layers"], m["vocab"]))
+    return flops, muon_elems, adamw_elems
+
+
+# ------------------------------------------------------------------ CPU baseline
+def cpu_reference_step_ms(nblocks: int, steps: int, warmup: int, threads: int | None = None):
+    """The oracle's restatement of the reference step (bf16 twin: bf16 state,
+    bf16 Newton-Schulz) on host cores, on a sample of blocks, scaled to the full
+    step.  Returns (ms per full step, description of the sample, threads)."""
+    from oracle import muon_oracle
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    m = S.MODEL_689B
+    shp = S.llama_monarch_muon_shapes(m["d_model"], m["n_layers"], m["intermediate"], nblocks)
+    full: dict = {}
+    for nb, r, c in shp:
+        full[(r, c)] = full.get((r, c), 0) + nb
+    # the same fraction of every block shape (96 of the 1408 square blocks at nblocks=4)
+    frac = 96.0 / max(full.values())
+    sample = {k: max(1, int(round(v * frac))) for k, v in full.items()}
+    gen = torch.Generator().manual_seed(7)
+    groups = {}
+    for (r, c), nb in sample.items():
+        w = (0.02 * torch.randn(nb, r, c, generator=gen)).bfloat16()
+        g = (1e-3 * torch.randn(nb, r, c, generator=gen)).bfloat16()
+        groups[(r, c)] = (w, g, torch.zeros_like(w))
+    _, _, adamw_elems = workload_counts(nblocks)
+    a_n = 1 << 23
+    ap = (0.02 * torch.randn(a_n, generator=gen)).bfloat16()
+    ag = (1e-3 * torch.randn(a_n, generator=gen)).bfloat16()
+    am, av = torch.zeros_like(ap), torch.zeros_like(ap)
+
+    def one_pass(step_no: int) -> float:
+        total = 0.0
+        for (r, c), (w, g, buf) in groups.items():
+            t0 = time.perf_counter()
+            muon_oracle.muon_group_step([w], [g], [buf], lr=0.02, beta=0.95, ns_dtype=torch.bfloat16)
+            total += (time.perf_counter() - t0) * full[(r, c)] / sample[(r, c)]
+        t0 = time.perf_counter()
+        muon_oracle.adamw_tensor_step(ap, ag, am, av, step_no, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, eps=1e-8)
+        total += (time.perf_counter() - t0) * adamw_elems / a_n
+        return total * 1e3
+
+    with torch.no_grad():
+        for i in range(warmup):
+            one_pass(i + 1)
+        times = [one_pass(warmup + i + 1) for i in range(steps)]
+    desc = ("bf16 reference step (momentum, cat, Newton-Schulz, update) on "
+            + ", ".join(f"{nb} of {full[k]} blocks {k[0]}x{k[1]}" for k, nb in sample.items())
+            + f"; AdamW on {a_n} of {adamw_elems} elements; each part scaled linearly to the full count")
+    return sum(times) / len(times), desc, threads
+
+
+# ------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--nblocks", type=int, default=4, choices=[2, 4])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {"workload": f"full optimizer step, 6.89B-dense-reference LLaMA, Monarch nblocks={args.nblocks}, "
+                          "FP8 E4M3 absmax momentum state, bf16 weights/grads, AdamW group vocab 50257",
+              "cache": "inputs_larger_than_l2 (5.9 GB of gradients and 5.9 GB of weights per step)"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        ms, desc, threads = cpu_reference_step_ms(args.nblocks, max(1, args.steps), max(0, args.warmup))
+        line = {"impl": "reference", "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": ms, "unit": "ms", "cores": threads, "kind": "port", "sample": desc},
+                "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return 0
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path for the product")
+    if world > 1:
+        from bench_sharded import run_sharded   # multi-GPU path lives beside this file
+        return run_sharded(args, rank, world, local_rank, config, METRIC)
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    from monarch_muon_b200 import MonarchMuonOptimizer, _lib
+
+    muon, adamw = build_workload(dev, args.nblocks)
+    opt = MonarchMuonOptimizer(muon, adamw, lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95),
+                               adamw_weight_decay=0.1, adamw_eps=1e-8, state_format="fp8_absmax")
+    flops, muon_elems, adamw_elems = workload_counts(args.nblocks)
+    pk = peaks()
+
+    for _ in range(max(3, args.warmup)):
+        opt.step()
+    torch.cuda.synchronize()
+    assert _lib.read_status(dev) == 0, "a kernel reported an expired wait"
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    opt.enable_phase_timing(True)
+    l0 = _lib.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        opt.step()
+    e1.record()
+    torch.cuda.synchronize()
+    launches = _lib.launch_count() - l0
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    phases = {k: v / args.steps for k, v in opt.phase_times_ms().items()}
+    opt.enable_phase_timing(False)
+    status = _lib.read_status(dev)
+
+    ns_ms = phases.get("newton_schulz", float("nan"))
+    ach_tf = flops / (ns_ms * 1e-3) / 1e12
+    roofline = {"kernel": "gemm_kernel (tcgen05 Newton-Schulz GEMMs, 15 launches per block-shape slice)",
+                "bound": "tensor", "achieved": ach_tf, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                "frac": ach_tf / pk["bf16_tflops_sustained"], "peak_kind": f"{pk['source']}, sustained bf16 GEMM",
+                "traffic": None}
+    mom_ms = phases.get("momentum", float("nan"))
+    mom_gbs = muon_elems * S.FP8_ABSMAX_BYTES_PER_ELEM / (mom_ms * 1e-3) / 1e9
+    roofline_fp8 = {"kernel": "momentum_kernel (FP8 absmax heavy-ball)", "bound": "hbm", "achieved": mom_gbs,
+                    "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": mom_gbs / pk["hbm_gbs"],
+                    "peak_kind": f"{pk['source']}, copy bandwidth", "traffic": None}
+
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(opt, muon, adamw, args.steps, dev)
+    cpu = None
+    if not args.no_cpu_baseline:
+        cms, desc, threads = cpu_reference_step_ms(args.nblocks, 1, 1)
+        cpu = {"value": cms, "unit": "ms", "cores": threads, "kind": "port", "sample": desc}
+
+    line = {"metric": METRIC, "value": ms, "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": ms / H100_PUBLISHED_MS, "dtype": "bf16", "data": "synthetic", "config": config,
+            "phases_ms": phases, "roofline": roofline, "roofline_fp8_state": roofline_fp8,
+            "ns_algorithmic_tflop_per_step": flops / 1e12, "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": launches, "clocks": clocks, "device_status": status,
+            "baseline_note": "vs_baseline divides by the reference's published 304.4 ms on one H100 (bf16 state)"}
+    print(json.dumps(line))
+    return 0
+
+
+def run_e2e(opt, muon, adamw, steps: int, dev):
+    """optimizer.step() with all gradients arriving from pinned host memory inside
+    the timed region, and the per-block momentum sums of squares read back."""
+    params = muon + adamw
+    host = [torch.empty(p.shape, dtype=p.dtype, pin_memory=True).copy_(p.grad) for p in params]
+    h2d = sum(h.numel() * h.element_size() for h in host)
+    ss = opt.block_sumsq()
+    out_host = torch.empty(ss.shape, dtype=ss.dtype, pin_memory=True)
+    d2h = out_host.numel() * out_host.element_size()
+
+    def one():
+        for p, h in zip(params, host):
+            p.grad.copy_(h, non_blocking=True)
+        opt.step()
+        out_host.copy_(opt.block_sumsq(), non_blocking=True)
+
+    for _ in range(2):
+        one()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    return {"value": e0.elapsed_time(e1) / steps, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "note": "gradients copied from pinned host memory each step, then optimizer.step(), then block norms read back"}
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -56,6 +56,8 @@ extern "C" {
 
 int mmb_version(void);
 const char* mmb_last_error(void);
+/* Kernels launched by this library in this process so far. */
+int64_t mmb_launch_count(void);
 
 /* ------------------------------------------------------------------------
  * Heavy-ball momentum with optimizer-state codec, fused:

@@ -40,6 +40,7 @@ _vp, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
 SYMBOLS = {
     "mmb_version": (_i, []),
     "mmb_last_error": (C.c_char_p, []),
+    "mmb_launch_count": (_i64, []),
     "mmb_momentum_scratch_floats": (_i64, [C.POINTER(MomentumSeg), _i]),
     "mmb_momentum_step": (_i, [C.POINTER(MomentumSeg), _i, _i, _i, _i, _f, _f, _i, _vp, _vp, _i64, _vp]),
     "mmb_fp8_quantize": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp]),
@@ -127,3 +128,8 @@ def read_status(device: torch.device, reset: bool = True) -> int:
         check(load().mmb_device_status_read(status_word(device), C.byref(host), int(reset), stream_ptr()),
               "device_status_read")
     return host.value
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(load().mmb_launch_count())

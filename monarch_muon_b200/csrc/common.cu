@@ -1,6 +1,7 @@
 // Error reporting, device queries and the device status word.
 #include "common.cuh"
 
+#include <atomic>
 #include <cstring>
 
 namespace mmb {
@@ -17,6 +18,10 @@ int fail(int code, const char* fmt, ...) {
   va_end(ap);
   return code;
 }
+
+static std::atomic<long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launches() { return g_launches.load(std::memory_order_relaxed); }
 
 int sm_count() {
   static thread_local int cached_dev = -1;
@@ -37,6 +42,8 @@ int sm_count() {
 extern "C" {
 
 int mmb_version(void) { return 100; }
+
+int64_t mmb_launch_count(void) { return mmb::launches(); }
 
 const char* mmb_last_error(void) { return mmb::error_buffer(); }
 

@@ -35,6 +35,9 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Process-wide count of kernels this library has launched (mmb_launch_count()).
+void count_launch(int n = 1);
+
 // Device status codes stored by kernels (first writer wins).
 enum : int32_t {
   STATUS_OK = 0,

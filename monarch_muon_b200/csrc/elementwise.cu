@@ -240,6 +240,7 @@ int mmb_muon_update(const mmb_update_seg* segs, int nseg, int weight_dtype, floa
     else
       muon_update_kernel<float><<<grid, THREADS, 0, st>>>(tab, alpha);
     MMB_CUDA_CHECK(cudaGetLastError());
+  count_launch();
   }
   return MMB_OK;
 }
@@ -290,6 +291,7 @@ int mmb_adamw_step(const mmb_adamw_seg* segs, int nseg, int dtype, float lr, flo
     else
       adamw_kernel<float><<<grid, THREADS, 0, st>>>(tab, decay, beta1, omb1, beta2, omb2, eps);
     MMB_CUDA_CHECK(cudaGetLastError());
+  count_launch();
   }
   return MMB_OK;
 }

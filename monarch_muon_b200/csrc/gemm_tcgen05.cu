@@ -428,6 +428,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, i
   MMB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES));
   kern<<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, st>>>(ta, tb, args);
   MMB_CUDA_CHECK(cudaGetLastError());
+  count_launch();
   return MMB_OK;
 }
 

@@ -580,6 +580,7 @@ int momentum_step_impl(const mmb_momentum_seg* segs, int nseg, int grad_dtype, i
       launch_momentum_format<float>(state_format, div_mode, tab, grid, beta, grad_scale,
                                     static_cast<float>(expand_min), partials, st);
     MMB_CUDA_CHECK(cudaGetLastError());
+  count_launch();
     if (block_sumsq_dev != nullptr) {
       long long nblk = 0;
       for (int i = 0; i < tab.nseg; ++i) nblk += tab.seg[i].numel / tab.seg[i].block_elems;
@@ -588,6 +589,7 @@ int momentum_step_impl(const mmb_momentum_seg* segs, int nseg, int grad_dtype, i
       if (g2 < 1) g2 = 1;
       block_sumsq_kernel<<<static_cast<int>(g2), THREADS, 0, st>>>(tab, partials, block_sumsq_dev);
       MMB_CUDA_CHECK(cudaGetLastError());
+  count_launch();
     }
   }
   return MMB_OK;
@@ -640,6 +642,7 @@ int mmb_fp8_quantize(const float* value_dev, uint8_t* codes_dev, float* scale_de
   }
 #undef MMB_Q
   MMB_CUDA_CHECK(cudaGetLastError());
+  count_launch();
   return MMB_OK;
 }
 
@@ -665,6 +668,7 @@ int mmb_fp8_dequantize(const uint8_t* codes_dev, const float* scale_dev, const f
     dequantize_kernel<MMB_STATE_FP8_EXPAND, MMB_DIV_IEEE><<<grid, THREADS, 0, st>>>(codes_dev, scale_dev, expand_dev,
                                                                                   sqrt_minmax_dev, out_dev, numel, is_signed);
   MMB_CUDA_CHECK(cudaGetLastError());
+  count_launch();
   return MMB_OK;
 }
 

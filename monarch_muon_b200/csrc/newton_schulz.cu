@@ -105,6 +105,7 @@ int gemm_simt(const void* a, const void* b, const void* c, void* d, int batch, i
                                           b_k, static_cast<long long>(N) * K, alpha, gamma,
                                           inv_norm ? inv_norm + b0 : nullptr, sigma_pow);
     MMB_CUDA_CHECK(cudaGetLastError());
+  count_launch();
   }
   return MMB_OK;
 }
@@ -230,10 +231,12 @@ int mmb_newton_schulz(const void* x_dev, void* out_dev, const float* block_sumsq
     block_sumsq_bf16_kernel<<<batch, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x_dev),
                                                    static_cast<long long>(rows) * cols, sumsq);
     MMB_CUDA_CHECK(cudaGetLastError());
+  count_launch();
     ss = sumsq;
   }
   inv_norm_kernel<<<(batch + 255) / 256, 256, 0, st>>>(ss, inv, batch);
   MMB_CUDA_CHECK(cudaGetLastError());
+  count_launch();
 
   const bool tall = rows > cols;
   const int m = tall ? cols : rows;

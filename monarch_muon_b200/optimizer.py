@@ -86,6 +86,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         self.expand_min = expand_min
         self.grad_scale = 1.0            # multiplies Muon gradients inside the momentum kernel
         self._plans: dict = {}           # id(group) -> plan
+        self._marks = None               # list of (phase, cuda event) while phase timing is on
         _lib.load()                      # fail now, not at the first step, if the library is missing
 
     # ------------------------------------------------------------------ public
@@ -102,6 +103,28 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
             else:
                 self._adamw_step(group, lr)
         return loss
+
+    # Phase timing: CUDA events on the current stream at phase boundaries.
+    def enable_phase_timing(self, on: bool = True) -> None:
+        self._marks = [] if on else None
+
+    def _mark(self, phase: str) -> None:
+        if self._marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._marks.append((phase, ev))
+
+    def phase_times_ms(self) -> dict:
+        """Milliseconds per phase accumulated since phase timing was enabled
+        (call after a synchronise); clears the recorded events."""
+        out: dict = {}
+        marks = self._marks or []
+        for (_, e0), (name, e1) in zip(marks, marks[1:]):
+            if name != "begin":
+                out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        if self._marks is not None:
+            self._marks = []
+        return out
 
     def block_sumsq(self, group_index: int = 0):
         """fp32 sums of squares of bf16(momentum) per block from the last step (device tensor)."""
@@ -210,6 +233,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         dev = plan["device"]
         lib = _lib.load()
         with torch.cuda.device(dev):
+            self._mark("begin")
             # register state lazily, like _get_momentum_buffer (monarch_muon.py:133-137)
             for p in live:
                 st = self.state[p]
@@ -235,6 +259,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                                         beta=group["momentum"], grad_scale=self.grad_scale,
                                         div_mode=self.fp8_div, expand_min=self.expand_min,
                                         block_sumsq=plan["block_sumsq"], scratch=plan["scratch"])
+            self._mark("momentum")
             # 2. Newton-Schulz and 3. update, per shape and per run of consecutive live tensors
             for sg in plan["shapes"].values():
                 alpha = -lr * (sg.rows / sg.cols) ** 0.5
@@ -254,6 +279,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                     ss = plan["block_sumsq"][sg.first_block_global + b0: sg.first_block_global + b1]
                     newton_schulz_batched(sg.m_arena[b0:b1], out=sg.ortho[b0:b1], block_sumsq=ss,
                                           backend=self.ns_backend, max_batch=self.ns_max_batch)
+                    self._mark("newton_schulz")
                     segs = (_lib.UpdateSeg * len(run))()
                     for k, (p, pb0) in enumerate(run):
                         if not p.data.is_contiguous():
@@ -263,6 +289,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                         segs[k].numel = p.numel()
                     _lib.check(lib.mmb_muon_update(segs, len(run), _lib.dtype_code(sg.dtype), alpha,
                                                    _lib.stream_ptr()), "muon_update")
+                    self._mark("update")
 
     # ----------------------------------------------------------------- AdamW
     def _adamw_step(self, group, lr: float) -> None:
@@ -289,6 +316,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         if not by_dtype:
             return
         lib = _lib.load()
+        self._mark("begin")
         for dtype, items in by_dtype.items():
             segs = (_lib.AdamWSeg * len(items))()
             for k, (p, g, state) in enumerate(items):
@@ -301,6 +329,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
             with torch.cuda.device(items[0][0].device):
                 _lib.check(lib.mmb_adamw_step(segs, len(items), _lib.dtype_code(dtype), lr, beta1, beta2,
                                               group["weight_decay"], group["eps"], _lib.stream_ptr()), "adamw_step")
+        self._mark("adamw")
 
     # ----------------------------------------------------------- checkpoints
     _MANAGED = ("momentum_buffer", "scale_momentum_buffer", "expand_momentum_buffer",

@@ -1,0 +1,267 @@
+"""The optimizer step through the public API on a GPU, against the CPU oracle."""
+import copy
+import io
+
+import numpy as np
+import pytest
+import torch
+
+import golden_inputs as gi
+
+pytestmark = pytest.mark.gpu
+
+
+def relf(a, b):
+    a = a.float().cpu()
+    b = b.float().cpu()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def _oracle(case, ns_bf16=True):
+    from oracle import muon_oracle
+    dtype, _, _, hyper = gi.OPT_CASES[case]
+    muon, adamw = gi.opt_params(case)
+    muon = [p.data for p in muon]
+    adamw = [p.data for p in adamw]
+    opt = muon_oracle.OracleMonarchMuon(muon, adamw, lr=hyper["lr"], momentum=hyper["momentum"],
+                                        adamw_betas=hyper["betas"], adamw_weight_decay=hyper["weight_decay"],
+                                        adamw_eps=hyper["eps"], ns_dtype=torch.bfloat16 if ns_bf16 else None)
+    opt.lr["adamw"] = hyper["adamw_lr"]
+    return opt, muon, adamw
+
+
+def _ours(case, **kw):
+    from monarch_muon_b200 import MonarchMuonOptimizer
+    dtype, _, _, hyper = gi.OPT_CASES[case]
+    muon, adamw = gi.opt_params(case)
+    muon = [torch.nn.Parameter(p.data.cuda()) for p in muon]
+    adamw = [torch.nn.Parameter(p.data.cuda()) for p in adamw]
+    cls = kw.pop("cls", MonarchMuonOptimizer)
+    opt = cls(muon, adamw, lr=hyper["lr"], momentum=hyper["momentum"], adamw_betas=hyper["betas"],
+              adamw_weight_decay=hyper["weight_decay"], adamw_eps=hyper["eps"], **kw)
+    opt.param_groups[1]["lr"] = hyper["adamw_lr"]
+    return opt, muon, adamw
+
+
+def _feed(muon, adamw, mg, ag):
+    for p, g in zip(muon, mg):
+        p.grad = None if g is None else g.cuda()
+    for p, g in zip(adamw, ag):
+        p.grad = None if g is None else g.cuda()
+
+
+# Tolerances (relative Frobenius norm):
+#  - weight *increments* after each step vs the bf16-Newton-Schulz oracle: the
+#    Newton-Schulz tolerance (5e-2) for fp32 weights; bf16 weights add their own
+#    storage rounding (one bf16 ulp of |W| ~ 2e-2 is ~7% of one step's increment).
+#  - weights themselves: 1e-2 (the test blocks are only 64-128 wide, so three
+#    steps of lr 0.02 move the weights by a third of their norm; 5e-2 of that).
+TOL_DELTA = {"fp32": 5e-2, "bf16": 1.2e-1}
+TOL_W = 1e-2
+
+
+@pytest.mark.parametrize("case", ["fp32", "bf16"])
+def test_three_steps_match_oracle(case):
+    from monarch_muon_b200 import _lib
+    ref, rmuon, radamw = _oracle(case)
+    w0 = [p.clone() for p in rmuon]
+    opt, muon, adamw = _ours(case)
+    for step in range(gi.OPT_STEPS):
+        mg, ag = gi.opt_grads(case, step)
+        ref.step(mg, ag)
+        _feed(muon, adamw, mg, ag)
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        if step == 0:
+            assert len(opt.state[muon[-1]]) == 0           # no gradient yet -> no state yet
+        for i, (p, r) in enumerate(zip(muon, rmuon)):
+            assert relf(p.data, r) < TOL_W, (step, i)
+            if mg[i] is not None or step > 0:
+                assert relf(p.data.float().cpu() - w0[i].float(), r.float() - w0[i].float()) < TOL_DELTA[case], (step, i)
+    assert _lib.read_status(muon[0].device) == 0
+    # momentum: same two roundings in the same type -> identical bits
+    for p, r in zip(muon, rmuon):
+        assert torch.equal(opt.state[p]["momentum_buffer"].cpu(), ref.state[id(r)]["momentum_buffer"])
+    # AdamW: same op order; fused-multiply-add vs separate multiply/add can move the last bit
+    for p, r in zip(adamw, radamw):
+        st, rst = opt.state[p], ref.state[id(r)]
+        assert st["step"] == rst["step"] == gi.OPT_STEPS
+        tol = 1e-6 if case == "fp32" else 4e-3
+        assert relf(p.data, r) < tol
+        assert relf(st["exp_avg"], rst["exp_avg"]) < tol
+        assert relf(st["exp_avg_sq"], rst["exp_avg_sq"]) < tol
+
+
+def test_fp32_weights_close_to_fp32_newton_schulz_oracle():
+    """Against the pretrain twin's fp32 Newton-Schulz the bf16 tensor-core path
+    must be no further than the reference's own bf16 path is."""
+    ref32, r32, _ = _oracle("fp32", ns_bf16=False)
+    ref16, r16, _ = _oracle("fp32", ns_bf16=True)
+    w0 = [p.clone() for p in r32]
+    opt, muon, adamw = _ours("fp32")
+    mg, ag = gi.opt_grads("fp32", 1)
+    ref32.step(mg, ag)
+    ref16.step(mg, ag)
+    _feed(muon, adamw, mg, ag)
+    opt.step()
+    for p, a, b, w in zip(muon, r32, r16, w0):
+        e_ref = relf(b - w, a - w)
+        e_got = relf(p.data.cpu() - w, a - w)
+        assert e_got <= max(1.15 * e_ref, 1e-2), (e_got, e_ref)
+
+
+@pytest.mark.parametrize("case", ["fp32", "bf16"])
+def test_fp8_absmax_state_is_bit_exact(case):
+    from oracle import fp8_oracle, muon_oracle
+    from monarch_muon_b200 import CoatStateMonarchMuon
+    opt, muon, adamw = _ours(case, cls=CoatStateMonarchMuon, codec="absmax")
+    _, _, _, hyper = gi.OPT_CASES[case]
+    # oracle chain per tensor: codes/scales start at zero (state created as zeros)
+    chain = [None] * len(muon)
+    w_ref = [p.data.clone().cpu() for p in muon]
+    for step in range(gi.OPT_STEPS):
+        mg, ag = gi.opt_grads(case, step)
+        _feed(muon, adamw, mg, ag)
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        for i, g in enumerate(mg):
+            if g is None:
+                continue
+            n = g.numel()
+            if chain[i] is None:
+                chain[i] = (torch.zeros(n, dtype=torch.uint8), torch.zeros(-(-n // 128)))
+            codes, scales, m32, m16 = fp8_oracle.absmax_momentum_step(chain[i][0], chain[i][1], g, hyper["momentum"])
+            chain[i] = (codes, scales)
+            st = opt.state[muon[i]]
+            assert st["momentum_buffer"].dtype == torch.float8_e4m3fn
+            assert st["momentum_buffer"].shape == muon[i].shape
+            assert torch.equal(st["momentum_buffer"].view(torch.uint8).cpu().reshape(-1), codes), (step, i)
+            assert np.array_equal(st["scale_momentum_buffer"].cpu().numpy().view(np.uint32),
+                                  scales.numpy().view(np.uint32)), (step, i)
+            # weights: oracle Newton-Schulz on the same bf16 momentum
+            o = muon_oracle.newton_schulz(m16.view(g.shape))
+            scale = (g.shape[1] / g.shape[2]) ** 0.5
+            w_ref[i] = (w_ref[i].float() - hyper["lr"] * scale * o.float()).to(w_ref[i].dtype)
+            assert relf(muon[i].data, w_ref[i]) < TOL_W
+    for p in adamw:                                   # AdamW moments are stored as E4M3 too
+        st = opt.state[p]
+        assert st["exp_avg"].dtype == torch.float8_e4m3fn and st["exp_avg_sq"].dtype == torch.float8_e4m3fn
+        assert st["scale_exp_avg"].dtype == torch.float32
+
+
+def test_fp8_expand_state_tracks_fp32_state():
+    from monarch_muon_b200 import CoatStateMonarchMuon
+
+    class Q:  # the optimizer fields of the reference's QuantizationConfig
+        qgroup_size = 128
+        first_order_expansion = second_order_expansion = "true"
+        first_order_bit = second_order_bit = "E4M3"
+        expand_min = 16
+
+    opt8, m8, a8 = _ours("fp32", cls=CoatStateMonarchMuon, qargs=Q())
+    opt, m, a = _ours("fp32")
+    w0 = [p.data.clone() for p in m]
+    for step in range(gi.OPT_STEPS):
+        mg, ag = gi.opt_grads("fp32", step)
+        _feed(m8, a8, mg, ag)
+        _feed(m, a, mg, ag)
+        opt8.step()
+        opt.step()
+    for p8, p, w in zip(m8, m, w0):
+        st = opt8.state[p8]
+        assert st["momentum_buffer"].dtype == torch.float8_e4m3fn
+        for key in ("scale", "expand", "sqrt_minmax"):
+            assert st[f"{key}_momentum_buffer"].dtype == torch.float32
+        # FP8 momentum is a perturbation of a few percent; the orthogonalised update stays close
+        assert relf(p8.data - w, p.data - w) < 0.25
+    for p8, p in zip(a8, a):
+        assert relf(p8.data, p.data) < 1e-3
+
+
+@pytest.mark.parametrize("fmt", ["param", "fp8_absmax", "fp8_expand"])
+def test_state_dict_round_trip(fmt):
+    from monarch_muon_b200 import MonarchMuonOptimizer
+    opt, muon, adamw = _ours("bf16", state_format=fmt)
+    for step in range(2):
+        _feed(muon, adamw, *gi.opt_grads("bf16", step + 1))
+        opt.step()
+    buf = io.BytesIO()
+    torch.save(opt.state_dict(), buf)
+    buf.seek(0)
+    opt2, muon2, adamw2 = _ours("bf16", state_format=fmt)
+    for a, b in zip(muon + adamw, muon2 + adamw2):
+        b.data.copy_(a.data)
+    opt2.load_state_dict(torch.load(buf, weights_only=False))
+    sd1, sd2 = opt.state_dict(), opt2.state_dict()
+    for key, entry in sd1["state"].items():
+        for name, v in entry.items():
+            w = sd2["state"][key][name]
+            if torch.is_tensor(v):
+                assert v.dtype == w.dtype, name
+                assert torch.equal(v.view(torch.uint8) if v.dtype == torch.float8_e4m3fn else v,
+                                   w.view(torch.uint8) if w.dtype == torch.float8_e4m3fn else w), name
+            else:
+                assert v == w
+    g = gi.opt_grads("bf16", 2)
+    _feed(muon, adamw, *g)
+    _feed(muon2, adamw2, *g)
+    opt.step()
+    opt2.step()
+    for a, b in zip(muon + adamw, muon2 + adamw2):
+        assert torch.equal(a.data, b.data)
+
+
+def test_optimizer_protocol_hooks_scheduler_and_errors():
+    from monarch_muon_b200 import MonarchMuonOptimizer
+    opt, muon, adamw = _ours("bf16")
+    assert [g["update_type"] for g in opt.param_groups] == ["muon", "adamw"]
+    assert "momentum" in opt.param_groups[0] and "betas" in opt.param_groups[1]
+    calls = []
+    opt.register_step_post_hook(lambda o, a, k: calls.append(1))
+    sched = torch.optim.lr_scheduler.LambdaLR(opt, lambda it: 0.5 ** it)
+    _feed(muon, adamw, *gi.opt_grads("bf16", 1))
+    before = [p.data.clone() for p in muon]
+    loss = opt.step(lambda: torch.tensor(3.0))
+    assert float(loss) == 3.0 and calls == [1]
+    sched.step()
+    assert opt.param_groups[0]["lr"] == pytest.approx(0.01)
+    d1 = [(p.data - b).float().norm() for p, b in zip(muon, before)]
+    before = [p.data.clone() for p in muon]
+    opt.step()                                           # same grads, half the lr, momentum grown
+    d2 = [(p.data - b).float().norm() for p, b in zip(muon, before)]
+    for a, b in zip(d1, d2):
+        assert 0.35 < float(b / a) < 0.65                # orthogonalised update scales with lr only
+    repr(opt)
+    cpu = [torch.nn.Parameter(torch.zeros(2, 8, 8))]
+    cpu[0].grad = torch.zeros(2, 8, 8)
+    with pytest.raises(RuntimeError):
+        MonarchMuonOptimizer(cpu, []).step()
+    with pytest.raises(ValueError):
+        bad = torch.nn.Parameter(torch.zeros(8, 8, device="cuda"))
+        bad.grad = torch.zeros_like(bad)
+        MonarchMuonOptimizer([bad], []).step()
+
+
+def test_many_tensors_span_several_launch_tables():
+    """More tensors than one kernel-parameter table holds (96 momentum / 128 update segments)."""
+    from monarch_muon_b200 import MonarchMuonOptimizer
+    from oracle import muon_oracle
+    gen = torch.Generator().manual_seed(11)
+    shapes = [(1, 64, 64)] * 150 + [(2, 64, 128)] * 60
+    ws = [(0.02 * torch.randn(s, generator=gen)).bfloat16() for s in shapes]
+    gs = [(1e-3 * torch.randn(s, generator=gen)).bfloat16() for s in shapes]
+    aw = [(0.02 * torch.randn(33, generator=gen)).bfloat16() for _ in range(140)]
+    ag = [(1e-3 * torch.randn(33, generator=gen)).bfloat16() for _ in range(140)]
+    ref = muon_oracle.OracleMonarchMuon([w.clone() for w in ws], [w.clone() for w in aw], lr=0.02,
+                                        ns_dtype=torch.bfloat16)
+    ref.step(gs, ag)
+    muon = [torch.nn.Parameter(w.cuda()) for w in ws]
+    adamw = [torch.nn.Parameter(w.cuda()) for w in aw]
+    opt = MonarchMuonOptimizer(muon, adamw, lr=0.02)
+    _feed(muon, adamw, gs, ag)
+    opt.step()
+    for p, r in zip(muon, ref.muon):
+        assert relf(p.data, r) < TOL_W
+        assert torch.equal(opt.state[p]["momentum_buffer"].cpu(), ref.state[id(r)]["momentum_buffer"])
+    for p, r in zip(adamw, ref.adamw):
+        assert relf(p.data, r) < 4e-3
