@@ -75,9 +75,9 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
 
-    def stop(self) -> dict:
+    def stop(self, t_begin: float = 0.0, t_end: float = float("inf")) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -87,8 +87,8 @@ class ClockSampler:
             self.proc.kill()
         sm, smax, reasons = [], None, set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for r in self.rows:
-            if len(r) < 8:
+        for ts, r in self.rows:
+            if len(r) < 8 or ts < t_begin or ts > t_end + 0.15:
                 continue
             try:
                 sm.append(float(r[0]))
@@ -189,6 +189,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--nblocks", type=int, default=4, choices=[2, 4])
+    ap.add_argument("--case", default="step", choices=["step", "ns", "fp8"],
+                    help="step: the full optimizer step (headline); ns: isolated batched Newton-Schulz on the "
+                         "128+64+64 block set; fp8: isolated FP8 momentum kernel on a flat buffer")
+    ap.add_argument("--ns-blocks", type=int, default=128, help="square blocks in --case ns (tall/wide get half each)")
+    ap.add_argument("--fp8-elems", type=int, default=1_600_000_000)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -221,6 +226,8 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     from monarch_muon_b200 import MonarchMuonOptimizer, _lib
+    if args.case != "step":
+        return run_isolated(args, dev)
 
     muon, adamw = build_workload(dev, args.nblocks)
     opt = MonarchMuonOptimizer(muon, adamw, lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95),
@@ -228,24 +235,26 @@ def main():
     flops, muon_elems, adamw_elems = workload_counts(args.nblocks)
     pk = peaks()
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(max(3, args.warmup)):
         opt.step()
     torch.cuda.synchronize()
     assert _lib.read_status(dev) == 0, "a kernel reported an expired wait"
 
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     opt.enable_phase_timing(True)
     l0 = _lib.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
+    t_begin = time.time()
     e0.record()
     for _ in range(args.steps):
         opt.step()
     e1.record()
     torch.cuda.synchronize()
+    t_end = time.time()
     launches = _lib.launch_count() - l0
-    clocks = sampler.stop()
+    clocks = sampler.stop(t_begin, t_end)
     ms = e0.elapsed_time(e1) / args.steps
     phases = {k: v / args.steps for k, v in opt.phase_times_ms().items()}
     opt.enable_phase_timing(False)
@@ -278,6 +287,82 @@ def main():
             "ns_algorithmic_tflop_per_step": flops / 1e12, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": launches, "clocks": clocks, "device_status": status,
             "baseline_note": "vs_baseline divides by the reference's published 304.4 ms on one H100 (bf16 state)"}
+    print(json.dumps(line))
+    return 0
+
+
+def _timed(fn, steps: int, warmup: int, sampler=None):
+    for _ in range(max(3, warmup)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin = time.time()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps, t_begin, time.time()
+
+
+def run_isolated(args, dev):
+    """The two isolated kernels of the metric: batched Newton-Schulz (TFLOP/s
+    against the bf16 tensor peak) and the FP8 momentum kernel (GB/s against HBM)."""
+    from monarch_muon_b200 import _lib, fp8_state, newton_schulz_batched
+    pk = peaks()
+    gen = torch.Generator(device=dev).manual_seed(99)
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    l0 = _lib.launch_count()
+    if args.case == "ns":
+        nb = args.ns_blocks
+        r = 1024 * 4 // args.nblocks
+        t = 2752 * 4 // args.nblocks
+        sets = [(nb, r, r), (max(1, nb // 2), t, r), (max(1, nb // 2), r, t)]
+        xs = [torch.empty(s, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=gen) for s in sets]
+        outs = [torch.empty_like(x) for x in xs]
+        flops = sum(s[0] * S.ns_flops(s[1], s[2]) for s in sets)
+
+        def fn():
+            for x, o in zip(xs, outs):
+                newton_schulz_batched(x, out=o, max_batch=256)
+        ms, tb, te = _timed(fn, args.steps, args.warmup)
+        ach = flops / (ms * 1e-3) / 1e12
+        line = {"metric": "newton_schulz_tflops", "value": ach, "unit": "TFLOP/s", "higher_is_better": True,
+                "ms_per_step": ms, "config": {"workload": "isolated batched Newton-Schulz, bf16, N(0,1) blocks: "
+                                              + ", ".join(f"{s[0]}x{s[1]}x{s[2]}" for s in sets),
+                                              "cache": "inputs_larger_than_l2"},
+                "roofline": {"bound": "tensor", "achieved": ach, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                             "frac": ach / pk["bf16_tflops"], "peak_kind": f"{pk['source']}, burst bf16 GEMM",
+                             "traffic": None}}
+    else:
+        n = args.fp8_elems // 128 * 128
+        codes = torch.zeros(n, dtype=torch.uint8, device=dev)
+        scales = torch.zeros(n // 128, dtype=torch.float32, device=dev)
+        m0 = torch.empty(n, dtype=torch.float32, device=dev).normal_(0, 1e-3, generator=gen)
+        st = {}
+        fp8_state.quantize_(st, "momentum_buffer", m0, codec="absmax")
+        codes.copy_(st["momentum_buffer"].view(torch.uint8))
+        scales.copy_(st["scale_momentum_buffer"])
+        del m0, st
+        g = torch.empty(n, dtype=torch.bfloat16, device=dev).normal_(0, 1e-3, generator=gen)
+        m16 = torch.empty(n, dtype=torch.bfloat16, device=dev)
+
+        def fn():
+            fp8_state.fp8_momentum_flat(codes, scales, g, 0.95, m_bf16=m16)
+        ms, tb, te = _timed(fn, args.steps, args.warmup)
+        ach = n * S.FP8_ABSMAX_BYTES_PER_ELEM / (ms * 1e-3) / 1e9
+        line = {"metric": "fp8_momentum_gbs", "value": ach, "unit": "GB/s", "higher_is_better": True,
+                "ms_per_step": ms, "config": {"workload": f"isolated FP8 absmax momentum kernel, flat buffer of {n} "
+                                              "elements, bf16 gradients N(0,1e-3), groups of 128",
+                                              "cache": "inputs_larger_than_l2"},
+                "roofline": {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                             "frac": ach / pk["hbm_gbs"], "peak_kind": f"{pk['source']}, copy bandwidth",
+                             "traffic": None}}
+    line.update({"n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "dtype": "bf16",
+                 "data": "synthetic", "scaling": "strong", "vs_baseline": None,
+                 "gpu_launches": _lib.launch_count() - l0, "clocks": sampler.stop(tb, te),
+                 "device_status": _lib.read_status(dev)})
     print(json.dumps(line))
     return 0
 
