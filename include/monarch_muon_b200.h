@@ -107,10 +107,11 @@ int mmb_fp8_dequantize(const uint8_t* codes_dev, const float* scale_dev, const f
  * Batched quintic Newton-Schulz on `batch` bf16 blocks of rows x cols.
  * Replaces _newton_schulz_batched, monarch_muon.py:36-50 (bf16 twin:
  * membench/.../monarch_muon.py:36-50 with the cast at :161-166):
- *   X = B / (||B||_F + 1e-7); 5 x { A = X X^T; X = aX + (bA + cA^2) X }
+ *   X = B / (||B||_F + 1e-7); 5 x { A = X X^T; X = (aI + bA + cA^2) X }
  * computed on the stored orientation (tall blocks are never transposed in
- * memory).  The norm prescale is applied inside the first iteration's
- * epilogues, bA + cA^2 is formed in one epilogue, aX + PX in another.
+ * memory), the polynomial in completed-square form c(A + b/2c I)^2 + (a -
+ * b^2/4c) I so that each GEMM epilogue only scales and adds a diagonal.  The
+ * norm prescale is applied inside the first iteration's epilogues.
  *   x_dev            bf16 [batch, rows, cols], input (momentum); also used as
  *                    scratch unless `out_dev` differs - see below
  *   out_dev          bf16 [batch, rows, cols]; may equal x_dev
@@ -126,12 +127,19 @@ int mmb_newton_schulz(const void* x_dev, void* out_dev, const float* block_sumsq
 
 /* One batched GEMM of the family Newton-Schulz is built from (exposed for
  * tests and profiling):
- *   D[b] = sigma_b * (alpha * opA[b] . opB[b]^T + gamma * C[b])
- * opA is M x K, opB is N x K.  a_kmajor=1: A stored [batch][M][K] (K
- * contiguous); a_kmajor=0: stored [batch][K][M].  Same for B with N.
- * C, D: bf16 [batch][M][N].  sigma_b = inv_norm[b]^sigma_pow (pow 0: 1). */
-int mmb_gemm_bf16(const void* a_dev, const void* b_dev, const void* c_dev, void* d_dev, int batch,
-                  int M, int N, int K, int a_kmajor, int b_kmajor, float alpha, float gamma,
+ *   D[b] = sigma_b * alpha * opA[b] . opB[b]^T + diag * I
+ * opA is M x K, opB is N x K, D is bf16 [batch][M][N].  Operand modes:
+ *   MMB_GEMM_K    stored [batch][rows][K] (K contiguous)
+ *   MMB_GEMM_MN   stored [batch][K][rows] (rows contiguous)
+ *   MMB_GEMM_SYM  symmetric rows x rows matrix of which only the 256 x 256
+ *                 blocks on or above the block diagonal are read
+ * sym_out != 0: D is symmetric and only those blocks of it are written.
+ * sigma_b = inv_norm[b]^sigma_pow (sigma_pow 0: 1). */
+#define MMB_GEMM_K 0
+#define MMB_GEMM_MN 1
+#define MMB_GEMM_SYM 2
+int mmb_gemm_bf16(const void* a_dev, const void* b_dev, void* d_dev, int batch, int M, int N, int K,
+                  int a_mode, int b_mode, int sym_out, float alpha, float diag,
                   const float* inv_norm_dev, int sigma_pow, int backend, int32_t* status_dev,
                   void* stream);
 

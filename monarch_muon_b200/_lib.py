@@ -18,6 +18,7 @@ BF16, F32 = 0, 1
 STATE_FP8_ABSMAX, STATE_FP8_EXPAND, STATE_BF16, STATE_F32 = 0, 1, 2, 3
 DIV_IEEE, DIV_FULL = 0, 1
 NS_TCGEN05, NS_SIMT = 0, 1
+GEMM_K, GEMM_MN, GEMM_SYM = 0, 1, 2
 
 
 class MomentumSeg(C.Structure):
@@ -47,7 +48,7 @@ SYMBOLS = {
     "mmb_fp8_dequantize": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _vp]),
     "mmb_ns_workspace_bytes": (_i64, [_i, _i, _i]),
     "mmb_newton_schulz": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i64, _i, _vp, _vp]),
-    "mmb_gemm_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _i, _i, _vp, _vp]),
+    "mmb_gemm_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _i, _i, _vp, _vp]),
     "mmb_muon_update": (_i, [C.POINTER(UpdateSeg), _i, _i, _f, _vp]),
     "mmb_adamw_step": (_i, [C.POINTER(AdamWSeg), _i, _i, _f, _f, _f, _f, _f, _vp]),
     "mmb_device_status_create": (_i, [C.POINTER(_vp)]),

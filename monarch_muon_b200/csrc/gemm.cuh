@@ -1,0 +1,27 @@
+// Interface between the Newton-Schulz driver and its GEMM back ends.
+#pragma once
+
+#include "common.cuh"
+
+namespace mmb {
+
+// Operand storage modes (same values as MMB_GEMM_* in the public header).
+enum : int { GEMM_K = 0, GEMM_MN = 1, GEMM_SYM = 2 };
+
+// D[b] = sigma_b * alpha * opA[b] . opB[b]^T + diag * I, bf16 in, bf16 out.
+struct GemmCall {
+  const void* a;
+  const void* b;
+  void* d;
+  int batch, M, N, K;
+  int a_mode, b_mode;     // GEMM_K / GEMM_MN / GEMM_SYM
+  int sym_out;            // D is symmetric: only 256-blocks on or above the block diagonal are written
+  float alpha, diag;
+  const float* inv_norm;  // per batch, may be null
+  int sigma_pow;          // sigma_b = inv_norm[b]^sigma_pow, 0..2
+};
+
+int gemm_tcgen05(const GemmCall& g, int32_t* status, cudaStream_t st);
+int gemm_simt(const GemmCall& g, cudaStream_t st);
+
+}  // namespace mmb

@@ -1,26 +1,40 @@
 // Batched bf16 GEMM for Newton-Schulz on sm_100a: TMA -> shared memory ->
-// tcgen05.mma -> TMEM -> fused epilogue.
+// tcgen05.mma -> TMEM -> shared memory -> TMA store.
 //
-//   D[b] = sigma_b * (alpha * opA[b] . opB[b]^T + gamma * C[b])
+//   D[b] = sigma_b * alpha * opA[b] . opB[b]^T + diag * I
 //
-// opA is M x K, opB is N x K; each may be stored K-major ([rows][K], K
-// contiguous) or MN-major ([K][rows], rows contiguous), so that X X^T, X^T X,
-// P X and Y P all run on the matrices as stored and nothing is ever
-// transposed in memory.
+// opA is M x K, opB is N x K.  Each operand has a storage mode:
+//   K    stored [rows][K]  (K contiguous)
+//   MN   stored [K][rows]  (rows contiguous) - used so that X^T X and P X run
+//        on the matrices as stored; nothing is ever transposed in memory
+//   SYM  a symmetric rows x rows matrix of which only the block-upper part is
+//        stored (blocks of 256 x 256 on or above the block diagonal).  A tile
+//        of the operand that lies in the stored part is fetched K-major; one
+//        that lies below is fetched from its mirror image as an MN-major tile.
+//        tcgen05.mma takes the major-ness per instruction, so both kinds mix
+//        freely inside one K loop.
+// With `sym_out` the output is such a symmetric matrix and only its block-upper
+// tiles are computed (62.5 % of the tiles of a 1024 x 1024 Gram matrix), and
+// nothing has to be mirrored because every consumer reads it through SYM.
+//
+// The epilogue needs no addend: the quintic polynomial is used in completed-
+// square form, so every GEMM of the iteration is "scale, add a constant on the
+// diagonal, round to bf16".
 //
 // CTA = 192 threads, persistent over output tiles of 128 x BN:
-//   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of a
-//               128x64 A tile and a BNx64 B tile (128-byte swizzle) per stage
-//               into a ring of STAGES buffers, arming the stage's mbarrier
-//               with the byte count.  No cluster multicast anywhere.
+//   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads per
+//               64-deep K slice into a ring of STAGES buffers (128-byte
+//               swizzle), arming the stage's mbarrier with the byte count.
+//               No cluster multicast anywhere.
 //   warp 1      MMA issuer: one lane issues four tcgen05.mma (K=16 each) per
 //               stage into one of two TMEM accumulators (128 lanes x BN fp32
-//               columns each), then tcgen05.commit to free the stage; after
-//               the last K tile, tcgen05.commit hands the accumulator over.
-//   warps 2-5   epilogue: tcgen05.ld 32 columns at a time (each warp owns the
-//               32 TMEM lanes its warp-id allows), apply alpha/gamma/sigma,
-//               round to bf16, store.  The double-buffered accumulator lets
-//               the epilogue of tile i overlap the main loop of tile i+1.
+//               columns each); tcgen05.commit frees the stage, and after the
+//               last K slice hands the accumulator to the epilogue.
+//   warps 2-5   epilogue: tcgen05.ld 64 columns at a time, scale, add the
+//               diagonal, round to bf16, write a swizzled 128 x 64 chunk to one
+//               of two staging buffers, one thread issues the TMA store.  The
+//               second accumulator lets this overlap the next tile's main loop;
+//               TMA clips rows/columns beyond M/N, so ragged edges need no masks.
 //
 // Every mbarrier wait is bounded (about two seconds of wall clock): on expiry
 // the waiting role stores a code in the device status word, raises a CTA-wide
@@ -29,6 +43,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "gemm.cuh"
 
 namespace mmb {
 namespace tc {
@@ -38,25 +53,26 @@ constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
 constexpr int A_TILE_BYTES = BM * BK * 2;
-constexpr int CHUNK_BYTES = 64 * BK * 2;  // one 64-wide MN-major chunk
+constexpr int CHUNK_BYTES = 64 * BK * 2;      // one 64-wide MN-major chunk (8 KiB)
+constexpr int EPI_CHUNK_BYTES = BM * 64 * 2;  // 128 rows x 64 columns of bf16 output (16 KiB)
+constexpr int SYM_SHIFT = 8;                  // symmetric storage granularity: 256
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 template <int BN>
 struct Cfg {
   static constexpr int B_TILE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 7);
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * EPI_CHUNK_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 struct GemmArgs {
   int M, N, K, batch;
-  int tiles_m, tiles_n;
+  int tiles_m, tiles_n, tiles_per_batch;
   long long total_tiles;
-  const __nv_bfloat16* C;
-  __nv_bfloat16* D;
-  float alpha, gamma;
+  int a_mode, b_mode, sym_out;
+  float alpha, diag;
   const float* inv_norm;
   int sigma_pow;
   int32_t* status;
@@ -115,6 +131,16 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
@@ -163,34 +189,58 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, bool k_major) 
 // Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B.
 //   bits 4-5 D format (1 = f32); 7-9 A format (1 = bf16); 10-12 B format;
 //   bit 15 / 16: A / B is MN-major; bits 17-22 N>>3; bits 24-28 M>>4.
-template <int BN, bool A_KMAJOR, bool B_KMAJOR>
-__device__ __forceinline__ constexpr uint32_t make_idesc() {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((A_KMAJOR ? 0u : 1u) << 15) | ((B_KMAJOR ? 0u : 1u) << 16) |
+template <int BN>
+__device__ __forceinline__ uint32_t make_idesc(bool a_kmajor, bool b_kmajor) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_kmajor ? 0u : 1u) << 15) | ((b_kmajor ? 0u : 1u) << 16) |
          (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
 }
 
+// Is the operand tile with first row r0 and first k k0 fetched K-major?
+__device__ __forceinline__ bool fetch_kmajor(int mode, int r0, int k0) {
+  return mode == GEMM_K || (mode == GEMM_SYM && (r0 >> SYM_SHIFT) <= (k0 >> SYM_SHIFT));
+}
+
+// Tile t of the launch -> batch, first row, first column.  With sym_out only
+// tiles with (n0 >> 8) >= (m0 >> 8) exist: tile rows come in pairs p (rows 2p,
+// 2p+1) that own the column tiles p .. tiles_n-1.
+template <int BN>
 __device__ __forceinline__ void tile_coords(long long t, const GemmArgs& a, int& b, int& m0, int& n0) {
-  const int per = a.tiles_m * a.tiles_n;
-  b = static_cast<int>(t / per);
-  const int r = static_cast<int>(t - static_cast<long long>(b) * per);
-  m0 = (r / a.tiles_n) * BM;
-  n0 = (r % a.tiles_n);
+  b = static_cast<int>(t / a.tiles_per_batch);
+  int r = static_cast<int>(t - static_cast<long long>(b) * a.tiles_per_batch);
+  if (a.sym_out && BN == 256) {
+    int p = 0;
+    for (;; ++p) {
+      const int rows = (a.tiles_m - 2 * p) >= 2 ? 2 : 1;
+      const int cnt = rows * (a.tiles_n - p);
+      if (r < cnt) break;
+      r -= cnt;
+    }
+    const int w = a.tiles_n - p;
+    const int hi = r >= w ? 1 : 0;
+    m0 = (2 * p + hi) * BM;
+    n0 = (p + r - hi * w) * BN;
+  } else {
+    m0 = (r / a.tiles_n) * BM;
+    n0 = (r % a.tiles_n) * BN;
+  }
 }
 
 // -------------------------------------------------------------------- kernel
-template <int BN, bool A_KMAJOR, bool B_KMAJOR>
+template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            const GemmArgs args) {
+gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__ CUtensorMap map_a_mn,
+            const __grid_constant__ CUtensorMap map_b_k, const __grid_constant__ CUtensorMap map_b_mn,
+            const __grid_constant__ CUtensorMap map_d, const GemmArgs args) {
   using C = Cfg<BN>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
   uint8_t* tiles_ptr = smem_raw + (tiles_addr - raw_addr);
-  // barrier block after the tiles
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles_ptr + STAGES * C::STAGE_BYTES);
-  const uint32_t bars_addr = tiles_addr + STAGES * C::STAGE_BYTES;
+  const uint32_t epi_addr = tiles_addr + STAGES * C::STAGE_BYTES;  // two 16 KiB output chunks
+  uint8_t* epi_ptr = tiles_ptr + STAGES * C::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_ptr + 2 * EPI_CHUNK_BYTES);
+  const uint32_t bars_addr = epi_addr + 2 * EPI_CHUNK_BYTES;
   const uint32_t full_bar = bars_addr;                      // STAGES
   const uint32_t empty_bar = bars_addr + 8 * STAGES;        // STAGES
   const uint32_t tmem_full_bar = bars_addr + 16 * STAGES;   // 2
@@ -231,9 +281,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (long long t = blockIdx.x; ok && t < args.total_tiles; t += gridDim.x) {
-        int b, m0, nt;
-        tile_coords(t, args, b, m0, nt);
-        const int n0 = nt * BN;
+        int b, m0, n0;
+        tile_coords<BN>(t, args, b, m0, n0);
         for (int kt = 0; kt < num_k_tiles; ++kt) {
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, args.status, STATUS_WAIT_PRODUCER_EMPTY)) {
             ok = false;
@@ -244,17 +293,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const uint32_t sa = tiles_addr + stage * C::STAGE_BYTES;
           const uint32_t sb = sa + A_TILE_BYTES;
           const int k0 = kt * BK;
-          if (A_KMAJOR) {
-            tma_load_3d(sa, &tmap_a, fb, k0, m0, b);
+          if (fetch_kmajor(args.a_mode, m0, k0)) {
+            tma_load_3d(sa, &map_a_k, fb, k0, m0, b);
           } else {
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c) tma_load_3d(sa + c * CHUNK_BYTES, &tmap_a, fb, m0 + 64 * c, k0, b);
+            for (int c = 0; c < BM / 64; ++c) tma_load_3d(sa + c * CHUNK_BYTES, &map_a_mn, fb, m0 + 64 * c, k0, b);
           }
-          if (B_KMAJOR) {
-            tma_load_3d(sb, &tmap_b, fb, k0, n0, b);
+          if (fetch_kmajor(args.b_mode, n0, k0)) {
+            tma_load_3d(sb, &map_b_k, fb, k0, n0, b);
           } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * CHUNK_BYTES, &tmap_b, fb, n0 + 64 * c, k0, b);
+            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * CHUNK_BYTES, &map_b_mn, fb, n0 + 64 * c, k0, b);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -263,13 +312,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else if (warp == 1) {
     // --------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc<BN, A_KMAJOR, B_KMAJOR>();
-      constexpr uint32_t a_step = A_KMAJOR ? (UMMA_K * 2) >> 4 : (UMMA_K * 128) >> 4;  // descriptor units of 16 B
-      constexpr uint32_t b_step = B_KMAJOR ? (UMMA_K * 2) >> 4 : (UMMA_K * 128) >> 4;
+      constexpr uint32_t K_STEP = (UMMA_K * 2) >> 4;     // K-major: 32 bytes per K=16, in 16-byte units
+      constexpr uint32_t MN_STEP = (UMMA_K * 128) >> 4;  // MN-major: 16 rows of 128 bytes
       uint32_t stage = 0, phase = 0;
       uint32_t local = 0;
       bool ok = true;
       for (long long t = blockIdx.x; ok && t < args.total_tiles; t += gridDim.x, ++local) {
+        int b, m0, n0;
+        tile_coords<BN>(t, args, b, m0, n0);
         const uint32_t acc = local & 1u;
         const uint32_t acc_phase = (local >> 1) & 1u;
         if (!mbar_wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, args.status, STATUS_WAIT_MMA_TMEM_EMPTY)) {
@@ -284,9 +334,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             break;
           }
           tcgen05_fence_after();
+          const int k0 = kt * BK;
+          const bool ak = fetch_kmajor(args.a_mode, m0, k0);
+          const bool bk = fetch_kmajor(args.b_mode, n0, k0);
           const uint32_t sa = tiles_addr + stage * C::STAGE_BYTES;
-          const uint64_t adesc = make_desc(sa, A_KMAJOR);
-          const uint64_t bdesc = make_desc(sa + A_TILE_BYTES, B_KMAJOR);
+          const uint64_t adesc = make_desc(sa, ak);
+          const uint64_t bdesc = make_desc(sa + A_TILE_BYTES, bk);
+          const uint32_t idesc = make_idesc<BN>(ak, bk);
+          const uint32_t a_step = ak ? K_STEP : MN_STEP;
+          const uint32_t b_step = bk ? K_STEP : MN_STEP;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
             tcgen05_mma_f16(d_tmem, adesc + k * a_step, bdesc + k * b_step, idesc, (kt > 0 || k > 0) ? 1u : 0u);
@@ -299,12 +355,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else {
     // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32) are this warp's
+    const int row_in_tile = quarter * 32 + lane;
+    const bool elected = threadIdx.x == 64;  // warp 2, lane 0 issues and tracks the TMA stores
     uint32_t local = 0;
+    uint32_t chunk_no = 0;  // running count of stored chunks: selects the staging buffer
     bool ok = true;
     for (long long t = blockIdx.x; ok && t < args.total_tiles; t += gridDim.x, ++local) {
-      int b, m0, nt;
-      tile_coords(t, args, b, m0, nt);
-      const int n0 = nt * BN;
+      int b, m0, n0;
+      tile_coords<BN>(t, args, b, m0, n0);
       const uint32_t acc = local & 1u;
       const uint32_t acc_phase = (local >> 1) & 1u;
       if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag, args.status, STATUS_WAIT_EPI_TMEM_FULL)) {
@@ -317,55 +375,52 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const float s = args.inv_norm[b];
         sigma = args.sigma_pow == 2 ? s * s : s;
       }
-      const float sa = sigma * args.alpha, sg = sigma * args.gamma;
-      const int row = m0 + quarter * 32 + lane;
-      const bool row_ok = row < args.M;
-      const long long row_off = (static_cast<long long>(b) * args.M + row) * args.N;
+      const float scale = sigma * args.alpha;
+      const int row = m0 + row_in_tile;
       const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tcgen05_ld_32x32b_x32(t_base + c * 32, v);
+      for (int c = 0; c < BN / 64; ++c) {
+        const int col0 = n0 + c * 64;
+        if (col0 >= args.N) break;  // uniform across the CTA
+        const uint32_t buf = chunk_no & 1u;
+        ++chunk_no;
+        if (elected) bulk_wait_read_1();  // the store issued from this buffer two chunks ago has been read
+        epilogue_bar();
+        uint32_t v[64];
+        tcgen05_ld_32x32b_x32(t_base + c * 64, v);
+        tcgen05_ld_32x32b_x32(t_base + c * 64 + 32, v + 32);
         tcgen05_wait_ld();
-        const int col0 = n0 + c * 32;
-        if (row_ok && col0 < args.N) {
-          const int nvec = (args.N - col0) >= 32 ? 4 : (args.N - col0) / 8;  // 16-byte vectors of 8 bf16
-          const __nv_bfloat16* cp = args.C != nullptr ? args.C + row_off + col0 : nullptr;
-          __nv_bfloat16* dp = args.D + row_off + col0;
+        // diagonal element of this row, if it falls inside the chunk
+        const int dcol = row - col0;
+        uint8_t* rowp = epi_ptr + buf * EPI_CHUNK_BYTES + row_in_tile * 128;
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            if (q < nvec) {
-              float addend[8];
-              if (cp != nullptr) {
-                uint4 cv = *reinterpret_cast<const uint4*>(cp + 8 * q);
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&cv);
+        for (int q = 0; q < 8; ++q) {
+          uint4 ov;
+          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ov);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  float2 f = __bfloat1622float2(h[i]);
-                  addend[2 * i] = f.x;
-                  addend[2 * i + 1] = f.y;
-                }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) addend[i] = 0.0f;
-              }
-              uint4 ov;
-              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ov);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                float x0 = fmaf(sa, __uint_as_float(v[8 * q + 2 * i]), sg * addend[2 * i]);
-                float x1 = fmaf(sa, __uint_as_float(v[8 * q + 2 * i + 1]), sg * addend[2 * i + 1]);
-                oh[i] = __floats2bfloat162_rn(x0, x1);
-              }
-              *reinterpret_cast<uint4*>(dp + 8 * q) = ov;
-            }
+          for (int i = 0; i < 4; ++i) {
+            const int e = 8 * q + 2 * i;
+            float x0 = scale * __uint_as_float(v[e]);
+            float x1 = scale * __uint_as_float(v[e + 1]);
+            if (e == dcol) x0 += args.diag;
+            if (e + 1 == dcol) x1 += args.diag;
+            oh[i] = __floats2bfloat162_rn(x0, x1);
           }
+          // 128-byte swizzle: 16-byte unit q of row r lives at unit q ^ (r & 7)
+          *reinterpret_cast<uint4*>(rowp + ((q ^ (row_in_tile & 7)) << 4)) = ov;
+        }
+        fence_proxy_async_smem();
+        epilogue_bar();
+        if (elected) {
+          tma_store_3d(&map_d, epi_addr + buf * EPI_CHUNK_BYTES, col0, m0, b);
+          bulk_commit();
         }
       }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar + 8 * acc);
     }
+    if (elected) bulk_wait_all();
   }
 
   // ------------------------------------------------------------- teardown
@@ -405,7 +460,8 @@ EncodeTiledFn encode_fn() {
 }
 
 // Tensor map over a bf16 array [batch][outer][inner] (inner contiguous) with a
-// box of {64, box_outer, 1} and 128-byte swizzle; out-of-range elements read 0.
+// box of {64, box_outer, 1} and 128-byte swizzle; out-of-range elements read 0
+// and are not written.
 int make_map(CUtensorMap* map, const void* base, int batch, int outer, int inner, int box_outer) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(MMB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
@@ -422,59 +478,73 @@ int make_map(CUtensorMap* map, const void* base, int batch, int outer, int inner
   return MMB_OK;
 }
 
-template <int BN, bool AK, bool BK_>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, int grid, cudaStream_t st) {
-  auto kern = gemm_kernel<BN, AK, BK_>;
+// Maps of one operand: K-major view (box rows x 64 k) and MN-major view (64 k x 64 rows).
+int operand_maps(CUtensorMap* k_map, CUtensorMap* mn_map, const void* base, int batch, int rows, int K, int mode,
+                 int box_rows) {
+  int rc;
+  if (mode == GEMM_K) {
+    if ((rc = make_map(k_map, base, batch, rows, K, box_rows)) != MMB_OK) return rc;
+    *mn_map = *k_map;  // never used
+  } else if (mode == GEMM_MN) {
+    if ((rc = make_map(mn_map, base, batch, K, rows, BK)) != MMB_OK) return rc;
+    *k_map = *mn_map;  // never used
+  } else {
+    if ((rc = make_map(k_map, base, batch, rows, K, box_rows)) != MMB_OK) return rc;
+    if ((rc = make_map(mn_map, base, batch, K, rows, BK)) != MMB_OK) return rc;
+  }
+  return MMB_OK;
+}
+
+template <int BN>
+int launch(const CUtensorMap* maps, const GemmArgs& args, int grid, cudaStream_t st) {
+  auto kern = gemm_kernel<BN>;
   MMB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES));
-  kern<<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, st>>>(ta, tb, args);
+  kern<<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], args);
   MMB_CUDA_CHECK(cudaGetLastError());
   count_launch();
   return MMB_OK;
 }
 
-template <int BN>
-int launch_major(bool ak, bool bk, const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, int grid,
-                 cudaStream_t st) {
-  if (ak && bk) return launch<BN, true, true>(ta, tb, args, grid, st);
-  if (ak && !bk) return launch<BN, true, false>(ta, tb, args, grid, st);
-  if (!ak && bk) return launch<BN, false, true>(ta, tb, args, grid, st);
-  return launch<BN, false, false>(ta, tb, args, grid, st);
-}
-
 }  // namespace tc
 
-int gemm_tcgen05(const void* a, const void* b, const void* c, void* d, int batch, int M, int N, int K, int a_kmajor,
-                 int b_kmajor, float alpha, float gamma, const float* inv_norm, int sigma_pow, int32_t* status,
-                 cudaStream_t st) {
+int gemm_tcgen05(const GemmCall& g, int32_t* status, cudaStream_t st) {
   using namespace tc;
-  MMB_REQUIRE(M % 8 == 0 && N % 8 == 0 && K % 8 == 0, "tcgen05 GEMM needs M, N, K multiples of 8 (got %d %d %d)", M, N, K);
-  MMB_REQUIRE(aligned16(a) && aligned16(b) && aligned16(d) && (c == nullptr || aligned16(c)),
-              "tcgen05 GEMM needs 16-byte aligned operands");
-  const int bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
-  CUtensorMap ta, tb;
+  MMB_REQUIRE(g.M % 8 == 0 && g.N % 8 == 0 && g.K % 8 == 0, "tcgen05 GEMM needs M, N, K multiples of 8 (got %d %d %d)",
+              g.M, g.N, g.K);
+  MMB_REQUIRE(aligned16(g.a) && aligned16(g.b) && aligned16(g.d), "tcgen05 GEMM needs 16-byte aligned operands");
+  if (g.a_mode == GEMM_SYM) MMB_REQUIRE(g.M == g.K, "symmetric A operand must be square (M == K)");
+  if (g.b_mode == GEMM_SYM) MMB_REQUIRE(g.N == g.K, "symmetric B operand must be square (N == K)");
+  if (g.sym_out) MMB_REQUIRE(g.M == g.N, "symmetric output must be square");
+  const int bn = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
+  CUtensorMap maps[5];
   int rc;
-  // K-major: [batch][rows][K], box {64 k, rows}; MN-major: [batch][K][rows], box {64 rows, 64 k}
-  rc = a_kmajor ? make_map(&ta, a, batch, M, K, BM) : make_map(&ta, a, batch, K, M, BK);
-  if (rc != MMB_OK) return rc;
-  rc = b_kmajor ? make_map(&tb, b, batch, N, K, bn) : make_map(&tb, b, batch, K, N, BK);
-  if (rc != MMB_OK) return rc;
+  if ((rc = operand_maps(&maps[0], &maps[1], g.a, g.batch, g.M, g.K, g.a_mode, BM)) != MMB_OK) return rc;
+  if ((rc = operand_maps(&maps[2], &maps[3], g.b, g.batch, g.N, g.K, g.b_mode, bn)) != MMB_OK) return rc;
+  if ((rc = make_map(&maps[4], g.d, g.batch, g.M, g.N, BM)) != MMB_OK) return rc;
   GemmArgs args;
-  args.M = M; args.N = N; args.K = K; args.batch = batch;
-  args.tiles_m = (M + BM - 1) / BM;
-  args.tiles_n = (N + bn - 1) / bn;
-  args.total_tiles = static_cast<long long>(batch) * args.tiles_m * args.tiles_n;
-  args.C = static_cast<const __nv_bfloat16*>(c);
-  args.D = static_cast<__nv_bfloat16*>(d);
-  args.alpha = alpha; args.gamma = gamma;
-  args.inv_norm = inv_norm; args.sigma_pow = inv_norm != nullptr ? sigma_pow : 0;
+  args.M = g.M; args.N = g.N; args.K = g.K; args.batch = g.batch;
+  args.tiles_m = (g.M + BM - 1) / BM;
+  args.tiles_n = (g.N + bn - 1) / bn;
+  args.sym_out = (g.sym_out && bn == 256) ? 1 : 0;
+  if (args.sym_out) {
+    int cnt = 0;
+    for (int p = 0; 2 * p < args.tiles_m; ++p) cnt += ((args.tiles_m - 2 * p) >= 2 ? 2 : 1) * (args.tiles_n - p);
+    args.tiles_per_batch = cnt;
+  } else {
+    args.tiles_per_batch = args.tiles_m * args.tiles_n;
+  }
+  args.total_tiles = static_cast<long long>(g.batch) * args.tiles_per_batch;
+  args.a_mode = g.a_mode; args.b_mode = g.b_mode;
+  args.alpha = g.alpha; args.diag = g.diag;
+  args.inv_norm = g.inv_norm; args.sigma_pow = g.inv_norm != nullptr ? g.sigma_pow : 0;
   args.status = status;
   const int sms = sm_count();
   if (sms <= 0) return fail(MMB_ERR_CUDA, "tcgen05 GEMM: no CUDA device");
   const int grid = static_cast<int>(args.total_tiles < sms ? args.total_tiles : sms);
   if (grid == 0) return MMB_OK;
-  if (bn == 256) return launch_major<256>(a_kmajor != 0, b_kmajor != 0, ta, tb, args, grid, st);
-  if (bn == 128) return launch_major<128>(a_kmajor != 0, b_kmajor != 0, ta, tb, args, grid, st);
-  return launch_major<64>(a_kmajor != 0, b_kmajor != 0, ta, tb, args, grid, st);
+  if (bn == 256) return launch<256>(maps, args, grid, st);
+  if (bn == 128) return launch<128>(maps, args, grid, st);
+  return launch<64>(maps, args, grid, st);
 }
 
 }  // namespace mmb

@@ -47,6 +47,7 @@ struct SegDev {
 struct SegTable {
   SegDev seg[MAX_SEG];
   long long unit_start[MAX_SEG + 1];
+  long long block_start[MAX_SEG + 1];  // launch-wide numbering of blocks
   int nseg;
 };
 
@@ -377,24 +378,29 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
   }
 }
 
-// Sum each block's partials in a fixed order (lane-strided, then a tree).
+// Sum each block's partials in a fixed order (lane-strided, then a tree): one
+// warp per block over all blocks of the launch.
 __global__ void __launch_bounds__(THREADS)
 block_sumsq_kernel(const __grid_constant__ SegTable tab, const float* __restrict__ partials,
                    float* __restrict__ block_sumsq) {
   const int lane = threadIdx.x & 31;
   const long long warp_global = static_cast<long long>(blockIdx.x) * (THREADS / 32) + (threadIdx.x >> 5);
   const long long nwarps = static_cast<long long>(gridDim.x) * (THREADS / 32);
-  for (int s = 0; s < tab.nseg; ++s) {
-    const SegDev& sg = tab.seg[s];
-    const long long nblk = sg.numel / sg.block_elems;
-    for (long long b = warp_global; b < nblk; b += nwarps) {
-      const float* p = partials + sg.partial_base + b * sg.cpb;
-      float acc = 0.0f;
-      for (int i = lane; i < sg.cpb; i += 32) acc += p[i];
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (lane == 0) block_sumsq[sg.first_block + b] = acc;
+  const long long total = tab.block_start[tab.nseg];
+  for (long long gb = warp_global; gb < total; gb += nwarps) {
+    int lo = 0, hi = tab.nseg;
+    while (hi - lo > 1) {
+      int mid = (lo + hi) >> 1;
+      if (tab.block_start[mid] <= gb) lo = mid; else hi = mid;
     }
+    const SegDev& sg = tab.seg[lo];
+    const long long b = gb - tab.block_start[lo];
+    const float* p = partials + sg.partial_base + b * sg.cpb;
+    float acc = 0.0f;
+    for (int i = lane; i < sg.cpb; i += 32) acc += p[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) block_sumsq[sg.first_block + b] = acc;
   }
 }
 
@@ -535,7 +541,7 @@ int momentum_step_impl(const mmb_momentum_seg* segs, int nseg, int grad_dtype, i
   for (int base = 0; base < nseg; base += MAX_SEG) {
     SegTable tab;
     tab.nseg = (nseg - base) < MAX_SEG ? (nseg - base) : MAX_SEG;
-    long long units = 0;
+    long long units = 0, blocks = 0;
     for (int i = 0; i < tab.nseg; ++i) {
       const mmb_momentum_seg& s = segs[base + i];
       MMB_REQUIRE(s.numel > 0 && s.grad != nullptr && s.state != nullptr, "mmb_momentum_step: segment %d empty",
@@ -564,10 +570,13 @@ int momentum_step_impl(const mmb_momentum_seg* segs, int nseg, int grad_dtype, i
       d.cpb = static_cast<int>(p.cpb);
       d.vec_ok = aligned16(s.grad) && aligned16(s.state) && (s.m_bf16 == nullptr || aligned16(s.m_bf16));
       tab.unit_start[i] = units;
+      tab.block_start[i] = blocks;
+      blocks += p.nblocks;
       units += p.nblocks * p.cpb;
       partial_base += p.nblocks * p.cpb;
     }
     tab.unit_start[tab.nseg] = units;
+    tab.block_start[tab.nseg] = blocks;
     const long long warps_per_cta = THREADS / 32;
     long long want = (units + warps_per_cta - 1) / warps_per_cta;
     long long cap = static_cast<long long>(sms) * 8 * 4;  // a few waves of 8 resident CTAs per SM
@@ -582,9 +591,7 @@ int momentum_step_impl(const mmb_momentum_seg* segs, int nseg, int grad_dtype, i
     MMB_CUDA_CHECK(cudaGetLastError());
   count_launch();
     if (block_sumsq_dev != nullptr) {
-      long long nblk = 0;
-      for (int i = 0; i < tab.nseg; ++i) nblk += tab.seg[i].numel / tab.seg[i].block_elems;
-      long long g2 = (nblk + warps_per_cta - 1) / warps_per_cta;
+      long long g2 = (blocks + warps_per_cta - 1) / warps_per_cta;
       if (g2 > sms * 4) g2 = sms * 4;
       if (g2 < 1) g2 = 1;
       block_sumsq_kernel<<<static_cast<int>(g2), THREADS, 0, st>>>(tab, partials, block_sumsq_dev);

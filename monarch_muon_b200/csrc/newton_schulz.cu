@@ -2,59 +2,66 @@
 // plus the small kernels around it and a plain CUDA-core GEMM used only to
 // cross-check the tensor-core path.
 //
-// For a block stored as rows x cols, let m = min(rows, cols), n = max.
-// Per iteration (a, b, c = 3.4445, -4.7750, 2.0315):
-//   Gram   A = X X^T                (m x m, contraction n)
-//   Poly   P = b A + c A A          (m x m, contraction m; epilogue adds b A)
-//   Apply  X = a X + P X            (m x n, contraction m; epilogue adds a X)
+// For a block stored as rows x cols, let m = min(rows, cols), n = max.  With
+// (a, b, c) = (3.4445, -4.7750, 2.0315) the reference iterates
+//   A = X X^T ;  X <- a X + b A X + c A A X = (a I + b A + c A^2) X.
+// Completing the square, a I + b A + c A^2 = c (A + beta I)^2 + kappa I with
+// beta = b / (2c) and kappa = a - b^2 / (4c), so one iteration is three GEMMs
+// whose epilogues only scale, add a constant on the diagonal and round:
+//   Gram   Ah = X X^T + beta I            (m x m, contraction n, symmetric)
+//   Poly   Pp = c Ah Ah + kappa I         (m x m, contraction m, symmetric)
+//   Apply  X  = Pp X                      (m x n, contraction m)
+// The sum c(.)^2 + kappa has only positive terms, so it is better conditioned
+// than a + b s + c s^2 evaluated term by term.  Symmetric results are stored
+// and read block-upper only (see gemm_tcgen05.cu).
 // Tall blocks (rows > cols) keep their stored orientation Y = X^T:
-//   A = Y^T Y (both operands MN-major), Y = a Y + Y P.
+//   Ah = Y^T Y + beta I (both operands MN-major), Y = Y Pp.
 // The Frobenius prescale s = 1/(||B||_F + 1e-7) is never applied to the data:
 // the first Gram epilogue multiplies by s^2, the first Apply epilogue by s.
 #include "common.cuh"
+#include "gemm.cuh"
 
 namespace mmb {
 
-int gemm_tcgen05(const void* a, const void* b, const void* c, void* d, int batch, int M, int N, int K, int a_kmajor,
-                 int b_kmajor, float alpha, float gamma, const float* inv_norm, int sigma_pow, int32_t* status,
-                 cudaStream_t st);
-
 namespace {
 
-constexpr float NS_A = 3.4445f, NS_B = -4.7750f, NS_C = 2.0315f;
+constexpr double NS_A = 3.4445, NS_B = -4.7750, NS_C = 2.0315;
 constexpr int NS_ITERS = 5;
 
 // ------------------------------------------------------------ SIMT GEMM
 // 64x64 output tile, 16-deep K slices, 256 threads x (4x4) results, fp32
-// accumulation of bf16 inputs.  Operands are addressed through element strides
-// so both storage orders go through the same code.
+// accumulation of bf16 inputs; same operand modes and output convention as
+// the tensor-core kernel.
 constexpr int ST = 64, SK = 16;
+
+__device__ __forceinline__ float fetch(const __nv_bfloat16* base, int mode, int rows, int K, int r, int k) {
+  if (r >= rows || k >= K) return 0.0f;
+  bool kmajor = mode == GEMM_K || (mode == GEMM_SYM && (r >> 8) <= (k >> 8));
+  if (mode == GEMM_SYM && !kmajor) return __bfloat162float(base[static_cast<long long>(k) * rows + r]);  // mirror
+  if (mode == GEMM_MN) return __bfloat162float(base[static_cast<long long>(k) * rows + r]);
+  return __bfloat162float(base[static_cast<long long>(r) * K + k]);
+}
 
 __global__ void __launch_bounds__(256)
 simt_gemm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ B,
-                 const __nv_bfloat16* __restrict__ C, __nv_bfloat16* __restrict__ D, int M, int N, int K,
-                 long long a_row, long long a_k, long long a_batch, long long b_row, long long b_k, long long b_batch,
-                 float alpha, float gamma, const float* __restrict__ inv_norm, int sigma_pow) {
+                 __nv_bfloat16* __restrict__ D, int M, int N, int K, int a_mode, int b_mode, int sym_out, float alpha,
+                 float diag, const float* __restrict__ inv_norm, int sigma_pow) {
   __shared__ float As[SK][ST + 1];
   __shared__ float Bs[SK][ST + 1];
   const int b = blockIdx.z;
   const int m0 = blockIdx.y * ST, n0 = blockIdx.x * ST;
+  if (sym_out && (m0 >> 8) > (n0 >> 8)) return;  // below the block diagonal: not stored
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-  const __nv_bfloat16* Ab = A + b * a_batch;
-  const __nv_bfloat16* Bb = B + b * b_batch;
+  const __nv_bfloat16* Ab = A + static_cast<long long>(b) * M * K;
+  const __nv_bfloat16* Bb = B + static_cast<long long>(b) * N * K;
   float acc[4][4] = {};
   for (int k0 = 0; k0 < K; k0 += SK) {
     for (int i = threadIdx.x; i < ST * SK; i += 256) {
-      // choose the index order that walks the contiguous dimension fastest
       int r, k;
-      if (a_k == 1) { k = i % SK; r = i / SK; } else { r = i % ST; k = i / ST; }
-      float v = 0.0f;
-      if (m0 + r < M && k0 + k < K) v = __bfloat162float(Ab[(m0 + r) * a_row + (k0 + k) * a_k]);
-      As[k][r] = v;
-      if (b_k == 1) { k = i % SK; r = i / SK; } else { r = i % ST; k = i / ST; }
-      v = 0.0f;
-      if (n0 + r < N && k0 + k < K) v = __bfloat162float(Bb[(n0 + r) * b_row + (k0 + k) * b_k]);
-      Bs[k][r] = v;
+      if (a_mode == GEMM_K) { k = i % SK; r = i / SK; } else { r = i % ST; k = i / ST; }
+      As[k][r] = fetch(Ab, a_mode, M, K, m0 + r, k0 + k);
+      if (b_mode == GEMM_K) { k = i % SK; r = i / SK; } else { r = i % ST; k = i / ST; }
+      Bs[k][r] = fetch(Bb, b_mode, N, K, n0 + r, k0 + k);
     }
     __syncthreads();
 #pragma unroll
@@ -74,7 +81,7 @@ simt_gemm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __res
     float s = inv_norm[b];
     sigma = sigma_pow == 2 ? s * s : s;
   }
-  const float sa = sigma * alpha, sg = sigma * gamma;
+  const float scale = sigma * alpha;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int r = m0 + ty * 4 + i;
@@ -83,40 +90,35 @@ simt_gemm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __res
     for (int j = 0; j < 4; ++j) {
       const int c = n0 + tx * 4 + j;
       if (c >= N) continue;
-      const long long at = (static_cast<long long>(b) * M + r) * N + c;
-      const float addend = C != nullptr ? __bfloat162float(C[at]) : 0.0f;
-      D[at] = __float2bfloat16_rn(fmaf(sa, acc[i][j], sg * addend));
+      float x = scale * acc[i][j];
+      if (r == c) x += diag;
+      D[(static_cast<long long>(b) * M + r) * N + c] = __float2bfloat16_rn(x);
     }
   }
 }
 
-int gemm_simt(const void* a, const void* b, const void* c, void* d, int batch, int M, int N, int K, int a_kmajor,
-              int b_kmajor, float alpha, float gamma, const float* inv_norm, int sigma_pow, cudaStream_t st) {
-  const long long a_row = a_kmajor ? K : 1, a_k = a_kmajor ? 1 : M;
-  const long long b_row = b_kmajor ? K : 1, b_k = b_kmajor ? 1 : N;
-  for (int b0 = 0; b0 < batch; b0 += 65535) {
-    const int nb = (batch - b0) < 65535 ? (batch - b0) : 65535;
-    dim3 grid((N + ST - 1) / ST, (M + ST - 1) / ST, nb);
-    const __nv_bfloat16* ap = static_cast<const __nv_bfloat16*>(a) + static_cast<long long>(b0) * M * K;
-    const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(b) + static_cast<long long>(b0) * N * K;
-    const __nv_bfloat16* cp = c ? static_cast<const __nv_bfloat16*>(c) + static_cast<long long>(b0) * M * N : nullptr;
-    __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(d) + static_cast<long long>(b0) * M * N;
-    simt_gemm_kernel<<<grid, 256, 0, st>>>(ap, bp, cp, dp, M, N, K, a_row, a_k, static_cast<long long>(M) * K, b_row,
-                                          b_k, static_cast<long long>(N) * K, alpha, gamma,
-                                          inv_norm ? inv_norm + b0 : nullptr, sigma_pow);
+}  // namespace
+
+int gemm_simt(const GemmCall& g, cudaStream_t st) {
+  for (int b0 = 0; b0 < g.batch; b0 += 65535) {
+    const int nb = (g.batch - b0) < 65535 ? (g.batch - b0) : 65535;
+    dim3 grid((g.N + ST - 1) / ST, (g.M + ST - 1) / ST, nb);
+    const __nv_bfloat16* ap = static_cast<const __nv_bfloat16*>(g.a) + static_cast<long long>(b0) * g.M * g.K;
+    const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(g.b) + static_cast<long long>(b0) * g.N * g.K;
+    __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(g.d) + static_cast<long long>(b0) * g.M * g.N;
+    simt_gemm_kernel<<<grid, 256, 0, st>>>(ap, bp, dp, g.M, g.N, g.K, g.a_mode, g.b_mode, g.sym_out, g.alpha, g.diag,
+                                          g.inv_norm ? g.inv_norm + b0 : nullptr, g.sigma_pow);
     MMB_CUDA_CHECK(cudaGetLastError());
-  count_launch();
+    count_launch();
   }
   return MMB_OK;
 }
 
-int gemm_dispatch(int backend, const void* a, const void* b, const void* c, void* d, int batch, int M, int N, int K,
-                  int a_kmajor, int b_kmajor, float alpha, float gamma, const float* inv_norm, int sigma_pow,
-                  int32_t* status, cudaStream_t st) {
-  if (backend == MMB_NS_TCGEN05)
-    return gemm_tcgen05(a, b, c, d, batch, M, N, K, a_kmajor, b_kmajor, alpha, gamma, inv_norm, sigma_pow, status, st);
-  if (backend == MMB_NS_SIMT)
-    return gemm_simt(a, b, c, d, batch, M, N, K, a_kmajor, b_kmajor, alpha, gamma, inv_norm, sigma_pow, st);
+namespace {
+
+int gemm_dispatch(int backend, const GemmCall& g, int32_t* status, cudaStream_t st) {
+  if (backend == MMB_NS_TCGEN05) return gemm_tcgen05(g, status, st);
+  if (backend == MMB_NS_SIMT) return gemm_simt(g, st);
   return fail(MMB_ERR_INVALID, "unknown Newton-Schulz backend %d", backend);
 }
 
@@ -195,15 +197,16 @@ int64_t mmb_ns_workspace_bytes(int batch, int rows, int cols) {
   return static_cast<int64_t>(mmb::ns_layout(batch, rows, cols).total);
 }
 
-int mmb_gemm_bf16(const void* a_dev, const void* b_dev, const void* c_dev, void* d_dev, int batch, int M, int N, int K,
-                  int a_kmajor, int b_kmajor, float alpha, float gamma, const float* inv_norm_dev, int sigma_pow,
+int mmb_gemm_bf16(const void* a_dev, const void* b_dev, void* d_dev, int batch, int M, int N, int K, int a_mode,
+                  int b_mode, int sym_out, float alpha, float diag, const float* inv_norm_dev, int sigma_pow,
                   int backend, int32_t* status_dev, void* stream) {
   using namespace mmb;
   MMB_REQUIRE(a_dev && b_dev && d_dev, "mmb_gemm_bf16: null operand");
   MMB_REQUIRE(batch > 0 && M > 0 && N > 0 && K > 0, "mmb_gemm_bf16: bad shape %d x (%d,%d,%d)", batch, M, N, K);
   MMB_REQUIRE(sigma_pow >= 0 && sigma_pow <= 2, "mmb_gemm_bf16: sigma_pow %d", sigma_pow);
-  return gemm_dispatch(backend, a_dev, b_dev, c_dev, d_dev, batch, M, N, K, a_kmajor, b_kmajor, alpha, gamma,
-                       inv_norm_dev, sigma_pow, status_dev, static_cast<cudaStream_t>(stream));
+  MMB_REQUIRE(a_mode >= 0 && a_mode <= 2 && b_mode >= 0 && b_mode <= 2, "mmb_gemm_bf16: operand mode");
+  GemmCall g{a_dev, b_dev, d_dev, batch, M, N, K, a_mode, b_mode, sym_out, alpha, diag, inv_norm_dev, sigma_pow};
+  return gemm_dispatch(backend, g, status_dev, static_cast<cudaStream_t>(stream));
 }
 
 int mmb_newton_schulz(const void* x_dev, void* out_dev, const float* block_sumsq_dev, int batch, int rows, int cols,
@@ -231,13 +234,16 @@ int mmb_newton_schulz(const void* x_dev, void* out_dev, const float* block_sumsq
     block_sumsq_bf16_kernel<<<batch, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x_dev),
                                                    static_cast<long long>(rows) * cols, sumsq);
     MMB_CUDA_CHECK(cudaGetLastError());
-  count_launch();
+    count_launch();
     ss = sumsq;
   }
   inv_norm_kernel<<<(batch + 255) / 256, 256, 0, st>>>(ss, inv, batch);
   MMB_CUDA_CHECK(cudaGetLastError());
   count_launch();
 
+  const float beta = static_cast<float>(NS_B / (2.0 * NS_C));
+  const float kappa = static_cast<float>(NS_A - NS_B * NS_B / (4.0 * NS_C));
+  const float c = static_cast<float>(NS_C);
   const bool tall = rows > cols;
   const int m = tall ? cols : rows;
   const int n = tall ? rows : cols;
@@ -246,19 +252,21 @@ int mmb_newton_schulz(const void* x_dev, void* out_dev, const float* block_sumsq
     __nv_bfloat16* nxt = (it == NS_ITERS - 1) ? static_cast<__nv_bfloat16*>(out_dev) : ((it & 1) ? xb : xa);
     const int first = it == 0;
     int rc;
-    // Gram: wide X X^T (both K-major, K = n); tall Y^T Y (both MN-major, K = n = rows)
-    rc = gemm_dispatch(backend, cur, cur, nullptr, gram, batch, m, m, n, tall ? 0 : 1, tall ? 0 : 1, 1.0f, 0.0f, inv,
-                       first ? 2 : 0, status_dev, st);
-    if (rc != MMB_OK) return rc;
-    // Poly: P = b A + c A A (A symmetric, so A serves as the K-major second operand)
-    rc = gemm_dispatch(backend, gram, gram, gram, poly, batch, m, m, m, 1, 1, NS_C, NS_B, nullptr, 0, status_dev, st);
-    if (rc != MMB_OK) return rc;
-    // Apply: wide X' = a X + P X  (opA = P K-major, opB = X stored [K][N] -> MN-major)
-    //        tall Y' = a Y + Y P  (opA = Y K-major, opB = P K-major by symmetry)
-    if (!tall)
-      rc = gemm_dispatch(backend, poly, cur, cur, nxt, batch, m, n, m, 1, 0, 1.0f, NS_A, inv, first ? 1 : 0, status_dev, st);
-    else
-      rc = gemm_dispatch(backend, cur, poly, cur, nxt, batch, n, m, m, 1, 1, 1.0f, NS_A, inv, first ? 1 : 0, status_dev, st);
+    // Gram: wide X X^T (K-major operands, contraction n); tall Y^T Y (MN-major operands, contraction rows)
+    const int xmode = tall ? GEMM_MN : GEMM_K;
+    GemmCall gram_call{cur, cur, gram, batch, m, m, n, xmode, xmode, 1, 1.0f, beta, inv, first ? 2 : 0};
+    if ((rc = gemm_dispatch(backend, gram_call, status_dev, st)) != MMB_OK) return rc;
+    // Poly: Pp = c Ah Ah + kappa I
+    GemmCall poly_call{gram, gram, poly, batch, m, m, m, GEMM_SYM, GEMM_SYM, 1, c, kappa, nullptr, 0};
+    if ((rc = gemm_dispatch(backend, poly_call, status_dev, st)) != MMB_OK) return rc;
+    // Apply: wide X' = Pp X (B = X stored [K][N]); tall Y' = Y Pp (A = Y, B = Pp by symmetry)
+    if (!tall) {
+      GemmCall ap{poly, cur, nxt, batch, m, n, m, GEMM_SYM, GEMM_MN, 0, 1.0f, 0.0f, inv, first ? 1 : 0};
+      rc = gemm_dispatch(backend, ap, status_dev, st);
+    } else {
+      GemmCall ap{cur, poly, nxt, batch, n, m, m, GEMM_K, GEMM_SYM, 0, 1.0f, 0.0f, inv, first ? 1 : 0};
+      rc = gemm_dispatch(backend, ap, status_dev, st);
+    }
     if (rc != MMB_OK) return rc;
     cur = nxt;
   }

@@ -72,27 +72,30 @@ def newton_schulz_batched(stack: torch.Tensor, *, out: torch.Tensor | None = Non
     return out
 
 
-def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, c: torch.Tensor | None = None, a_kmajor: bool = True,
-              b_kmajor: bool = True, alpha: float = 1.0, gamma: float = 0.0,
-              inv_norm: torch.Tensor | None = None, sigma_pow: int = 0,
-              backend: int = _lib.NS_TCGEN05) -> torch.Tensor:
-    """D[b] = sigma_b * (alpha * opA[b] @ opB[b]^T + gamma * C[b]) on bf16 stacks.
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mode: int = _lib.GEMM_K, b_mode: int = _lib.GEMM_K,
+              sym_out: bool = False, alpha: float = 1.0, diag: float = 0.0, inv_norm: torch.Tensor | None = None,
+              sigma_pow: int = 0, backend: int = _lib.NS_TCGEN05, out: torch.Tensor | None = None) -> torch.Tensor:
+    """D[b] = sigma_b * alpha * opA[b] @ opB[b]^T + diag * I on bf16 stacks.
 
-    a is (batch, M, K) when a_kmajor else (batch, K, M); b likewise with N.
+    a is (batch, M, K) in GEMM_K mode, (batch, K, M) in GEMM_MN mode, and a
+    symmetric (batch, M, M) matrix in GEMM_SYM mode, of which only the 256x256
+    blocks on or above the block diagonal are read; b likewise with N.
+    With sym_out only those blocks of D are written (the rest of `out` is left
+    untouched).
     """
     _lib.require_cuda(a, b)
     batch = a.shape[0]
-    M, K = (a.shape[1], a.shape[2]) if a_kmajor else (a.shape[2], a.shape[1])
-    N, Kb = (b.shape[1], b.shape[2]) if b_kmajor else (b.shape[2], b.shape[1])
+    M, K = (a.shape[2], a.shape[1]) if a_mode == _lib.GEMM_MN else (a.shape[1], a.shape[2])
+    N, Kb = (b.shape[2], b.shape[1]) if b_mode == _lib.GEMM_MN else (b.shape[1], b.shape[2])
     if K != Kb or b.shape[0] != batch:
         raise ValueError("operand shapes do not agree")
-    for t in (a, b, c):
-        if t is not None and (t.dtype != torch.bfloat16 or not t.is_contiguous()):
+    for t in (a, b):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous():
             raise TypeError("gemm_bf16 expects contiguous bfloat16 tensors")
-    d = torch.empty(batch, M, N, dtype=torch.bfloat16, device=a.device)
+    d = out if out is not None else torch.empty(batch, M, N, dtype=torch.bfloat16, device=a.device)
     lib = _lib.load()
     with torch.cuda.device(a.device):
-        _lib.check(lib.mmb_gemm_bf16(a.data_ptr(), b.data_ptr(), _lib.ptr(c), d.data_ptr(), batch, M, N, K,
-                                     int(a_kmajor), int(b_kmajor), alpha, gamma, _lib.ptr(inv_norm), sigma_pow,
-                                     backend, _lib.status_word(a.device), _lib.stream_ptr()), "gemm_bf16")
+        _lib.check(lib.mmb_gemm_bf16(a.data_ptr(), b.data_ptr(), d.data_ptr(), batch, M, N, K, a_mode, b_mode,
+                                     int(sym_out), alpha, diag, _lib.ptr(inv_norm), sigma_pow, backend,
+                                     _lib.status_word(a.device), _lib.stream_ptr()), "gemm_bf16")
     return d

@@ -207,6 +207,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         plan["momentum"] = mplan
         plan["block_sumsq"] = torch.zeros(total_blocks, dtype=torch.float32, device=dev)
         plan["scratch"] = None
+        plan["tables"] = {}
         return plan
 
     def _plan_for(self, group):
@@ -239,7 +240,8 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                 st = self.state[p]
                 if "momentum_buffer" not in st:
                     st.update(plan["entry"][id(p)][3])
-            # 1. momentum (+codec, +bf16 copy, +block norms): one table per (grad dtype, state format)
+            # 1. momentum (+codec, +bf16 copy, +block norms): one table per (grad dtype, state format).
+            # Tables are cached per set of live tensors; only the gradient pointers change per step.
             buckets: "OrderedDict[tuple, list]" = OrderedDict()
             for p in live:
                 idx, sg, _, _ = plan["entry"][id(p)]
@@ -251,8 +253,16 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                 buckets.setdefault((g.dtype, self._state_code(sg)), []).append((idx, g))
             mplan = plan["momentum"]
             for (gdtype, scode), items in buckets.items():
-                segs = mplan.table([g for _, g in items], [i for i, _ in items])
-                need = fp8_state.scratch_floats(segs, len(items))
+                key = (gdtype, scode, tuple(i for i, _ in items))
+                cached = plan["tables"].get(key)
+                if cached is None:
+                    segs = mplan.table([g for _, g in items], [i for i, _ in items])
+                    cached = plan["tables"][key] = (segs, fp8_state.scratch_floats(segs, len(items)))
+                else:
+                    segs = cached[0]
+                    for k, (_, g) in enumerate(items):
+                        segs[k].grad = g.data_ptr()
+                need = cached[1]
                 if plan["scratch"] is None or plan["scratch"].numel() < need:
                     plan["scratch"] = torch.empty(need, dtype=torch.float32, device=dev)
                 fp8_state.momentum_step(segs, len(items), grad_dtype=gdtype, state_format=scode,

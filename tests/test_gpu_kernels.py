@@ -32,7 +32,18 @@ GEMM_CASES = [
     (2, 128, 128, 344),      # ragged K (not a multiple of 64)
     (1, 1024, 2752, 1024),
     (1, 2752, 1024, 1024),
+    (2, 64, 64, 256),        # the 64-wide tile variant
 ]
+
+
+def _backend(mm, name):
+    return mm["lib"].NS_TCGEN05 if name == "tcgen05" else mm["lib"].NS_SIMT
+
+
+def _check(got, want):
+    # fp32 accumulation of exact bf16 products; only the final bf16 rounding differs
+    assert relf(got, want) < 4e-3, relf(got, want)
+    assert torch.allclose(got.float().cpu(), want, rtol=1.6e-2, atol=1e-2 * float(want.abs().max()))
 
 
 @pytest.mark.parametrize("backend", ["tcgen05", "simt"])
@@ -45,19 +56,61 @@ def test_gemm_family(mm, shape, a_k, b_k, backend):
     g = torch.Generator().manual_seed(hash(shape) % 1000 + 2 * a_k + b_k)
     a = torch.randn(batch, M, K, generator=g).bfloat16()
     b = torch.randn(batch, N, K, generator=g).bfloat16()
-    c = torch.randn(batch, M, N, generator=g).bfloat16()
     inv = torch.rand(batch, generator=g) * 0.1 + 0.01
-    alpha, gamma = 2.0315, -4.775
-    want = (inv.view(-1, 1, 1) ** 2) * (alpha * (a.float() @ b.float().transpose(1, 2)) + gamma * c.float())
+    alpha, diag = 2.0315, -1.175
+    want = (inv.view(-1, 1, 1) ** 2) * alpha * (a.float() @ b.float().transpose(1, 2))
+    idx = torch.arange(min(M, N))
+    want[:, idx, idx] += diag
     a_dev = (a if a_k else a.transpose(1, 2).contiguous()).cuda()
     b_dev = (b if b_k else b.transpose(1, 2).contiguous()).cuda()
-    be = mm["lib"].NS_TCGEN05 if backend == "tcgen05" else mm["lib"].NS_SIMT
-    got = mm["ns"].gemm_bf16(a_dev, b_dev, c=c.cuda(), a_kmajor=a_k, b_kmajor=b_k, alpha=alpha, gamma=gamma,
-                             inv_norm=inv.cuda(), sigma_pow=2, backend=be)
-    assert mm["lib"].read_status(got.device) == 0
-    # fp32 accumulation of exact bf16 products; only the final bf16 rounding differs
-    assert relf(got, want) < 4e-3, relf(got, want)
-    assert torch.allclose(got.float().cpu(), want, rtol=1.6e-2, atol=1e-2 * float(want.abs().max()))
+    L = mm["lib"]
+    got = mm["ns"].gemm_bf16(a_dev, b_dev, a_mode=L.GEMM_K if a_k else L.GEMM_MN,
+                             b_mode=L.GEMM_K if b_k else L.GEMM_MN, alpha=alpha, diag=diag,
+                             inv_norm=inv.cuda(), sigma_pow=2, backend=_backend(mm, backend))
+    assert L.read_status(got.device) == 0
+    _check(got, want)
+
+
+def _poison_lower_blocks(s):
+    """NaN in every 256x256 block strictly below the block diagonal: a symmetric
+    operand must never be read there."""
+    out = s.clone()
+    m = s.shape[-1]
+    r = torch.arange(m) // 256
+    below = r.view(-1, 1) > r.view(1, -1)
+    out[:, below] = float("nan")
+    return out, below
+
+
+@pytest.mark.parametrize("backend", ["tcgen05", "simt"])
+@pytest.mark.parametrize("m,n", [(1024, 1024), (512, 1280), (344, 128), (1024, 2752), (128, 128)])
+def test_gemm_symmetric_operands(mm, m, n, backend):
+    if backend == "simt" and m * n > 512 * 1280:
+        pytest.skip("cross-check kernel only on small shapes")
+    L = mm["lib"]
+    g = torch.Generator().manual_seed(m + n)
+    h = torch.randn(2, m, m, generator=g).bfloat16()
+    sym = (h.float() + h.float().transpose(1, 2)).bfloat16()      # exactly symmetric in bf16
+    x = torch.randn(2, m, n, generator=g).bfloat16()              # stored [K=m][N=n] -> MN-major B
+    y = torch.randn(2, n, m, generator=g).bfloat16()              # stored [M=n][K=m] -> K-major A
+    poisoned, below = _poison_lower_blocks(sym)
+    be = _backend(mm, backend)
+    # A symmetric:  D = S X
+    got = mm["ns"].gemm_bf16(poisoned.cuda(), x.cuda(), a_mode=L.GEMM_SYM, b_mode=L.GEMM_MN, backend=be)
+    _check(got, sym.float() @ x.float())
+    # B symmetric:  D = Y S
+    got = mm["ns"].gemm_bf16(y.cuda(), poisoned.cuda(), a_mode=L.GEMM_K, b_mode=L.GEMM_SYM, backend=be)
+    _check(got, y.float() @ sym.float())
+    # both symmetric, symmetric output: only blocks on or above the block diagonal are written
+    out = torch.full((2, m, m), 7.0, dtype=torch.bfloat16, device="cuda")
+    mm["ns"].gemm_bf16(poisoned.cuda(), poisoned.cuda(), a_mode=L.GEMM_SYM, b_mode=L.GEMM_SYM, sym_out=True,
+                       alpha=0.5, diag=0.25, backend=be, out=out)
+    want = 0.5 * (sym.float() @ sym.float()) + 0.25 * torch.eye(m)
+    got = out.float().cpu()
+    assert torch.all(got[:, below] == 7.0)                         # untouched
+    keep = ~below
+    assert relf(got[:, keep], want[:, keep]) < 4e-3
+    assert L.read_status(out.device) == 0
 
 
 # ------------------------------------------------------------------ Newton-Schulz
@@ -65,12 +118,13 @@ NS_SHAPES = [(3, 128, 128), (2, 344, 128), (2, 128, 344), (2, 256, 512), (2, 102
              (1, 1024, 2752)]
 
 # Tolerances, relative Frobenius norm per stack.  The reference's own bf16 path
-# differs from its fp32 path by about 2.4e-2 on N(0,1) blocks because the
-# quintic amplifies rounding of small singular values; this kernel keeps fp32
-# accumulators through each fused epilogue, so it must be at least as close to
-# the fp32 oracle as the reference bf16 path is (with 15% slack for different
-# rounding points), and within 5e-2 of the bf16 oracle.
-NS_TOL_VS_BF16_ORACLE = 5e-2
+# differs from its fp32 path by e_ref (about 2.4e-2 on N(0,1) blocks, more on
+# ill-conditioned ones) because the quintic amplifies the rounding of small
+# singular values.  This kernel rounds in fewer places, so it must be at least
+# as close to the fp32 oracle as the reference's bf16 path is (15 % slack for
+# different rounding points), and - two independent perturbations of that size
+# adding in quadrature - within 1.5 e_ref of the bf16 oracle.
+NS_SLACK_VS_BF16_ORACLE = 1.5
 NS_SLACK_VS_FP32 = 1.15
 
 
@@ -93,7 +147,7 @@ def test_newton_schulz_against_oracle(mm, shape, backend):
     e_got16 = relf(got, ref16)
     print(f"NS {shape} {backend}: ours-vs-fp32 {e_got32:.3e}  ref-bf16-vs-fp32 {e_ref:.3e}  ours-vs-bf16 {e_got16:.3e}")
     assert e_got32 <= max(NS_SLACK_VS_FP32 * e_ref, 1e-2)
-    assert e_got16 <= NS_TOL_VS_BF16_ORACLE
+    assert e_got16 <= max(NS_SLACK_VS_BF16_ORACLE * e_ref, 1.5e-2)
     # scale invariance of the normalised iteration: NS(7x) == NS(x) up to bf16 noise
     got7 = mm["ns"].newton_schulz_batched((x * 7).cuda(), backend=be)
     assert relf(got7, got) < 3e-2
