@@ -94,6 +94,32 @@ int mmb_momentum_step(const mmb_momentum_seg* segs, int nseg, int grad_dtype, in
                       float* block_sumsq_dev, /* [total blocks] or NULL           */
                       float* scratch_dev, int64_t scratch_floats, void* stream);
 
+/* Same step for callers that cannot allocate device memory.  (No counterpart
+ * in the reference; added for this library's users.)  Some hosts of this code
+ * may not call cudaMalloc: a plugin running inside someone else's memory pool
+ * or under a fixed device-memory budget, code on a latency-critical path where
+ * an allocation could stall or fail, a process that has handed all free memory
+ * to another allocator.  They still own gradients, state and outputs, but have
+ * nowhere to put the kernel's scratch (one partial sum of squares per 4096
+ * elements).  This entry point keeps that scratch in a fixed array compiled
+ * into the library (4 MiB of device memory on every GPU that loads it, held
+ * until the process exits) and calls no cudaMalloc, cudaFree or other
+ * allocating routine.
+ *   - Limit: mmb_momentum_static_max_floats() partial sums (2^20), i.e. tables
+ *     for which mmb_momentum_scratch_floats() is larger are refused with
+ *     MMB_ERR_INVALID and a message; about 4.29e9 state elements fit.
+ *   - The first call on each device looks up the array's device address, with
+ *     that device current; make that first call outside any stream capture.
+ *   - All calls on a device share the array.  It keeps whatever the last call
+ *     left; nothing in it has to start at zero because every partial a call
+ *     reads is written by that same call first.  Two calls whose kernels can
+ *     overlap on the GPU (different streams) race on it - serialise them.
+ * Arguments and results are exactly those of mmb_momentum_step. */
+int64_t mmb_momentum_static_max_floats(void);
+int mmb_momentum_step_static(const mmb_momentum_seg* segs, int nseg, int grad_dtype, int state_format,
+                             int div_mode, float beta, float grad_scale, int expand_min,
+                             float* block_sumsq_dev, void* stream);
+
 /* Stand-alone codecs on one flat fp32 tensor (first-step quantise, state_dict
  * export, tests).  Replace coat_state_muon.py:94-114 (dequantize, quantize_). */
 int mmb_fp8_quantize(const float* value_dev, uint8_t* codes_dev, float* scale_dev, float* expand_dev,

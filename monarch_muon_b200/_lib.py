@@ -44,6 +44,8 @@ SYMBOLS = {
     "mmb_launch_count": (_i64, []),
     "mmb_momentum_scratch_floats": (_i64, [C.POINTER(MomentumSeg), _i]),
     "mmb_momentum_step": (_i, [C.POINTER(MomentumSeg), _i, _i, _i, _i, _f, _f, _i, _vp, _vp, _i64, _vp]),
+    "mmb_momentum_static_max_floats": (_i64, []),
+    "mmb_momentum_step_static": (_i, [C.POINTER(MomentumSeg), _i, _i, _i, _i, _f, _f, _i, _vp, _vp]),
     "mmb_fp8_quantize": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp]),
     "mmb_fp8_dequantize": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _vp]),
     "mmb_ns_workspace_bytes": (_i64, [_i, _i, _i]),

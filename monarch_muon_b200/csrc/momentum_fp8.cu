@@ -604,6 +604,35 @@ int momentum_step_impl(const mmb_momentum_seg* segs, int nseg, int grad_dtype, i
 
 }  // namespace mmb
 
+// ------------------------------------------------ scratch that needs no allocator
+// Per-chunk partial sums for mmb_momentum_step_static().  A file-scope device
+// array: every GPU that loads this library carries these 4 MiB until the
+// process exits, and no allocator is involved in getting it.
+constexpr long long STATIC_SCRATCH_FLOATS = 1ll << 20;  // 4096 elements per partial -> 2^32 state elements
+static __device__ __align__(256) float g_static_partials[STATIC_SCRATCH_FLOATS];
+
+namespace mmb {
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_static_partials_addr[MAX_DEVICES] = {nullptr};
+
+// In host code `g_static_partials` is only a handle for the runtime, not a
+// device address; the address on the current device has to be asked for.
+int static_partials_for_current_device(float** out) {
+  int dev = -1;
+  MMB_CUDA_CHECK(cudaGetDevice(&dev));
+  MMB_REQUIRE(dev >= 0 && dev < MAX_DEVICES, "mmb_momentum_step_static: device index %d not supported", dev);
+  if (g_static_partials_addr[dev] == nullptr) {
+    void* p = nullptr;
+    MMB_CUDA_CHECK(cudaGetSymbolAddress(&p, g_static_partials));
+    g_static_partials_addr[dev] = static_cast<float*>(p);
+  }
+  *out = g_static_partials_addr[dev];
+  return MMB_OK;
+}
+}  // namespace
+}  // namespace mmb
+
 extern "C" {
 
 int64_t mmb_momentum_scratch_floats(const mmb_momentum_seg* segs, int nseg) {
@@ -621,6 +650,24 @@ int mmb_momentum_step(const mmb_momentum_seg* segs, int nseg, int grad_dtype, in
                       int64_t scratch_floats, void* stream) {
   return mmb::momentum_step_impl(segs, nseg, grad_dtype, state_format, div_mode, beta, grad_scale, expand_min,
                                  block_sumsq_dev, scratch_dev, scratch_floats, stream);
+}
+
+int64_t mmb_momentum_static_max_floats(void) { return STATIC_SCRATCH_FLOATS; }
+
+int mmb_momentum_step_static(const mmb_momentum_seg* segs, int nseg, int grad_dtype, int state_format, int div_mode,
+                             float beta, float grad_scale, int expand_min, float* block_sumsq_dev, void* stream) {
+  using namespace mmb;
+  MMB_REQUIRE(nseg >= 0 && (nseg == 0 || segs != nullptr), "mmb_momentum_step_static: bad segment table");
+  const int64_t need = mmb_momentum_scratch_floats(segs, nseg);
+  MMB_REQUIRE(need <= STATIC_SCRATCH_FLOATS,
+              "mmb_momentum_step_static: this table needs %lld partial sums but the built-in scratch holds %lld "
+              "(about 4.29e9 state elements); split the table or use mmb_momentum_step with your own scratch",
+              (long long)need, (long long)STATIC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  int rc = static_partials_for_current_device(&scratch);
+  if (rc != MMB_OK) return rc;
+  return momentum_step_impl(segs, nseg, grad_dtype, state_format, div_mode, beta, grad_scale, expand_min,
+                            block_sumsq_dev, scratch, STATIC_SCRATCH_FLOATS, stream);
 }
 
 int mmb_fp8_quantize(const float* value_dev, uint8_t* codes_dev, float* scale_dev, float* expand_dev,
