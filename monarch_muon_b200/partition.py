@@ -1,0 +1,129 @@
+"""Ownership plan for the data-parallel (owner-computes) Monarch-Muon step.
+
+Every Monarch block is an independent unit of the Muon update (momentum, FP8
+groups, Newton-Schulz and the weight update touch only that block), and AdamW is
+element-wise, so the step shards without any exchange inside it: one gradient
+reduce-scatter before and one all-gather of updated values after.  This module
+only computes *where things live*; it has no torch.distributed or CUDA in it so
+it can be tested anywhere.
+
+Layout.  The flat arenas (one for weights, one for gradients, same geometry) are
+cut into `n_chunks` chunk arenas that are communicated and processed one after
+the other so that communication of one chunk overlaps computation of another.
+A chunk arena is `world` equal shards, shard r owned by rank r:
+
+    arena = [chunk 0: shard(rank 0) | shard(rank 1) | ... ][chunk 1: ...] ... [AdamW chunk]
+
+Inside a Muon shard the owned tensors lie back to back, grouped by block shape.
+Whole tensors are owned (a parameter must stay one contiguous view), tensors of
+one shape are dealt to ranks in equal contiguous runs, and shards are padded to
+the longest one.  The AdamW chunk is cut element-wise into equal slices, so a
+tensor may straddle ranks.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+
+@dataclass
+class TensorPlace:
+    index: int          # position in the caller's parameter list
+    chunk: int
+    rank: int
+    offset: int         # element offset inside the whole arena
+    numel: int
+
+
+@dataclass
+class ChunkPlan:
+    offset: int         # element offset of the chunk arena inside the whole arena
+    shard_elems: int    # elements per rank (padded); chunk arena = world * shard_elems
+    kind: str           # "muon" or "adamw"
+
+
+@dataclass
+class Plan:
+    world: int
+    chunks: list = field(default_factory=list)            # ChunkPlan
+    muon: list = field(default_factory=list)              # TensorPlace per Muon tensor
+    adamw: list = field(default_factory=list)             # (index, offset, numel) of AdamW tensors in the arena
+    total_elems: int = 0
+
+    def owned_muon(self, rank: int, chunk: int):
+        return [t for t in self.muon if t.rank == rank and t.chunk == chunk]
+
+    def adamw_slices(self, rank: int):
+        """Intersections of AdamW tensors with the slice rank `rank` owns:
+        (tensor index, start inside the tensor, length, arena offset)."""
+        ch = self.chunks[-1]
+        if ch.kind != "adamw":
+            return []
+        lo = ch.offset + rank * ch.shard_elems
+        hi = lo + ch.shard_elems
+        out = []
+        for idx, off, n in self.adamw:
+            a, b = max(lo, off), min(hi, off + n)
+            if a < b:
+                out.append((idx, a - off, b - a, a))
+        return out
+
+
+def _align(n: int, a: int) -> int:
+    return -(-n // a) * a
+
+
+def make_plan(muon_shapes, adamw_numels, world: int, n_chunks: int = 4, align: int = 128) -> Plan:
+    """muon_shapes: (nblocks, rows, cols) per Muon tensor; adamw_numels: element
+    counts of the AdamW tensors.  `align` keeps every tensor and shard on a
+    128-element (256-byte) boundary: FP8 groups and vector accesses stay aligned."""
+    if world < 1 or n_chunks < 1:
+        raise ValueError("world and n_chunks must be positive")
+    plan = Plan(world=world)
+    by_shape: dict = {}
+    for i, (nb, r, c) in enumerate(muon_shapes):
+        by_shape.setdefault((r, c), []).append(i)
+    places = {}
+    cursor = 0
+    for ch in range(n_chunks):
+        per_rank = [[] for _ in range(world)]
+        for (r, c), idxs in by_shape.items():
+            n = len(idxs)
+            mine = idxs[ch * n // n_chunks:(ch + 1) * n // n_chunks]      # this chunk's share of the shape
+            k = len(mine)
+            for rank in range(world):
+                per_rank[rank] += mine[rank * k // world:(rank + 1) * k // world]
+        sizes = [sum(_align(muon_shapes[i][0] * muon_shapes[i][1] * muon_shapes[i][2], align) for i in lst)
+                 for lst in per_rank]
+        shard = _align(max(sizes) if sizes else 0, align)
+        if shard == 0:
+            continue
+        chunk_index = len(plan.chunks)
+        plan.chunks.append(ChunkPlan(offset=cursor, shard_elems=shard, kind="muon"))
+        for rank, lst in enumerate(per_rank):
+            at = cursor + rank * shard
+            for i in lst:
+                numel = muon_shapes[i][0] * muon_shapes[i][1] * muon_shapes[i][2]
+                places[i] = TensorPlace(index=i, chunk=chunk_index, rank=rank, offset=at, numel=numel)
+                at += _align(numel, align)
+        cursor += world * shard
+    plan.muon = [places[i] for i in range(len(muon_shapes))]
+    if adamw_numels:
+        total = sum(_align(n, align) for n in adamw_numels)
+        shard = _align(-(-total // world), align)
+        plan.chunks.append(ChunkPlan(offset=cursor, shard_elems=shard, kind="adamw"))
+        at = cursor
+        for i, n in enumerate(adamw_numels):
+            plan.adamw.append((i, at, n))
+            at += _align(n, align)
+        cursor += world * shard
+    plan.total_elems = cursor
+    return plan
+
+
+def flops_per_rank(plan: Plan, muon_shapes, ns_flops) -> list:
+    """Newton-Schulz FLOPs each rank owns (for reporting balance)."""
+    out = [0.0] * plan.world
+    for t in plan.muon:
+        nb, r, c = muon_shapes[t.index]
+        out[t.rank] += nb * ns_flops(r, c)
+    return out

@@ -1,0 +1,63 @@
+"""The sharded step on real GPUs (needs at least two; skipped otherwise)."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["MMB_ROOT"]); sys.path.insert(0, os.path.join(os.environ["MMB_ROOT"], "tests"))
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+from monarch_muon_b200.sharded import ShardedMonarchMuon
+from monarch_muon_b200 import MonarchMuonOptimizer
+gen = torch.Generator().manual_seed(5)
+ms = [(2, 128, 128)] * 6 + [(1, 344, 128)] * 4 + [(1, 128, 344)] * 2
+asz = [(1000, 64), (64,), (64,)]
+w_m = [(0.02 * torch.randn(s, generator=gen)).bfloat16() for s in ms]
+w_a = [(0.02 * torch.randn(s, generator=gen)).bfloat16() for s in asz]
+def grads(r, step):
+    g = torch.Generator().manual_seed(100 * step + r)
+    # multiples of 2^-12 keep the bf16 sums over ranks exact, so the reduction order cannot matter
+    return [(torch.randint(-8, 9, s, generator=g).float() * 2.0 ** -12).bfloat16() for s in ms + asz]
+muon = [torch.nn.Parameter(w.to(dev)) for w in w_m]; adamw = [torch.nn.Parameter(w.to(dev)) for w in w_a]
+opt = ShardedMonarchMuon(muon, adamw, lr=0.02, n_chunks=2, average=False, state_format="fp8_absmax")
+# serial twin on the summed gradient, same kernels
+smuon = [torch.nn.Parameter(w.to(dev)) for w in w_m]; sadamw = [torch.nn.Parameter(w.to(dev)) for w in w_a]
+ser = MonarchMuonOptimizer(smuon, sadamw, lr=0.02, state_format="fp8_absmax")
+for step in range(2):
+    for p, g in zip(muon + adamw, grads(rank, step)):
+        p.grad.copy_(g.to(dev))
+    opt.step()
+    tot = [sum(gs) for gs in zip(*[[t.float() for t in grads(r, step)] for r in range(world)])]
+    for p, g in zip(smuon + sadamw, tot):
+        p.grad = g.bfloat16().to(dev)
+    ser.step()
+torch.cuda.synchronize()
+ok = all(torch.equal(a.data, b.data) for a, b in zip(muon + adamw, smuon + sadamw))
+flag = torch.tensor([1 if ok else 0], device=dev); dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+if rank == 0: print("SHARDED_EQUALS_SERIAL" if int(flag) == 1 else "SHARDED_DIFFERS")
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_step_is_bitwise_the_serial_step(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, MMB_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+               NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
+                         env=env, capture_output=True, text=True, timeout=600)
+    assert "SHARDED_EQUALS_SERIAL" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
