@@ -63,7 +63,7 @@ int64_t mmb_launch_count(void);
  * Heavy-ball momentum with optimizer-state codec, fused:
  *   dequantise -> m = beta*m (rounded) -> m = m + grad_scale*g (rounded)
  *   -> requantise; also writes bf16(m) for Newton-Schulz and the per-block
- *   sum of squares of bf16(m).
+ *   sum of squares of m.
  * Replaces: momentum update   pretrain/src/models/monarch/monarch_muon.py:146-148
  *                             membench/src/models/monarch/monarch_muon.py:150-151
  *           cat + bf16 cast   membench/.../monarch_muon.py:161-163

@@ -5,7 +5,7 @@
 // m = round(beta*m) then m = round(m + g) - two roundings, like the
 // reference's mul_ followed by add_ (pretrain/src/models/monarch/
 // monarch_muon.py:148) - requantise, and emit what Newton-Schulz needs: the
-// bf16 copy of m and per-block sums of squares.
+// bf16 copy of m and per-block sums of squares of m.
 //
 // Work decomposition.  A group is 128 contiguous elements and is handled by 8
 // lanes x 16 elements, so the group maximum is three xor-shuffles and every
@@ -250,9 +250,55 @@ __device__ __forceinline__ void store_codes16(uint8_t* p, bool vec, int n, const
   }
 }
 
+// ------------------------------------------------- fast path (FP8 absmax, full groups)
+// Raw 16-byte loads of one lane's share of a group, kept undecoded so that the
+// next group's loads can be in flight while the current one is computed.
+template <typename GradT>
+struct RawGroup {
+  uint4 codes;
+  uint4 grad[sizeof(GradT) == 2 ? 2 : 4];
+  float scale;
+};
+
+template <typename GradT>
+__device__ __forceinline__ void load_raw(RawGroup<GradT>& r, const SegDev& sg, long long at) {
+  r.codes = __ldcs(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(sg.state) + at));
+  const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const GradT*>(sg.grad) + at);
+#pragma unroll
+  for (int i = 0; i < (sizeof(GradT) == 2 ? 2 : 4); ++i) r.grad[i] = __ldcs(gp + i);
+  r.scale = __ldg(sg.scale + at / GROUP);
+}
+
+template <typename GradT>
+__device__ __forceinline__ float raw_grad(const RawGroup<GradT>& r, int i) {
+  if (sizeof(GradT) == 2) {
+    const uint32_t w = reinterpret_cast<const uint32_t*>(r.grad)[i >> 1];
+    return __uint_as_float((i & 1) ? (w & 0xffff0000u) : (w << 16));  // bf16 -> fp32 is a shift
+  }
+  return reinterpret_cast<const float*>(r.grad)[i];
+}
+
+// Quotient m / s rounded like IEEE division, at the cost of a multiply: with
+// r = rn(1/s), rn(m*r) is within one representable step of rn(m/s), so the two
+// give the same E4M3 code unless the product sits within two steps of a
+// rounding boundary of E4M3 (normal range: the dropped 20 mantissa bits equal
+// 0x80000) or falls into E4M3's subnormal range, where the exact division is
+// done instead.  Checked against IEEE division on 1.6e8 random cases.
+__device__ __forceinline__ float quotient_for_e4m3(float m, float s, float r) {
+  float q = __fmul_rn(m, r);
+  const uint32_t bits = __float_as_uint(q);
+  const uint32_t low = bits & 0xFFFFFu;
+  const bool near_tie = (low - 0x7FFFEu) <= 4u;                 // |low - 0x80000| <= 2
+  const bool small_or_special = ((bits >> 23) & 0xFFu) - 121u >= 134u;  // exponent < 121 (|q| < 2^-6) or 255
+  if (near_tie || small_or_special) q = __fdiv_rn(m, s);
+  return q;
+}
+
 // -------------------------------------------------------------- fused kernel
-template <int FORMAT, typename GradT, int DIV>
-__global__ void __launch_bounds__(THREADS)
+// ALL_FAST: the host has checked that every unit of the launch qualifies for the
+// fast path, so the general path is compiled out (fewer registers, more warps).
+template <int FORMAT, typename GradT, int DIV, bool ALL_FAST>
+__global__ void __launch_bounds__(THREADS, ALL_FAST ? 3 : 1)
 momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_scale, float expand_min,
                 float* __restrict__ partials) {
   const int lane = threadIdx.x & 31;
@@ -280,6 +326,76 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
     const int ngroups = static_cast<int>((e1 - e0 + GROUP - 1) / GROUP);
     float ss = 0.0f;
 
+    // Fast path: FP8 absmax state, aligned pointers, only full groups.  One group of loads is kept in
+    // flight ahead of the arithmetic.
+    const bool fast = ALL_FAST || (FORMAT == MMB_STATE_FP8_ABSMAX && sg.vec_ok && ((e1 - e0) % GROUP) == 0);
+    if (fast) {
+      RawGroup<GradT> cur, nxt;
+      bool cur_ok = grp_in_warp < ngroups;
+      if (cur_ok) load_raw<GradT>(cur, sg, e0 + static_cast<long long>(grp_in_warp) * GROUP + sub * ELEMS_PER_LANE);
+      for (int g0 = 0; g0 < ngroups; g0 += 4) {
+        const int gi_next = g0 + 4 + grp_in_warp;
+        const bool nxt_ok = gi_next < ngroups;
+        if (nxt_ok) load_raw<GradT>(nxt, sg, e0 + static_cast<long long>(gi_next) * GROUP + sub * ELEMS_PER_LANE);
+        const long long at = e0 + static_cast<long long>(g0 + grp_in_warp) * GROUP + sub * ELEMS_PER_LANE;
+        float m[ELEMS_PER_LANE];
+        float amax = 0.0f;
+        if (cur_ok) {
+          const uint16_t* h = reinterpret_cast<const uint16_t*>(&cur.codes);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float2 f = e4m3x2_to_float2(h[i]);
+            m[2 * i] = f.x;
+            m[2 * i + 1] = f.y;
+          }
+          const bool scaled = grad_scale != 1.0f;
+#pragma unroll
+          for (int i = 0; i < ELEMS_PER_LANE; ++i) {
+            float g = raw_grad<GradT>(cur, i);
+            if (scaled) g = __fmul_rn(g, grad_scale);
+            float t = __fmul_rn(beta, __fmul_rn(m[i], cur.scale));
+            t = __fadd_rn(t, g);
+            m[i] = t;
+            amax = fmaxf(amax, fabsf(t));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < ELEMS_PER_LANE; ++i) m[i] = 0.0f;
+        }
+        amax = group_max(amax);
+        const float s_new = fdiv<DIV>(__fadd_rn(amax, 1e-20f), 448.0f);
+        if (cur_ok) {
+          float q[ELEMS_PER_LANE];
+          if (DIV == MMB_DIV_IEEE) {
+            const float r = __frcp_rn(s_new);
+#pragma unroll
+            for (int i = 0; i < ELEMS_PER_LANE; ++i) q[i] = quotient_for_e4m3(m[i], s_new, r);
+          } else {
+#pragma unroll
+            for (int i = 0; i < ELEMS_PER_LANE; ++i) q[i] = fdiv<DIV>(m[i], s_new);
+          }
+          uint4 cv;
+          uint16_t* ch = reinterpret_cast<uint16_t*>(&cv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ch[i] = float2_to_e4m3x2(q[2 * i], q[2 * i + 1]);
+          *reinterpret_cast<uint4*>(static_cast<uint8_t*>(sg.state) + at) = cv;
+          if (sub == 0) sg.scale[at / GROUP] = s_new;
+#pragma unroll
+          for (int i = 0; i < ELEMS_PER_LANE; ++i) ss = fmaf(m[i], m[i], ss);
+          if (sg.m_out != nullptr) {
+            uint4 mv[2];
+            __nv_bfloat162* mh = reinterpret_cast<__nv_bfloat162*>(mv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) mh[i] = __floats2bfloat162_rn(m[2 * i], m[2 * i + 1]);
+            uint4* mp = reinterpret_cast<uint4*>(sg.m_out + at);
+            mp[0] = mv[0];
+            mp[1] = mv[1];
+          }
+        }
+        cur = nxt;
+        cur_ok = nxt_ok;
+      }
+    } else if (!ALL_FAST)
     for (int g0 = 0; g0 < ngroups; g0 += 4) {
       const int gi = g0 + grp_in_warp;
       const bool active = gi < ngroups;
@@ -364,10 +480,7 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
 
       // what Newton-Schulz reads, and its squared norm
 #pragma unroll
-      for (int i = 0; i < ELEMS_PER_LANE; ++i) {
-        float r = bf16_round(m[i]);
-        ss = fmaf(r, r, ss);
-      }
+      for (int i = 0; i < ELEMS_PER_LANE; ++i) ss = fmaf(m[i], m[i], ss);
       if (n > 0 && sg.m_out != nullptr && static_cast<void*>(sg.m_out) != sg.state)
         Elem<__nv_bfloat16>::store16(sg.m_out, at, vec, n, m);
     }
@@ -489,29 +602,36 @@ Plan plan_segment(const mmb_momentum_seg& s) {
 }
 
 template <int FORMAT, typename GradT>
-void launch_momentum(int div_mode, const SegTable& tab, int grid, float beta, float grad_scale, float expand_min,
-                     float* partials, cudaStream_t st) {
+void launch_momentum(int div_mode, bool all_fast, const SegTable& tab, int grid, float beta, float grad_scale,
+                     float expand_min, float* partials, cudaStream_t st) {
+  if (FORMAT == MMB_STATE_FP8_ABSMAX && all_fast) {
+    if (div_mode == MMB_DIV_IEEE)
+      momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_IEEE, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
+    else
+      momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_FULL, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
+    return;
+  }
   if (div_mode == MMB_DIV_IEEE)
-    momentum_kernel<FORMAT, GradT, MMB_DIV_IEEE><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
+    momentum_kernel<FORMAT, GradT, MMB_DIV_IEEE, false><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
   else
-    momentum_kernel<FORMAT, GradT, MMB_DIV_FULL><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
+    momentum_kernel<FORMAT, GradT, MMB_DIV_FULL, false><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
 }
 
 template <typename GradT>
-void launch_momentum_format(int format, int div_mode, const SegTable& tab, int grid, float beta, float grad_scale,
-                            float expand_min, float* partials, cudaStream_t st) {
+void launch_momentum_format(int format, int div_mode, bool all_fast, const SegTable& tab, int grid, float beta,
+                            float grad_scale, float expand_min, float* partials, cudaStream_t st) {
   switch (format) {
     case MMB_STATE_FP8_ABSMAX:
-      launch_momentum<MMB_STATE_FP8_ABSMAX, GradT>(div_mode, tab, grid, beta, grad_scale, expand_min, partials, st);
+      launch_momentum<MMB_STATE_FP8_ABSMAX, GradT>(div_mode, all_fast, tab, grid, beta, grad_scale, expand_min, partials, st);
       break;
     case MMB_STATE_FP8_EXPAND:
-      launch_momentum<MMB_STATE_FP8_EXPAND, GradT>(div_mode, tab, grid, beta, grad_scale, expand_min, partials, st);
+      launch_momentum<MMB_STATE_FP8_EXPAND, GradT>(div_mode, false, tab, grid, beta, grad_scale, expand_min, partials, st);
       break;
     case MMB_STATE_BF16:
-      launch_momentum<MMB_STATE_BF16, GradT>(MMB_DIV_IEEE, tab, grid, beta, grad_scale, expand_min, partials, st);
+      launch_momentum<MMB_STATE_BF16, GradT>(MMB_DIV_IEEE, false, tab, grid, beta, grad_scale, expand_min, partials, st);
       break;
     default:
-      launch_momentum<MMB_STATE_F32, GradT>(MMB_DIV_IEEE, tab, grid, beta, grad_scale, expand_min, partials, st);
+      launch_momentum<MMB_STATE_F32, GradT>(MMB_DIV_IEEE, false, tab, grid, beta, grad_scale, expand_min, partials, st);
       break;
   }
 }
@@ -542,6 +662,7 @@ int momentum_step_impl(const mmb_momentum_seg* segs, int nseg, int grad_dtype, i
     SegTable tab;
     tab.nseg = (nseg - base) < MAX_SEG ? (nseg - base) : MAX_SEG;
     long long units = 0, blocks = 0;
+    bool all_fast = true;
     for (int i = 0; i < tab.nseg; ++i) {
       const mmb_momentum_seg& s = segs[base + i];
       MMB_REQUIRE(s.numel > 0 && s.grad != nullptr && s.state != nullptr, "mmb_momentum_step: segment %d empty",
@@ -569,6 +690,7 @@ int momentum_step_impl(const mmb_momentum_seg* segs, int nseg, int grad_dtype, i
       d.first_block = s.first_block;
       d.cpb = static_cast<int>(p.cpb);
       d.vec_ok = aligned16(s.grad) && aligned16(s.state) && (s.m_bf16 == nullptr || aligned16(s.m_bf16));
+      all_fast = all_fast && d.vec_ok && (s.numel % GROUP) == 0;
       tab.unit_start[i] = units;
       tab.block_start[i] = blocks;
       blocks += p.nblocks;
@@ -583,10 +705,10 @@ int momentum_step_impl(const mmb_momentum_seg* segs, int nseg, int grad_dtype, i
     int grid = static_cast<int>(want < cap ? want : cap);
     if (grid < 1) grid = 1;
     if (grad_dtype == MMB_BF16)
-      launch_momentum_format<__nv_bfloat16>(state_format, div_mode, tab, grid, beta, grad_scale,
+      launch_momentum_format<__nv_bfloat16>(state_format, div_mode, all_fast, tab, grid, beta, grad_scale,
                                             static_cast<float>(expand_min), partials, st);
     else
-      launch_momentum_format<float>(state_format, div_mode, tab, grid, beta, grad_scale,
+      launch_momentum_format<float>(state_format, div_mode, all_fast, tab, grid, beta, grad_scale,
                                     static_cast<float>(expand_min), partials, st);
     MMB_CUDA_CHECK(cudaGetLastError());
   count_launch();

@@ -87,22 +87,53 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         self.grad_scale = 1.0            # multiplies Muon gradients inside the momentum kernel
         self._plans: dict = {}           # id(group) -> plan
         self._marks = None               # list of (phase, cuda event) while phase timing is on
+        self._host = None                # {id(param): host gradient} during a step fed from host memory
+        self._copy_streams: dict = {}
         _lib.load()                      # fail now, not at the first step, if the library is missing
 
     # ------------------------------------------------------------------ public
     @torch.no_grad()
-    def step(self, closure=None):
+    def step(self, closure=None, *, host_grads=None):
+        """One optimizer step.
+
+        host_grads (extension): a sequence parallel to all parameters (Muon group
+        first, then AdamW, `None` entries allowed) or a dict {parameter: tensor}
+        of gradients in (pinned) host memory.  They are copied to the device
+        slice by slice on a side stream while earlier slices are already being
+        stepped, instead of being staged in full before the step starts.
+        """
         loss = None
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
-        for group in self.param_groups:
-            lr = group["lr"]
-            if group["update_type"] == "muon":
-                self._muon_step(group, lr)
-            else:
-                self._adamw_step(group, lr)
+        self._host = self._host_map(host_grads)
+        try:
+            for group in self.param_groups:
+                lr = group["lr"]
+                if group["update_type"] == "muon":
+                    self._muon_step(group, lr)
+                else:
+                    self._adamw_step(group, lr)
+        finally:
+            if self._host is not None:
+                for plan in self._plans.values():          # events belong to this step only
+                    if plan is not None:
+                        for sls in plan["slices"].values():
+                            for sl in sls:
+                                sl["event"] = None
+            self._host = None
         return loss
+
+    def _host_map(self, host_grads):
+        if host_grads is None:
+            return None
+        if isinstance(host_grads, dict):
+            return {id(p): g for p, g in host_grads.items() if g is not None}
+        params = [p for g in self.param_groups for p in g["params"]]
+        host_grads = list(host_grads)
+        if len(host_grads) != len(params):
+            raise ValueError("host_grads must have one entry per parameter")
+        return {id(p): g for p, g in zip(params, host_grads) if g is not None}
 
     # Phase timing: CUDA events on the current stream at phase boundaries.
     def enable_phase_timing(self, on: bool = True) -> None:
@@ -207,7 +238,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         plan["momentum"] = mplan
         plan["block_sumsq"] = torch.zeros(total_blocks, dtype=torch.float32, device=dev)
         plan["scratch"] = None
-        plan["tables"] = {}
+        plan["slices"] = {}
         return plan
 
     def _plan_for(self, group):
@@ -226,87 +257,152 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         return _lib.STATE_BF16 if sg.dtype == torch.bfloat16 else _lib.STATE_F32
 
     # ------------------------------------------------------------ Muon: step
+    def _slices_for(self, plan, live):
+        """Cut the live tensors into slices: runs of consecutive tensors of one block shape holding at
+        most `ns_max_batch` blocks.  A slice is the unit of work (momentum -> Newton-Schulz -> update) and
+        of host-to-device pipelining.  Cached per set of live tensors."""
+        key = tuple(id(p) for p in live)
+        cached = plan["slices"].get(key)
+        if cached is not None:
+            return cached
+        live_ids = set(key)
+        cap = self.ns_max_batch or (1 << 30)
+        slices = []
+        for sg in plan["shapes"].values():
+            cur = None
+            for p, b0 in zip(sg.params, sg.block_start):
+                if id(p) not in live_ids:
+                    cur = None
+                    continue
+                nb = p.shape[0]
+                if cur is None or cur["b1"] - cur["b0"] + nb > cap:
+                    cur = {"sg": sg, "items": [], "b0": b0, "b1": b0, "tables": {}, "upd": None, "event": None}
+                    slices.append(cur)
+                cur["items"].append((p, b0))
+                cur["b1"] = b0 + nb
+        plan["slices"][key] = slices
+        return slices
+
     def _muon_step(self, group, lr: float) -> None:
-        live = [p for p in group["params"] if p.grad is not None]
+        host = self._host
+        # fed from the host, only the parameters named there step (a device buffer left over from an
+        # earlier step is not a gradient of this one)
+        live = [p for p in group["params"] if (id(p) in host if host is not None else p.grad is not None)]
         if not live:
             return
         plan = self._plan_for(group)
         dev = plan["device"]
         lib = _lib.load()
+        mplan = plan["momentum"]
         with torch.cuda.device(dev):
             self._mark("begin")
-            # register state lazily, like _get_momentum_buffer (monarch_muon.py:133-137)
-            for p in live:
-                st = self.state[p]
-                if "momentum_buffer" not in st:
-                    st.update(plan["entry"][id(p)][3])
-            # 1. momentum (+codec, +bf16 copy, +block norms): one table per (grad dtype, state format).
-            # Tables are cached per set of live tensors; only the gradient pointers change per step.
-            buckets: "OrderedDict[tuple, list]" = OrderedDict()
-            for p in live:
-                idx, sg, _, _ = plan["entry"][id(p)]
-                g = p.grad
-                if g.shape != p.shape:
-                    raise ValueError("gradient shape differs from its parameter")
-                if not g.is_contiguous():
-                    g = g.contiguous()
-                buckets.setdefault((g.dtype, self._state_code(sg)), []).append((idx, g))
-            mplan = plan["momentum"]
-            for (gdtype, scode), items in buckets.items():
-                key = (gdtype, scode, tuple(i for i, _ in items))
-                cached = plan["tables"].get(key)
-                if cached is None:
-                    segs = mplan.table([g for _, g in items], [i for i, _ in items])
-                    cached = plan["tables"][key] = (segs, fp8_state.scratch_floats(segs, len(items)))
-                else:
-                    segs = cached[0]
-                    for k, (_, g) in enumerate(items):
-                        segs[k].grad = g.data_ptr()
-                need = cached[1]
-                if plan["scratch"] is None or plan["scratch"].numel() < need:
-                    plan["scratch"] = torch.empty(need, dtype=torch.float32, device=dev)
-                fp8_state.momentum_step(segs, len(items), grad_dtype=gdtype, state_format=scode,
-                                        beta=group["momentum"], grad_scale=self.grad_scale,
-                                        div_mode=self.fp8_div, expand_min=self.expand_min,
-                                        block_sumsq=plan["block_sumsq"], scratch=plan["scratch"])
-            self._mark("momentum")
-            # 2. Newton-Schulz and 3. update, per shape and per run of consecutive live tensors
-            for sg in plan["shapes"].values():
+            slices = self._slices_for(plan, live)
+            if host is not None:
+                self._enqueue_host_copies(slices, host, dev)
+            for sl in slices:
+                sg = sl["sg"]
+                if sl["event"] is not None:
+                    torch.cuda.current_stream().wait_event(sl["event"])
+                # register state lazily, like _get_momentum_buffer (monarch_muon.py:133-137)
+                buckets: "OrderedDict[tuple, list]" = OrderedDict()
+                for p, _ in sl["items"]:
+                    st = self.state[p]
+                    idx, _, _, views = plan["entry"][id(p)]
+                    if "momentum_buffer" not in st:
+                        st.update(views)
+                    g = p.grad
+                    if g.shape != p.shape:
+                        raise ValueError("gradient shape differs from its parameter")
+                    if not g.is_contiguous():
+                        g = g.contiguous()
+                    buckets.setdefault(g.dtype, []).append((idx, g))
+                # 1. momentum (+codec, +bf16 copy, +block norms); tables are cached, only gradient pointers change
+                scode = self._state_code(sg)
+                for gdtype, items in buckets.items():
+                    cached = sl["tables"].get(gdtype)
+                    if cached is None or cached[2] != len(items):
+                        segs = mplan.table([g for _, g in items], [i for i, _ in items])
+                        cached = sl["tables"][gdtype] = (segs, fp8_state.scratch_floats(segs, len(items)), len(items))
+                    else:
+                        segs = cached[0]
+                        for k, (_, g) in enumerate(items):
+                            segs[k].grad = g.data_ptr()
+                    if plan["scratch"] is None or plan["scratch"].numel() < cached[1]:
+                        plan["scratch"] = torch.empty(cached[1], dtype=torch.float32, device=dev)
+                    fp8_state.momentum_step(segs, len(items), grad_dtype=gdtype, state_format=scode,
+                                            beta=group["momentum"], grad_scale=self.grad_scale,
+                                            div_mode=self.fp8_div, expand_min=self.expand_min,
+                                            block_sumsq=plan["block_sumsq"], scratch=plan["scratch"])
+                self._mark("momentum")
+                # 2. Newton-Schulz on the slice of the arena
+                b0, b1 = sl["b0"], sl["b1"]
+                ss = plan["block_sumsq"][sg.first_block_global + b0: sg.first_block_global + b1]
+                newton_schulz_batched(sg.m_arena[b0:b1], out=sg.ortho[b0:b1], block_sumsq=ss,
+                                      backend=self.ns_backend, max_batch=None)
+                self._mark("newton_schulz")
+                # 3. W <- W - lr*sqrt(rows/cols)*O
                 alpha = -lr * (sg.rows / sg.cols) ** 0.5
-                runs: list[list] = []
-                prev_live = False
-                for p, b0 in zip(sg.params, sg.block_start):
-                    if p.grad is None:
-                        prev_live = False
-                        continue
-                    if not prev_live:
-                        runs.append([])
-                    runs[-1].append((p, b0))
-                    prev_live = True
-                for run in runs:
-                    b0 = run[0][1]
-                    b1 = run[-1][1] + run[-1][0].shape[0]
-                    ss = plan["block_sumsq"][sg.first_block_global + b0: sg.first_block_global + b1]
-                    newton_schulz_batched(sg.m_arena[b0:b1], out=sg.ortho[b0:b1], block_sumsq=ss,
-                                          backend=self.ns_backend, max_batch=self.ns_max_batch)
-                    self._mark("newton_schulz")
-                    segs = (_lib.UpdateSeg * len(run))()
-                    for k, (p, pb0) in enumerate(run):
-                        if not p.data.is_contiguous():
-                            raise ValueError("Muon parameters must be contiguous")
-                        segs[k].weight = p.data.data_ptr()
+                segs = sl["upd"]
+                if segs is None:
+                    segs = sl["upd"] = (_lib.UpdateSeg * len(sl["items"]))()
+                    for k, (p, pb0) in enumerate(sl["items"]):
                         segs[k].ortho = sg.ortho[pb0:pb0 + p.shape[0]].data_ptr()
                         segs[k].numel = p.numel()
-                    _lib.check(lib.mmb_muon_update(segs, len(run), _lib.dtype_code(sg.dtype), alpha,
-                                                   _lib.stream_ptr()), "muon_update")
-                    self._mark("update")
+                for k, (p, _) in enumerate(sl["items"]):
+                    if not p.data.is_contiguous():
+                        raise ValueError("Muon parameters must be contiguous")
+                    segs[k].weight = p.data.data_ptr()
+                _lib.check(lib.mmb_muon_update(segs, len(sl["items"]), _lib.dtype_code(sg.dtype), alpha,
+                                               _lib.stream_ptr()), "muon_update")
+                self._mark("update")
+
+    # ------------------------------------------------- gradients from the host
+    def _copy_stream(self, dev):
+        st = self._copy_streams.get(dev)
+        if st is None:
+            st = self._copy_streams[dev] = torch.cuda.Stream(device=dev)
+        return st
+
+    def _device_grad(self, p, h):
+        if h.shape != p.shape:
+            raise ValueError("host gradient shape differs from its parameter")
+        if p.grad is None or p.grad.dtype != h.dtype or not p.grad.is_contiguous():
+            p.grad = torch.empty(p.shape, dtype=h.dtype, device=p.device)
+        return p.grad
+
+    def _enqueue_host_copies(self, slices, host, dev):
+        """Queue every slice's host-to-device gradient copies on a side stream, one event per slice, so
+        the copy of slice i+1 runs while slice i is being computed."""
+        cs = self._copy_stream(dev)
+        cs.wait_stream(torch.cuda.current_stream())     # last step's kernels are done with the buffers
+        with torch.cuda.stream(cs):
+            for sl in slices:
+                for p, _ in sl["items"]:
+                    h = host.get(id(p))
+                    if h is not None:
+                        self._device_grad(p, h).copy_(h, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(cs)
+                sl["event"] = ev
 
     # ----------------------------------------------------------------- AdamW
     def _adamw_step(self, group, lr: float) -> None:
         beta1, beta2 = group["betas"]
         by_dtype: "OrderedDict[torch.dtype, list]" = OrderedDict()
+        host = self._host
+        if host is not None:
+            fed = [p for p in group["params"] if id(p) in host]
+            if fed:
+                dev = fed[0].device
+                _lib.require_cuda(fed[0])
+                with torch.cuda.device(dev):
+                    cs = self._copy_stream(dev)
+                    with torch.cuda.stream(cs):
+                        for p in fed:
+                            self._device_grad(p, host[id(p)]).copy_(host[id(p)], non_blocking=True)
+                    torch.cuda.current_stream().wait_stream(cs)
         for p in group["params"]:
-            if p.grad is None:
+            if p.grad is None or (host is not None and id(p) not in host):
                 continue
             _lib.require_cuda(p)
             state = self.state[p]

@@ -188,7 +188,7 @@ def test_fp8_absmax_momentum_bit_exact(mm, n, block, gdtype):
         assert torch.equal(d_codes.cpu(), codes), f"codes differ at step {step}"
         assert np.array_equal(d_scales.cpu().numpy().view(np.uint32), scales.numpy().view(np.uint32))
         assert torch.equal(d_m.cpu(), m16)
-        want_ss = m16.double().pow(2).view(nblk, -1).sum(1)
+        want_ss = m32.double().pow(2).view(nblk, -1).sum(1)
         assert torch.allclose(d_ss.cpu().double(), want_ss, rtol=1e-5)
 
 

@@ -265,3 +265,21 @@ def test_many_tensors_span_several_launch_tables():
         assert torch.equal(opt.state[p]["momentum_buffer"].cpu(), ref.state[id(r)]["momentum_buffer"])
     for p, r in zip(adamw, ref.adamw):
         assert relf(p.data, r) < 4e-3
+
+
+def test_step_fed_from_host_memory_equals_step_on_device_gradients():
+    opt_a, muon_a, adamw_a = _ours("bf16", state_format="fp8_absmax", ns_max_batch=2)
+    opt_b, muon_b, adamw_b = _ours("bf16", state_format="fp8_absmax", ns_max_batch=2)
+    for step in range(gi.OPT_STEPS):
+        mg, ag = gi.opt_grads("bf16", step)
+        _feed(muon_a, adamw_a, mg, ag)
+        opt_a.step()
+        host = [None if g is None else g.pin_memory() for g in mg + ag]
+        opt_b.step(host_grads=host)
+        opt_a.zero_grad(set_to_none=True)
+    torch.cuda.synchronize()
+    for a, b in zip(muon_a + adamw_a, muon_b + adamw_b):
+        assert torch.equal(a.data, b.data)
+    for a, b in zip(muon_a, muon_b):
+        assert torch.equal(opt_a.state[a]["momentum_buffer"].view(torch.uint8),
+                           opt_b.state[b]["momentum_buffer"].view(torch.uint8))
