@@ -49,6 +49,8 @@ extern "C" {
  * the reference's Triton build emits for `/`. */
 #define MMB_DIV_IEEE 0
 #define MMB_DIV_FULL 1
+#define MMB_DIV_IEEE_STRICT 2 /* IEEE results through the compiler's division everywhere: slower, same bits
+                                 as MMB_DIV_IEEE; exists to verify the fast exact quotient against */
 
 /* Newton-Schulz GEMM back ends */
 #define MMB_NS_TCGEN05 0 /* tcgen05.mma + TMEM + TMA (the product)             */

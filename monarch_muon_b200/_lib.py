@@ -16,7 +16,7 @@ from . import build as _build
 
 BF16, F32 = 0, 1
 STATE_FP8_ABSMAX, STATE_FP8_EXPAND, STATE_BF16, STATE_F32 = 0, 1, 2, 3
-DIV_IEEE, DIV_FULL = 0, 1
+DIV_IEEE, DIV_FULL, DIV_IEEE_STRICT = 0, 1, 2
 NS_TCGEN05, NS_SIMT = 0, 1
 GEMM_K, GEMM_MN, GEMM_SYM = 0, 1, 2
 

@@ -54,7 +54,7 @@ struct SegTable {
 // ---------------------------------------------------------------- arithmetic
 template <int DIV>
 __device__ __forceinline__ float fdiv(float a, float b) {
-  if (DIV == MMB_DIV_IEEE) return __fdiv_rn(a, b);
+  if (DIV != MMB_DIV_FULL) return __fdiv_rn(a, b);
   float r;
   asm("div.full.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
   return r;
@@ -62,7 +62,7 @@ __device__ __forceinline__ float fdiv(float a, float b) {
 
 template <int DIV>
 __device__ __forceinline__ float fsqrt(float a) {
-  if (DIV == MMB_DIV_IEEE) return __fsqrt_rn(a);
+  if (DIV != MMB_DIV_FULL) return __fsqrt_rn(a);
   float r;
   asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));
   return r;
@@ -278,20 +278,22 @@ __device__ __forceinline__ float raw_grad(const RawGroup<GradT>& r, int i) {
   return reinterpret_cast<const float*>(r.grad)[i];
 }
 
-// Quotient m / s rounded like IEEE division, at the cost of a multiply: with
-// r = rn(1/s), rn(m*r) is within one representable step of rn(m/s), so the two
-// give the same E4M3 code unless the product sits within two steps of a
-// rounding boundary of E4M3 (normal range: the dropped 20 mantissa bits equal
-// 0x80000) or falls into E4M3's subnormal range, where the exact division is
-// done instead.  Checked against IEEE division on 1.6e8 random cases.
-__device__ __forceinline__ float quotient_for_e4m3(float m, float s, float r) {
-  float q = __fmul_rn(m, r);
-  const uint32_t bits = __float_as_uint(q);
-  const uint32_t low = bits & 0xFFFFFu;
-  const bool near_tie = (low - 0x7FFFEu) <= 4u;                 // |low - 0x80000| <= 2
-  const bool small_or_special = ((bits >> 23) & 0xFFu) - 121u >= 134u;  // exponent < 121 (|q| < 2^-6) or 255
-  if (near_tie || small_or_special) q = __fdiv_rn(m, s);
-  return q;
+// m / s rounded like IEEE division in three instructions.  With r = rn(1/s) and
+// q0 = rn(m*r), the residual e = m - q0*s is exact in one fused multiply-add and
+// rn(q0 + e*r) is the correctly rounded quotient (Markstein's correction step,
+// the core of the compiler's own division), provided s is finite, its mantissa
+// is not all ones and nothing underflows.  The caller checks s once per group
+// (`markstein_ok`); an element so small that the residual could underflow has a
+// quotient below 2^-27, far under half of E4M3's smallest subnormal, and is
+// encoded as a signed zero by any approximation.
+__device__ __forceinline__ bool markstein_ok(float s) {
+  const uint32_t b = __float_as_uint(s);
+  return (b & 0x7F800000u) != 0x7F800000u && (b & 0x007FFFFFu) != 0x007FFFFFu;
+}
+__device__ __forceinline__ float quotient_markstein(float m, float s, float r) {
+  const float q0 = __fmul_rn(m, r);
+  const float e = __fmaf_rn(-q0, s, m);
+  return __fmaf_rn(e, r, q0);
 }
 
 // -------------------------------------------------------------- fused kernel
@@ -366,10 +368,10 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
         const float s_new = fdiv<DIV>(__fadd_rn(amax, 1e-20f), 448.0f);
         if (cur_ok) {
           float q[ELEMS_PER_LANE];
-          if (DIV == MMB_DIV_IEEE) {
+          if (DIV == MMB_DIV_IEEE && markstein_ok(s_new)) {   // uniform over the group
             const float r = __frcp_rn(s_new);
 #pragma unroll
-            for (int i = 0; i < ELEMS_PER_LANE; ++i) q[i] = quotient_for_e4m3(m[i], s_new, r);
+            for (int i = 0; i < ELEMS_PER_LANE; ++i) q[i] = quotient_markstein(m[i], s_new, r);
           } else {
 #pragma unroll
             for (int i = 0; i < ELEMS_PER_LANE; ++i) q[i] = fdiv<DIV>(m[i], s_new);
@@ -607,11 +609,13 @@ void launch_momentum(int div_mode, bool all_fast, const SegTable& tab, int grid,
   if (FORMAT == MMB_STATE_FP8_ABSMAX && all_fast) {
     if (div_mode == MMB_DIV_IEEE)
       momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_IEEE, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
+    else if (div_mode == MMB_DIV_IEEE_STRICT)
+      momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_IEEE_STRICT, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
     else
       momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_FULL, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
     return;
   }
-  if (div_mode == MMB_DIV_IEEE)
+  if (div_mode != MMB_DIV_FULL)
     momentum_kernel<FORMAT, GradT, MMB_DIV_IEEE, false><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
   else
     momentum_kernel<FORMAT, GradT, MMB_DIV_FULL, false><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
@@ -645,7 +649,7 @@ int momentum_step_impl(const mmb_momentum_seg* segs, int nseg, int grad_dtype, i
   MMB_REQUIRE(grad_dtype == MMB_BF16 || grad_dtype == MMB_F32, "mmb_momentum_step: grad_dtype %d", grad_dtype);
   MMB_REQUIRE(state_format >= MMB_STATE_FP8_ABSMAX && state_format <= MMB_STATE_F32,
               "mmb_momentum_step: state_format %d", state_format);
-  MMB_REQUIRE(div_mode == MMB_DIV_IEEE || div_mode == MMB_DIV_FULL, "mmb_momentum_step: div_mode %d", div_mode);
+  MMB_REQUIRE(div_mode >= MMB_DIV_IEEE && div_mode <= MMB_DIV_IEEE_STRICT, "mmb_momentum_step: div_mode %d", div_mode);
   if (nseg == 0) return MMB_OK;
   const int64_t need = mmb_momentum_scratch_floats(segs, nseg);
   if (block_sumsq_dev != nullptr)

@@ -239,3 +239,35 @@ def test_standalone_codecs(mm, codec, signed):
         nz = v != 0
         assert relf(back.cpu()[nz], v[nz]) < 0.08 and relf(want[nz], v[nz]) < 0.08
         assert torch.all(back.cpu()[~nz] == 0)
+
+
+def test_fast_exact_quotient_equals_compiler_division_on_many_elements(mm):
+    """MMB_DIV_IEEE forms m/s with a reciprocal and one correction step; it must give the bits of the
+    compiler's IEEE division (MMB_DIV_IEEE_STRICT) - here on 2^28 elements over a wide range of group
+    scales, including groups whose scale has an all-ones mantissa, infinities and zeros."""
+    n = 1 << 28
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    g = torch.empty(n, device="cuda").normal_(0, 1, generator=gen)
+    g *= torch.pow(10.0, torch.empty(n // 128, device="cuda").uniform_(-12, 4, generator=gen)).repeat_interleave(128)
+    g[:128] = 0.0
+    # a group whose new scale (absmax + 1e-20)/448 has an all-ones mantissa (the correction step's one
+    # exception): search the neighbourhood of 448 * 1.9999999 for such an absmax
+    import numpy as np
+    top = np.array([0x3FFFFFFF], dtype=np.uint32).view(np.float32)[0]
+    near = (np.array([np.float32(top * np.float32(448.0))]).view(np.uint32)[0]
+            + np.arange(-2000, 2000)).astype(np.uint32).view(np.float32)
+    sc = ((near + np.float32(1e-20)) / np.float32(448.0)).astype(np.float32)
+    hit = near[(sc.view(np.uint32) & 0x7FFFFF) == 0x7FFFFF]
+    assert hit.size > 0
+    g[128:256] *= 1e-3
+    g[128] = float(hit[0])
+    g[256] = float("inf")                      # fp32 gradients keep these exact values
+    out = []
+    for mode in (mm["lib"].DIV_IEEE, mm["lib"].DIV_IEEE_STRICT):
+        codes = torch.zeros(n, dtype=torch.uint8, device="cuda")
+        scales = torch.zeros(n // 128, device="cuda")
+        for _ in range(2):
+            mm["fp8"].fp8_momentum_flat(codes, scales, g, 0.95, div_mode=mode)
+        out.append((codes, scales))
+    assert torch.equal(out[0][0], out[1][0])
+    assert torch.equal(out[0][1].view(torch.int32), out[1][1].view(torch.int32))
