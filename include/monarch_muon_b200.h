@@ -163,6 +163,9 @@ int mmb_newton_schulz(const void* x_dev, void* out_dev, const float* block_sumsq
  *                 blocks on or above the block diagonal are read
  * sym_out != 0: D is symmetric and only those blocks of it are written.
  * sigma_b = inv_norm[b]^sigma_pow (sigma_pow 0: 1). */
+/* Diagnostic: CTAs (pair = 0) or two-CTA clusters (pair = 1) of the 256-wide
+ * GEMM kernel that fit on the current device at once. */
+int mmb_gemm_occupancy(int pair, int* out);
 #define MMB_GEMM_K 0
 #define MMB_GEMM_MN 1
 #define MMB_GEMM_SYM 2

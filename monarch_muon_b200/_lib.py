@@ -50,6 +50,7 @@ SYMBOLS = {
     "mmb_fp8_dequantize": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _vp]),
     "mmb_ns_workspace_bytes": (_i64, [_i, _i, _i]),
     "mmb_newton_schulz": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i64, _i, _vp, _vp]),
+    "mmb_gemm_occupancy": (_i, [_i, C.POINTER(C.c_int)]),
     "mmb_gemm_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _i, _i, _vp, _vp]),
     "mmb_muon_update": (_i, [C.POINTER(UpdateSeg), _i, _i, _f, _vp]),
     "mmb_adamw_step": (_i, [C.POINTER(AdamWSeg), _i, _i, _f, _f, _f, _f, _f, _vp]),

@@ -23,5 +23,6 @@ struct GemmCall {
 
 int gemm_tcgen05(const GemmCall& g, int32_t* status, cudaStream_t st);
 int gemm_simt(const GemmCall& g, cudaStream_t st);
+int gemm_occupancy(int pair, int* out);
 
 }  // namespace mmb

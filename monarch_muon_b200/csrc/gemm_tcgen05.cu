@@ -21,20 +21,29 @@
 // square form, so every GEMM of the iteration is "scale, add a constant on the
 // diagonal, round to bf16".
 //
-// CTA = 192 threads, persistent over output tiles of 128 x BN:
-//   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads per
-//               64-deep K slice into a ring of STAGES buffers (128-byte
-//               swizzle), arming the stage's mbarrier with the byte count.
-//               No cluster multicast anywhere.
+// CTA = 416 threads, persistent over output tiles of 128 x BN:
+//   warps 0,10-12  TMA producers (two for the A tile, two for the B tile, taking
+//               K slices in turn): one lane each issues cp.async.bulk.tensor
+//               loads into a ring of STAGES buffers (128-byte swizzle), arming
+//               the stage's mbarrier with its byte count.  No cluster multicast.
 //   warp 1      MMA issuer: one lane issues four tcgen05.mma (K=16 each) per
 //               stage into one of two TMEM accumulators (128 lanes x BN fp32
 //               columns each); tcgen05.commit frees the stage, and after the
 //               last K slice hands the accumulator to the epilogue.
-//   warps 2-5   epilogue: tcgen05.ld 64 columns at a time, scale, add the
-//               diagonal, round to bf16, write a swizzled 128 x 64 chunk to one
-//               of two staging buffers, one thread issues the TMA store.  The
+//   warps 2-9   epilogue: each warp takes 32 rows x 64 columns at a time
+//               (tcgen05.ld), scales, adds the diagonal, rounds to bf16, writes a
+//               swizzled piece into its own 4 KiB staging buffer and issues its
+//               own TMA store - no barrier couples the epilogue warps.  The
 //               second accumulator lets this overlap the next tile's main loop;
 //               TMA clips rows/columns beyond M/N, so ragged edges need no masks.
+//
+// PAIR variant (used when M > 128 and N > 128): two CTAs of a cluster share one
+// 256 x 256 tile through tcgen05.mma cta_group::2.  Each CTA loads 128 rows of A
+// and 128 rows of B per K slice (32 KiB instead of 48 KiB per SM and K slice,
+// so a third less operand traffic from L2, and six stages instead of four);
+// the even CTA issues the MMAs for both, each CTA drains its own 128 x 256 half
+// of the accumulator.  Loads are plain per-CTA TMA loads (cta_group::2 only so
+// that the peer's loads can signal the issuing CTA's barrier) - no multicast.
 //
 // Every mbarrier wait is bounded (about two seconds of wall clock): on expiry
 // the waiting role stores a code in the device status word, raises a CTA-wide
@@ -42,29 +51,38 @@
 // bulk copies land, frees its TMEM and returns.  Nothing traps.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "gemm.cuh"
 
 namespace mmb {
 namespace tc {
 
+
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_EPI_WARPS = 8;
+constexpr int PRODUCERS_PER_OPERAND = 2;         // producer warps per operand, taking K slices in turn
+constexpr int FIRST_EXTRA_PRODUCER = 2 + NUM_EPI_WARPS;  // warp 0 is a producer too
+constexpr int NUM_THREADS = 32 * (2 + NUM_EPI_WARPS + 2 * PRODUCERS_PER_OPERAND - 1);
 constexpr int A_TILE_BYTES = BM * BK * 2;
 constexpr int CHUNK_BYTES = 64 * BK * 2;      // one 64-wide MN-major chunk (8 KiB)
-constexpr int EPI_CHUNK_BYTES = BM * 64 * 2;  // 128 rows x 64 columns of bf16 output (16 KiB)
+constexpr int EPI_WARP_BYTES = 32 * 64 * 2;   // one epilogue warp's staging buffer: 32 rows x 64 columns of bf16
+constexpr int EPI_BYTES = NUM_EPI_WARPS * EPI_WARP_BYTES;
 constexpr int SYM_SHIFT = 8;                  // symmetric storage granularity: 256
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;
 
-template <int BN>
+template <int BN, bool PAIR>
 struct Cfg {
-  static constexpr int B_TILE_BYTES = BN * BK * 2;
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;  // rows of B this CTA stages
+  static constexpr int B_TILE_BYTES = B_ROWS * BK * 2;
   static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 7);
+  static constexpr int STAGES = PAIR ? 6 : (BN == 256 ? 4 : (BN == 128 ? 6 : 7));
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * EPI_CHUNK_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int TILE_M = PAIR ? 2 * BM : BM;   // rows of the output tile (both CTAs of a pair)
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 struct GemmArgs {
@@ -107,17 +125,48 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return done;
 }
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `addr` (a shared::cta address) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Relaxed on purpose: the arrival only announces bytes; the data itself is ordered by the bulk copy's
+// complete_tx.  A release here would make the producer wait for its own loads in flight and collapse
+// the pipeline to one stage.
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.relaxed.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
 // Bounded wait.  Returns false when the CTA is aborting (this wait expired or
-// another role's did).
+// another role's did).  The fast path is a bare try_wait loop: the clock is
+// only consulted every 256 unsuccessful polls (each poll already suspends the
+// thread for a while), because reading a timer on every miss sits on the
+// critical path of each producer/consumer hand-off.  The limit is counted in SM
+// cycles (clock64): 4e9 cycles is about two seconds at 2 GHz.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
                                           int32_t code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
+  long long t0 = 0;
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 63u) == 0u) {
+    if ((spin & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > WAIT_LIMIT_CYCLES) {
         *abort_flag = 1;
         if (status != nullptr) atomicCAS(status, 0, code);
         return false;
@@ -131,20 +180,43 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// Same load issued by a CTA of a pair: the data lands in this CTA's shared memory, the byte count is
+// signalled to `cluster_bar`, which may live in the peer CTA.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c0, int c1,
+                                                 int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
                ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
                : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {  // arrives on `bar` in both CTAs of the pair
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(mask)
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                     uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 __device__ __forceinline__ void tcgen05_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                                 uint32_t accumulate) {
@@ -189,10 +261,10 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, bool k_major) 
 // Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B.
 //   bits 4-5 D format (1 = f32); 7-9 A format (1 = bf16); 10-12 B format;
 //   bit 15 / 16: A / B is MN-major; bits 17-22 N>>3; bits 24-28 M>>4.
-template <int BN>
+template <int BN, int MMA_M>
 __device__ __forceinline__ uint32_t make_idesc(bool a_kmajor, bool b_kmajor) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((a_kmajor ? 0u : 1u) << 15) | ((b_kmajor ? 0u : 1u) << 16) |
-         (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+         (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(MMA_M >> 4) << 24);
 }
 
 // Is the operand tile with first row r0 and first k k0 fetched K-major?
@@ -200,169 +272,224 @@ __device__ __forceinline__ bool fetch_kmajor(int mode, int r0, int k0) {
   return mode == GEMM_K || (mode == GEMM_SYM && (r0 >> SYM_SHIFT) <= (k0 >> SYM_SHIFT));
 }
 
-// Tile t of the launch -> batch, first row, first column.  With sym_out only
-// tiles with (n0 >> 8) >= (m0 >> 8) exist: tile rows come in pairs p (rows 2p,
-// 2p+1) that own the column tiles p .. tiles_n-1.
-template <int BN>
+// Tile t of the launch -> batch, first row, first column.  Tiles are TILE_M rows
+// by BN columns.  With sym_out only tiles with (n0 >> 8) >= (m0 >> 8) exist:
+// the tile rows of 256-block p own the column tiles p .. tiles_n-1.
+template <int BN, int TILE_M>
 __device__ __forceinline__ void tile_coords(long long t, const GemmArgs& a, int& b, int& m0, int& n0) {
   b = static_cast<int>(t / a.tiles_per_batch);
   int r = static_cast<int>(t - static_cast<long long>(b) * a.tiles_per_batch);
   if (a.sym_out && BN == 256) {
+    constexpr int ROWS_PER_BLOCK = 256 / TILE_M;  // tile rows per 256-block: 2 (single CTA) or 1 (pair)
     int p = 0;
     for (;; ++p) {
-      const int rows = (a.tiles_m - 2 * p) >= 2 ? 2 : 1;
+      const int rows = (a.tiles_m - ROWS_PER_BLOCK * p) >= ROWS_PER_BLOCK ? ROWS_PER_BLOCK : 1;
       const int cnt = rows * (a.tiles_n - p);
       if (r < cnt) break;
       r -= cnt;
     }
     const int w = a.tiles_n - p;
     const int hi = r >= w ? 1 : 0;
-    m0 = (2 * p + hi) * BM;
+    m0 = (ROWS_PER_BLOCK * p + hi) * TILE_M;
     n0 = (p + r - hi * w) * BN;
   } else {
-    m0 = (r / a.tiles_n) * BM;
+    m0 = (r / a.tiles_n) * TILE_M;
     n0 = (r % a.tiles_n) * BN;
   }
 }
 
 // -------------------------------------------------------------------- kernel
-template <int BN>
+template <int BN, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__ CUtensorMap map_a_mn,
             const __grid_constant__ CUtensorMap map_b_k, const __grid_constant__ CUtensorMap map_b_mn,
             const __grid_constant__ CUtensorMap map_d, const GemmArgs args) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, PAIR>;
   constexpr int STAGES = C::STAGES;
+  constexpr int TILE_M = C::TILE_M;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
   uint8_t* tiles_ptr = smem_raw + (tiles_addr - raw_addr);
-  const uint32_t epi_addr = tiles_addr + STAGES * C::STAGE_BYTES;  // two 16 KiB output chunks
+  const uint32_t epi_addr = tiles_addr + STAGES * C::STAGE_BYTES;  // one 4 KiB staging buffer per epilogue warp
   uint8_t* epi_ptr = tiles_ptr + STAGES * C::STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_ptr + 2 * EPI_CHUNK_BYTES);
-  const uint32_t bars_addr = epi_addr + 2 * EPI_CHUNK_BYTES;
-  const uint32_t full_bar = bars_addr;                      // STAGES
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_ptr + EPI_BYTES);
+  const uint32_t bars_addr = epi_addr + EPI_BYTES;
+  const uint32_t full_bar = bars_addr;                      // STAGES (pair: only the even CTA's are used)
   const uint32_t empty_bar = bars_addr + 8 * STAGES;        // STAGES
   const uint32_t tmem_full_bar = bars_addr + 16 * STAGES;   // 2
-  const uint32_t tmem_empty_bar = tmem_full_bar + 16;       // 2
+  const uint32_t tmem_empty_bar = tmem_full_bar + 16;       // 2 (pair: only the even CTA's are used)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_k_tiles = (args.K + BK - 1) / BK;
+  // In a pair the even CTA of the cluster issues the MMAs; each CTA owns rows
+  // [128*cta_rank, +128) of the tile for A and for the output, and the same
+  // rows of the B tile.
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  const long long first_tile = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+  const long long tile_step = PAIR ? (gridDim.x >> 1) : gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(full_bar + 8 * s, PAIR ? 4 : 2);  // one expect-tx arrival per producer warp (of both CTAs)
       mbar_init(empty_bar + 8 * s, 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(tmem_full_bar + 8 * i, 1);
-      mbar_init(tmem_empty_bar + 8 * i, 4);  // one arrival per epilogue warp
+      mbar_init(tmem_empty_bar + 8 * i, (PAIR ? 2 : 1) * NUM_EPI_WARPS);  // one arrival per epilogue warp (of both CTAs)
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"(static_cast<uint32_t>(C::TMEM_COLS))
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                   "r"(static_cast<uint32_t>(C::TMEM_COLS))
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                   "r"(static_cast<uint32_t>(C::TMEM_COLS))
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tcgen05_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync();  // the peer's barriers exist before anything is signalled across
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
-    // ------------------------------------------------------- TMA producer
+  if (warp == 0 || warp >= FIRST_EXTRA_PRODUCER) {
+    // ------------------------------------------------------ TMA producers
+    // Issuing a bulk tensor copy keeps the issuing thread busy for several hundred cycles, so one
+    // thread cannot feed a 64-deep K slice per 512 cycles of MMA work.  2 x PRODUCERS_PER_OPERAND warps
+    // share the job: producer p of an operand loads that operand's tile for the K slices whose running
+    // number is congruent to p, and arms the stage's barrier with its own byte count.
+    const int pid = warp == 0 ? 0 : warp - FIRST_EXTRA_PRODUCER + 1;  // 0 .. 2*PRODUCERS_PER_OPERAND-1
+    const bool is_a = (pid & 1) == 0;
+    const uint32_t turn = static_cast<uint32_t>(pid >> 1);
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
+      uint32_t slice = 0;  // running number of the K slice over all tiles of this CTA
       bool ok = true;
-      for (long long t = blockIdx.x; ok && t < args.total_tiles; t += gridDim.x) {
+      const int mode = is_a ? args.a_mode : args.b_mode;
+      const int chunks = is_a ? BM / 64 : C::B_ROWS / 64;
+      const uint32_t bytes = is_a ? A_TILE_BYTES : C::B_TILE_BYTES;
+      const CUtensorMap* map_k = is_a ? &map_a_k : &map_b_k;
+      const CUtensorMap* map_mn = is_a ? &map_a_mn : &map_b_mn;
+      for (long long t = first_tile; ok && t < args.total_tiles; t += tile_step) {
         int b, m0, n0;
-        tile_coords<BN>(t, args, b, m0, n0);
-        for (int kt = 0; kt < num_k_tiles; ++kt) {
+        tile_coords<BN, TILE_M>(t, args, b, m0, n0);
+        const int r_tile = is_a ? m0 : n0;                       // decides K-major vs mirrored fetch
+        const int r_cta = is_a ? m0 + static_cast<int>(cta_rank) * BM : n0 + static_cast<int>(cta_rank) * C::B_ROWS;
+        for (int kt = 0; kt < num_k_tiles; ++kt, ++slice) {
+          if (slice % PRODUCERS_PER_OPERAND != turn) continue;
+          const uint32_t stage = slice % STAGES;
+          const uint32_t phase = (slice / STAGES) & 1u;
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, args.status, STATUS_WAIT_PRODUCER_EMPTY)) {
             ok = false;
             break;
           }
-          const uint32_t fb = full_bar + 8 * stage;
-          mbar_expect_tx(fb, C::STAGE_BYTES);
-          const uint32_t sa = tiles_addr + stage * C::STAGE_BYTES;
-          const uint32_t sb = sa + A_TILE_BYTES;
+          const uint32_t dst = tiles_addr + stage * C::STAGE_BYTES + (is_a ? 0 : A_TILE_BYTES);
           const int k0 = kt * BK;
-          if (fetch_kmajor(args.a_mode, m0, k0)) {
-            tma_load_3d(sa, &map_a_k, fb, k0, m0, b);
+          const bool kmajor = fetch_kmajor(mode, r_tile, k0);
+          if (PAIR) {
+            const uint32_t fb = mapa(full_bar + 8 * stage, 0);  // the even CTA's barrier
+            mbar_expect_tx_cluster(fb, bytes);
+            if (kmajor) {
+              tma_load_3d_pair(dst, map_k, fb, k0, r_cta, b);
+            } else {
+              for (int c = 0; c < chunks; ++c) tma_load_3d_pair(dst + c * CHUNK_BYTES, map_mn, fb, r_cta + 64 * c, k0, b);
+            }
           } else {
-#pragma unroll
-            for (int c = 0; c < BM / 64; ++c) tma_load_3d(sa + c * CHUNK_BYTES, &map_a_mn, fb, m0 + 64 * c, k0, b);
+            const uint32_t fb = full_bar + 8 * stage;
+            mbar_expect_tx(fb, bytes);
+            if (kmajor) {
+              tma_load_3d(dst, map_k, fb, k0, r_cta, b);
+            } else {
+              for (int c = 0; c < chunks; ++c) tma_load_3d(dst + c * CHUNK_BYTES, map_mn, fb, r_cta + 64 * c, k0, b);
+            }
           }
-          if (fetch_kmajor(args.b_mode, n0, k0)) {
-            tma_load_3d(sb, &map_b_k, fb, k0, n0, b);
-          } else {
-#pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * CHUNK_BYTES, &map_b_mn, fb, n0 + 64 * c, k0, b);
-          }
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     // --------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // One thread issues everything; each tcgen05.mma costs it on the order of a hundred cycles, so the
+    // loop body is kept to the wait, four MMAs and the commit.
+    if (lane == 0 && cta_rank == 0) {
       constexpr uint32_t K_STEP = (UMMA_K * 2) >> 4;     // K-major: 32 bytes per K=16, in 16-byte units
       constexpr uint32_t MN_STEP = (UMMA_K * 128) >> 4;  // MN-major: 16 rows of 128 bytes
+      const bool a_fixed = args.a_mode != GEMM_SYM, b_fixed = args.b_mode != GEMM_SYM;
       uint32_t stage = 0, phase = 0;
       uint32_t local = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; ok && t < args.total_tiles; t += gridDim.x, ++local) {
+      for (long long t = first_tile; ok && t < args.total_tiles; t += tile_step, ++local) {
         int b, m0, n0;
-        tile_coords<BN>(t, args, b, m0, n0);
+        tile_coords<BN, TILE_M>(t, args, b, m0, n0);
         const uint32_t acc = local & 1u;
         const uint32_t acc_phase = (local >> 1) & 1u;
         if (!mbar_wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, args.status, STATUS_WAIT_MMA_TMEM_EMPTY)) {
           ok = false;
           break;
         }
-        tcgen05_fence_after();
+        tcgen05_fence_after();  // the epilogue's reads of this accumulator are ordered before the overwrite
         const uint32_t d_tmem = tmem_base + acc * BN;
+        bool ak = args.a_mode == GEMM_K, bk = args.b_mode == GEMM_K;
+        uint32_t accumulate = 0;
         for (int kt = 0; kt < num_k_tiles; ++kt) {
+          if (!a_fixed) ak = fetch_kmajor(GEMM_SYM, m0, kt * BK);
+          if (!b_fixed) bk = fetch_kmajor(GEMM_SYM, n0, kt * BK);
+          const uint32_t sa = tiles_addr + stage * C::STAGE_BYTES;
+          const uint64_t adesc = make_desc(sa, ak);
+          const uint64_t bdesc = make_desc(sa + A_TILE_BYTES, bk);
+          const uint32_t idesc = make_idesc<BN, TILE_M>(ak, bk);
+          const uint32_t a_step = ak ? K_STEP : MN_STEP;
+          const uint32_t b_step = bk ? K_STEP : MN_STEP;
           if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, args.status, STATUS_WAIT_MMA_FULL)) {
             ok = false;
             break;
           }
-          tcgen05_fence_after();
-          const int k0 = kt * BK;
-          const bool ak = fetch_kmajor(args.a_mode, m0, k0);
-          const bool bk = fetch_kmajor(args.b_mode, n0, k0);
-          const uint32_t sa = tiles_addr + stage * C::STAGE_BYTES;
-          const uint64_t adesc = make_desc(sa, ak);
-          const uint64_t bdesc = make_desc(sa + A_TILE_BYTES, bk);
-          const uint32_t idesc = make_idesc<BN>(ak, bk);
-          const uint32_t a_step = ak ? K_STEP : MN_STEP;
-          const uint32_t b_step = bk ? K_STEP : MN_STEP;
+          if (PAIR) {
+            tcgen05_mma_f16_pair(d_tmem, adesc, bdesc, idesc, accumulate);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            tcgen05_mma_f16(d_tmem, adesc + k * a_step, bdesc + k * b_step, idesc, (kt > 0 || k > 0) ? 1u : 0u);
-          tcgen05_commit(empty_bar + 8 * stage);  // frees the stage once these MMAs have read it
+            for (int k = 1; k < BK / UMMA_K; ++k) tcgen05_mma_f16_pair(d_tmem, adesc + k * a_step, bdesc + k * b_step, idesc, 1u);
+            tcgen05_commit_pair(empty_bar + 8 * stage);  // frees the stage in both CTAs once these MMAs have read it
+          } else {
+            tcgen05_mma_f16(d_tmem, adesc, bdesc, idesc, accumulate);
+#pragma unroll
+            for (int k = 1; k < BK / UMMA_K; ++k) tcgen05_mma_f16(d_tmem, adesc + k * a_step, bdesc + k * b_step, idesc, 1u);
+            tcgen05_commit(empty_bar + 8 * stage);
+          }
+          accumulate = 1u;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) tcgen05_commit(tmem_full_bar + 8 * acc);  // accumulator complete
+        if (ok) {  // accumulator complete
+          if (PAIR) tcgen05_commit_pair(tmem_full_bar + 8 * acc); else tcgen05_commit(tmem_full_bar + 8 * acc);
+        }
       }
     }
   } else {
     // ------------------------------------------------------------ epilogue
-    const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32) are this warp's
+    // Eight warps: warp w may touch TMEM lanes [32*(w%4), +32) only, so two warps share each quarter of
+    // the rows and split the 64-column chunks between them (even / odd).  Every warp works alone: it
+    // stages its 32 x 64 piece in its own buffer and issues its own TMA store, so no barrier couples
+    // the warps and a store's latency is hidden behind the other warps' work.
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    const int half = ew >> 2;
     const int row_in_tile = quarter * 32 + lane;
-    const bool elected = threadIdx.x == 64;  // warp 2, lane 0 issues and tracks the TMA stores
+    uint8_t* my_buf = epi_ptr + ew * EPI_WARP_BYTES;
+    const uint32_t my_buf_addr = epi_addr + ew * EPI_WARP_BYTES;
     uint32_t local = 0;
-    uint32_t chunk_no = 0;  // running count of stored chunks: selects the staging buffer
     bool ok = true;
-    for (long long t = blockIdx.x; ok && t < args.total_tiles; t += gridDim.x, ++local) {
+    for (long long t = first_tile; ok && t < args.total_tiles; t += tile_step, ++local) {
       int b, m0, n0;
-      tile_coords<BN>(t, args, b, m0, n0);
+      tile_coords<BN, TILE_M>(t, args, b, m0, n0);
+      m0 += static_cast<int>(cta_rank) * BM;  // this CTA's half of a pair tile
       const uint32_t acc = local & 1u;
       const uint32_t acc_phase = (local >> 1) & 1u;
       if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag, args.status, STATUS_WAIT_EPI_TMEM_FULL)) {
@@ -376,27 +503,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
         sigma = args.sigma_pow == 2 ? s * s : s;
       }
       const float scale = sigma * args.alpha;
-      const int row = m0 + row_in_tile;
+      const int row0 = m0 + quarter * 32;  // first row of this warp's piece
+      const int row = row0 + lane;
       const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 64; ++c) {
+      for (int c = half; c < BN / 64; c += 2) {
         const int col0 = n0 + c * 64;
-        if (col0 >= args.N) break;  // uniform across the CTA
-        const uint32_t buf = chunk_no & 1u;
-        ++chunk_no;
-        if (elected) bulk_wait_read_1();  // the store issued from this buffer two chunks ago has been read
-        epilogue_bar();
+        if (col0 >= args.N || row0 >= args.M) break;  // uniform across the warp
         uint32_t v[64];
         tcgen05_ld_32x32b_x32(t_base + c * 64, v);
         tcgen05_ld_32x32b_x32(t_base + c * 64 + 32, v + 32);
         tcgen05_wait_ld();
-        // diagonal element of this row, if it falls inside the chunk
-        const int dcol = row - col0;
-        uint8_t* rowp = epi_ptr + buf * EPI_CHUNK_BYTES + row_in_tile * 128;
+        const int dcol = row - col0;  // column of this row's diagonal element inside the chunk, if any
+        uint4 ov[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-          uint4 ov;
-          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ov);
+          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ov[q]);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int e = 8 * q + 2 * i;
@@ -406,21 +528,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
             if (e + 1 == dcol) x1 += args.diag;
             oh[i] = __floats2bfloat162_rn(x0, x1);
           }
-          // 128-byte swizzle: 16-byte unit q of row r lives at unit q ^ (r & 7)
-          *reinterpret_cast<uint4*>(rowp + ((q ^ (row_in_tile & 7)) << 4)) = ov;
         }
+        if (lane == 0) bulk_wait_read_0();  // this warp's previous store has left the buffer
+        __syncwarp();
+        // 128-byte swizzle: 16-byte unit q of row r lives at unit q ^ (r & 7)
+        uint8_t* rowp = my_buf + lane * 128;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) << 4)) = ov[q];
         fence_proxy_async_smem();
-        epilogue_bar();
-        if (elected) {
-          tma_store_3d(&map_d, epi_addr + buf * EPI_CHUNK_BYTES, col0, m0, b);
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_3d(&map_d, my_buf_addr, col0, row0, b);
           bulk_commit();
         }
       }
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tmem_empty_bar + 8 * acc);
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(mapa(tmem_empty_bar + 8 * acc, 0)); else mbar_arrive(tmem_empty_bar + 8 * acc);
+      }
     }
-    if (elected) bulk_wait_all();
+    if (lane == 0) bulk_wait_all();
   }
 
   // ------------------------------------------------------------- teardown
@@ -431,12 +559,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
   }
+  if (PAIR) cluster_sync();  // neither CTA leaves (or frees TMEM) while its peer may still signal or write to it
   if (warp == 1) {
     __syncwarp();
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(static_cast<uint32_t>(C::TMEM_COLS))
-                 : "memory");
+    if (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"(static_cast<uint32_t>(C::TMEM_COLS))
+                   : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"(static_cast<uint32_t>(C::TMEM_COLS))
+                   : "memory");
   }
 }
 
@@ -495,17 +629,60 @@ int operand_maps(CUtensorMap* k_map, CUtensorMap* mn_map, const void* base, int 
   return MMB_OK;
 }
 
-template <int BN>
+template <int BN, bool PAIR>
 int launch(const CUtensorMap* maps, const GemmArgs& args, int grid, cudaStream_t st) {
-  auto kern = gemm_kernel<BN>;
-  MMB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES));
-  kern<<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], args);
-  MMB_CUDA_CHECK(cudaGetLastError());
+  auto kern = gemm_kernel<BN, PAIR>;
+  constexpr int smem = Cfg<BN, PAIR>::SMEM_BYTES;
+  MMB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MMB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[2], maps[3], maps[4], args));
   count_launch();
   return MMB_OK;
 }
 
 }  // namespace tc
+
+int gemm_trace_read(long long* host) {  // DEV TRACE
+  return MMB_OK;
+}
+
+// How many CTAs (single) or clusters (pair) of the 256-wide kernel the device can hold at once.
+int gemm_occupancy(int pair, int* out) {
+  using namespace tc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(pair ? 2 * 74 : 148, 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = pair ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (pair) {
+    cfg.dynamicSmemBytes = Cfg<256, true>::SMEM_BYTES;
+    MMB_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Cfg<256, true>::SMEM_BYTES));
+    MMB_CUDA_CHECK(cudaOccupancyMaxActiveClusters(out, gemm_kernel<256, true>, &cfg));
+  } else {
+    cfg.dynamicSmemBytes = Cfg<256, false>::SMEM_BYTES;
+    MMB_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Cfg<256, false>::SMEM_BYTES));
+    MMB_CUDA_CHECK(cudaOccupancyMaxActiveClusters(out, gemm_kernel<256, false>, &cfg));
+  }
+  return MMB_OK;
+}
 
 int gemm_tcgen05(const GemmCall& g, int32_t* status, cudaStream_t st) {
   using namespace tc;
@@ -516,19 +693,28 @@ int gemm_tcgen05(const GemmCall& g, int32_t* status, cudaStream_t st) {
   if (g.b_mode == GEMM_SYM) MMB_REQUIRE(g.N == g.K, "symmetric B operand must be square (N == K)");
   if (g.sym_out) MMB_REQUIRE(g.M == g.N, "symmetric output must be square");
   const int bn = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
+  // two CTAs per 256 x 256 tile when the problem has at least two tile rows of 128
+  static const bool pair_allowed = [] {
+    const char* e = getenv("MMB_GEMM_PAIR");
+    return e == nullptr || e[0] != '0';
+  }();
+  const bool pair = pair_allowed && bn == 256 && g.M > BM;
+  const int tile_m = pair ? 2 * BM : BM;
   CUtensorMap maps[5];
   int rc;
   if ((rc = operand_maps(&maps[0], &maps[1], g.a, g.batch, g.M, g.K, g.a_mode, BM)) != MMB_OK) return rc;
-  if ((rc = operand_maps(&maps[2], &maps[3], g.b, g.batch, g.N, g.K, g.b_mode, bn)) != MMB_OK) return rc;
-  if ((rc = make_map(&maps[4], g.d, g.batch, g.M, g.N, BM)) != MMB_OK) return rc;
+  if ((rc = operand_maps(&maps[2], &maps[3], g.b, g.batch, g.N, g.K, g.b_mode, pair ? bn / 2 : bn)) != MMB_OK) return rc;
+  if ((rc = make_map(&maps[4], g.d, g.batch, g.M, g.N, 32)) != MMB_OK) return rc;  // one epilogue warp's piece
   GemmArgs args;
   args.M = g.M; args.N = g.N; args.K = g.K; args.batch = g.batch;
-  args.tiles_m = (g.M + BM - 1) / BM;
+  args.tiles_m = (g.M + tile_m - 1) / tile_m;
   args.tiles_n = (g.N + bn - 1) / bn;
   args.sym_out = (g.sym_out && bn == 256) ? 1 : 0;
   if (args.sym_out) {
+    const int rows_per_block = 256 / tile_m;
     int cnt = 0;
-    for (int p = 0; 2 * p < args.tiles_m; ++p) cnt += ((args.tiles_m - 2 * p) >= 2 ? 2 : 1) * (args.tiles_n - p);
+    for (int p = 0; rows_per_block * p < args.tiles_m; ++p)
+      cnt += ((args.tiles_m - rows_per_block * p) >= rows_per_block ? rows_per_block : 1) * (args.tiles_n - p);
     args.tiles_per_batch = cnt;
   } else {
     args.tiles_per_batch = args.tiles_m * args.tiles_n;
@@ -540,11 +726,16 @@ int gemm_tcgen05(const GemmCall& g, int32_t* status, cudaStream_t st) {
   args.status = status;
   const int sms = sm_count();
   if (sms <= 0) return fail(MMB_ERR_CUDA, "tcgen05 GEMM: no CUDA device");
+  if (args.total_tiles == 0) return MMB_OK;
+  if (pair) {
+    const long long pairs = sms / 2;
+    const int grid = 2 * static_cast<int>(args.total_tiles < pairs ? args.total_tiles : pairs);
+    return launch<256, true>(maps, args, grid, st);
+  }
   const int grid = static_cast<int>(args.total_tiles < sms ? args.total_tiles : sms);
-  if (grid == 0) return MMB_OK;
-  if (bn == 256) return launch<256>(maps, args, grid, st);
-  if (bn == 128) return launch<128>(maps, args, grid, st);
-  return launch<64>(maps, args, grid, st);
+  if (bn == 256) return launch<256, false>(maps, args, grid, st);
+  if (bn == 128) return launch<128, false>(maps, args, grid, st);
+  return launch<64, false>(maps, args, grid, st);
 }
 
 }  // namespace mmb

@@ -192,6 +192,8 @@ NsLayout ns_layout(int batch, int rows, int cols) {
 
 extern "C" {
 
+int mmb_gemm_occupancy(int pair, int* out) { return mmb::gemm_occupancy(pair, out); }
+
 int64_t mmb_ns_workspace_bytes(int batch, int rows, int cols) {
   if (batch <= 0 || rows <= 0 || cols <= 0) return 0;
   return static_cast<int64_t>(mmb::ns_layout(batch, rows, cols).total);
