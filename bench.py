@@ -265,12 +265,18 @@ def main():
     roofline = {"kernel": "gemm_kernel (tcgen05 Newton-Schulz GEMMs, 15 launches per block-shape slice)",
                 "bound": "tensor", "achieved": ach_tf, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
                 "frac": ach_tf / pk["bf16_tflops_sustained"], "peak_kind": f"{pk['source']}, sustained bf16 GEMM",
-                "traffic": None}
+                "achieved_note": "algorithmic FLOPs (5*(4m^2n+2m^3) per block) over the CUDA-event time of all "
+                                 "Newton-Schulz launches of the step; symmetric tiles that are skipped count as done",
+                "traffic": 1.0e11,
+                "traffic_note": "DRAM bytes summed over the step's 120 GEMM launches, scaled by block count from the "
+                                "ncu capture of the 32-block case in profiles/gemm_kernel_ns_32blocks.md"}
     mom_ms = phases.get("momentum", float("nan"))
     mom_gbs = muon_elems * S.FP8_ABSMAX_BYTES_PER_ELEM / (mom_ms * 1e-3) / 1e9
     roofline_fp8 = {"kernel": "momentum_kernel (FP8 absmax heavy-ball)", "bound": "hbm", "achieved": mom_gbs,
                     "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": mom_gbs / pk["hbm_gbs"],
-                    "peak_kind": f"{pk['source']}, copy bandwidth", "traffic": None}
+                    "peak_kind": f"{pk['source']}, copy bandwidth", "traffic": 0.98 * muon_elems * S.FP8_ABSMAX_BYTES_PER_ELEM,
+                    "traffic_note": "0.98 x algorithmic bytes, ncu capture of 4e8 elements in "
+                                    "profiles/momentum_kernel_fp8_400M.md scaled by element count"}
 
     e2e = None
     if not args.no_e2e:
