@@ -58,6 +58,9 @@ extern "C" {
 
 int mmb_version(void);
 const char* mmb_last_error(void);
+/* Size every kernel's grid for at most n SMs (0 = all).  Leaving a few SMs
+ * free lets communication kernels (NCCL) run beside the persistent GEMMs. */
+int mmb_set_sm_limit(int n);
 /* Kernels launched by this library in this process so far. */
 int64_t mmb_launch_count(void);
 

@@ -42,6 +42,7 @@ SYMBOLS = {
     "mmb_version": (_i, []),
     "mmb_last_error": (C.c_char_p, []),
     "mmb_launch_count": (_i64, []),
+    "mmb_set_sm_limit": (_i, [_i]),
     "mmb_momentum_scratch_floats": (_i64, [C.POINTER(MomentumSeg), _i]),
     "mmb_momentum_step": (_i, [C.POINTER(MomentumSeg), _i, _i, _i, _i, _f, _f, _i, _vp, _vp, _i64, _vp]),
     "mmb_momentum_static_max_floats": (_i64, []),
@@ -137,3 +138,8 @@ def read_status(device: torch.device, reset: bool = True) -> int:
 def launch_count() -> int:
     """Kernels launched by the library in this process so far."""
     return int(load().mmb_launch_count())
+
+
+def set_sm_limit(n: int) -> None:
+    """Size kernel grids for at most n SMs (0 = all)."""
+    load().mmb_set_sm_limit(int(n))

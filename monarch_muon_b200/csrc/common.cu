@@ -23,6 +23,9 @@ static std::atomic<long long> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 long long launches() { return g_launches.load(std::memory_order_relaxed); }
 
+static std::atomic<int> g_sm_limit{0};
+void set_sm_limit(int n) { g_sm_limit.store(n < 0 ? 0 : n, std::memory_order_relaxed); }
+
 int sm_count() {
   static thread_local int cached_dev = -1;
   static thread_local int cached_sms = 0;
@@ -34,6 +37,8 @@ int sm_count() {
     cached_dev = dev;
     cached_sms = sms;
   }
+  const int limit = g_sm_limit.load(std::memory_order_relaxed);
+  if (limit > 0 && limit < cached_sms) return limit;
   return cached_sms;
 }
 
@@ -42,6 +47,11 @@ int sm_count() {
 extern "C" {
 
 int mmb_version(void) { return 100; }
+
+int mmb_set_sm_limit(int n) {
+  mmb::set_sm_limit(n);
+  return MMB_OK;
+}
 
 int64_t mmb_launch_count(void) { return mmb::launches(); }
 

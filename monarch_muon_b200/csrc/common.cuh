@@ -32,8 +32,10 @@ int fail(int code, const char* fmt, ...);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Number of SMs of the current device (cached per device).
+// Number of SMs kernels may size their grids for: the device's count, or the limit set with
+// mmb_set_sm_limit() if that is smaller.
 int sm_count();
+void set_sm_limit(int n);
 
 // Process-wide count of kernels this library has launched (mmb_launch_count()).
 void count_launch(int n = 1);

@@ -25,7 +25,7 @@
 //   warps 0,10-12  TMA producers (two for the A tile, two for the B tile, taking
 //               K slices in turn): one lane each issues cp.async.bulk.tensor
 //               loads into a ring of STAGES buffers (128-byte swizzle), arming
-//               the stage's mbarrier with its byte count.  No cluster multicast.
+//               the stage's mbarrier with its byte count.  Each CTA loads its own data.
 //   warp 1      MMA issuer: one lane issues four tcgen05.mma (K=16 each) per
 //               stage into one of two TMEM accumulators (128 lanes x BN fp32
 //               columns each); tcgen05.commit frees the stage, and after the
@@ -43,7 +43,8 @@
 // so a third less operand traffic from L2, and six stages instead of four);
 // the even CTA issues the MMAs for both, each CTA drains its own 128 x 256 half
 // of the accumulator.  Loads are plain per-CTA TMA loads (cta_group::2 only so
-// that the peer's loads can signal the issuing CTA's barrier) - no multicast.
+// that the peer's loads can signal the issuing CTA's barrier); each CTA
+// fetches its own operands, nothing is broadcast across the cluster.
 //
 // Every mbarrier wait is bounded (about two seconds of wall clock): on expiry
 // the waiting role stores a code in the device status word, raises a CTA-wide

@@ -46,12 +46,14 @@ class ShardedMonarchMuon:
     average : divide the reduced gradient by the world size (DDP semantics).
     local_factory(muon_params, adamw_params, **hyper) : builds the optimizer
         that steps the owned views; defaults to MonarchMuonOptimizer (CUDA).
+    comm_sms : SMs kept free of this library's kernels during the step, for the
+        collectives' kernels.
     """
 
     def __init__(self, muon_params, adamw_params, *, process_group=None, lr: float = 5e-3, momentum: float = 0.95,
                  adamw_betas=(0.9, 0.95), adamw_weight_decay: float = 0.1, adamw_eps: float = 1e-8,
                  n_chunks: int = 4, average: bool = True, local_factory=None, second_group: bool = True,
-                 **local_kwargs):
+                 comm_sms: int = 0, **local_kwargs):
         if not dist.is_initialized():
             raise RuntimeError("ShardedMonarchMuon needs an initialised torch.distributed process group")
         self.group = process_group
@@ -75,6 +77,9 @@ class ShardedMonarchMuon:
         self.plan = partition.make_plan([tuple(p.shape) for p in self.muon_params],
                                         [p.numel() for p in self.adamw_params], self.world, n_chunks)
         self.average = average
+        # SMs left free during the step so that NCCL's kernels can run beside the persistent GEMMs
+        # (which otherwise occupy every SM and serialise with them)
+        self.comm_sms = comm_sms
         n = self.plan.total_elems
         self.w_arena = torch.zeros(n, dtype=self.dtype, device=self.device)
         self.g_arena = torch.zeros(n, dtype=self.dtype, device=self.device)
@@ -162,6 +167,10 @@ class ShardedMonarchMuon:
     @torch.no_grad()
     def step(self):
         nchunks = len(self.plan.chunks)
+        if self.comm_sms > 0 and self.backend == "nccl":
+            from . import _lib
+            total = torch.cuda.get_device_properties(self.device).multi_processor_count
+            _lib.set_sm_limit(max(2, total - self.comm_sms))
         rs = []
         for k in range(nchunks):
             g_whole, g_mine, _, _ = self.chunk_views(k)
@@ -188,6 +197,9 @@ class ShardedMonarchMuon:
             ag.append(self._all_gather(w_whole, w_mine))
         for w in ag:
             w.wait()
+        if self.comm_sms > 0 and self.backend == "nccl":
+            from . import _lib
+            _lib.set_sm_limit(0)
 
     def zero_grad(self, set_to_none: bool = False):
         """Gradients are arena views and stay allocated; they are zeroed in place."""
