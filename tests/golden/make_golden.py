@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 The reference modules are loaded by file path (both optimizer twins are called
 models.monarch.monarch_muon upstream, so they get distinct module names here).
@@ -127,7 +127,9 @@ def make_coat(ref_root, out):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference-checkout")
+    ref_root = sys.argv[1]
     pre = _load("ref_pretrain_monarch_muon",
                 os.path.join(ref_root, "pretrain/src/models/monarch/monarch_muon.py"))
     mem = _load("ref_membench_monarch_muon",
