@@ -174,18 +174,20 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         shapes: "OrderedDict[tuple, _ShapeGroup]" = OrderedDict()
         for p in params:
             _lib.require_cuda(p)
-            if p.dim() != 3:
-                raise ValueError("Muon parameters must be 3-D (nblocks, rows, cols) Monarch factors")
+            if p.dim() not in (2, 3):
+                raise ValueError("Muon parameters must be 3-D (nblocks, rows, cols) Monarch factors "
+                                 "or 2-D matrices (treated as one block)")
             if p.device != dev:
                 raise ValueError("all Muon parameters must live on one device")
             _lib.dtype_code(p.dtype)
-            key = (p.dtype, p.shape[1], p.shape[2])
+            nb, rows, cols = self._blocks_of(p)
+            key = (p.dtype, rows, cols)
             sg = shapes.get(key)
             if sg is None:
                 sg = shapes[key] = _ShapeGroup(*key)
             sg.params.append(p)
             sg.block_start.append(sg.nblocks)
-            sg.nblocks += p.shape[0]
+            sg.nblocks += nb
         plan = {"device": dev, "shapes": shapes, "params": list(params), "entry": {}}
         total_blocks = 0
         mplan = fp8_state.MomentumPlan(dev)
@@ -210,19 +212,19 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                     sg.sqrt_mm = torch.ones(ngroups, dtype=torch.float32, device=dev)
             g_at = 0
             for p, b0 in zip(sg.params, sg.block_start):
-                nb = p.shape[0]
-                m_view = sg.m_arena[b0:b0 + nb]
+                nb = self._blocks_of(p)[0]
+                m_view = sg.m_arena[b0:b0 + nb].view(p.shape)
                 ng = fp8_state.groups_of(p.numel())
                 views = {}
                 if self._fp8():
-                    state_t = sg.codes[b0:b0 + nb]
+                    state_t = sg.codes[b0:b0 + nb].view(p.shape)
                     views["momentum_buffer"] = state_t.view(torch.float8_e4m3fn)
                     views["scale_momentum_buffer"] = sg.scale[g_at:g_at + ng]
                     if sg.expand is not None:
                         views["expand_momentum_buffer"] = sg.expand[g_at:g_at + ng]
                         views["sqrt_minmax_momentum_buffer"] = sg.sqrt_mm[g_at:g_at + ng]
                 elif sg.fp32_state is not None:
-                    state_t = sg.fp32_state[b0:b0 + nb]
+                    state_t = sg.fp32_state[b0:b0 + nb].view(p.shape)
                     views["momentum_buffer"] = state_t
                 else:
                     state_t = m_view
@@ -240,6 +242,12 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         plan["scratch"] = None
         plan["slices"] = {}
         return plan
+
+    @staticmethod
+    def _blocks_of(p):
+        """(nblocks, rows, cols) of a Muon parameter; a 2-D matrix is one block (the reference's
+        fine-tuning optimizer applies the same update to dense matrices, finetune/sft_optimizer.py:40-50)."""
+        return (p.shape[0], p.shape[1], p.shape[2]) if p.dim() == 3 else (1, p.shape[0], p.shape[1])
 
     def _plan_for(self, group):
         plan = self._plans.get(id(group))
@@ -274,7 +282,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                 if id(p) not in live_ids:
                     cur = None
                     continue
-                nb = p.shape[0]
+                nb = self._blocks_of(p)[0]
                 if cur is None or cur["b1"] - cur["b0"] + nb > cap:
                     cur = {"sg": sg, "items": [], "b0": b0, "b1": b0, "tables": {}, "upd": None, "event": None}
                     slices.append(cur)
@@ -346,7 +354,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                 if segs is None:
                     segs = sl["upd"] = (_lib.UpdateSeg * len(sl["items"]))()
                     for k, (p, pb0) in enumerate(sl["items"]):
-                        segs[k].ortho = sg.ortho[pb0:pb0 + p.shape[0]].data_ptr()
+                        segs[k].ortho = sg.ortho[pb0:].data_ptr()
                         segs[k].numel = p.numel()
                 for k, (p, _) in enumerate(sl["items"]):
                     if not p.data.is_contiguous():

@@ -237,7 +237,7 @@ def test_optimizer_protocol_hooks_scheduler_and_errors():
     with pytest.raises(RuntimeError):
         MonarchMuonOptimizer(cpu, []).step()
     with pytest.raises(ValueError):
-        bad = torch.nn.Parameter(torch.zeros(8, 8, device="cuda"))
+        bad = torch.nn.Parameter(torch.zeros(2, 2, 8, 8, device="cuda"))
         bad.grad = torch.zeros_like(bad)
         MonarchMuonOptimizer([bad], []).step()
 
@@ -283,3 +283,25 @@ def test_step_fed_from_host_memory_equals_step_on_device_gradients():
     for a, b in zip(muon_a, muon_b):
         assert torch.equal(opt_a.state[a]["momentum_buffer"].view(torch.uint8),
                            opt_b.state[b]["momentum_buffer"].view(torch.uint8))
+
+
+def test_dense_2d_matrices_take_the_muon_update_as_single_blocks():
+    """The reference's fine-tuning optimizer applies the same Newton-Schulz update to plain 2-D weight
+    matrices (finetune/sft_optimizer.py:40-50); here a 2-D Muon parameter is one block."""
+    from monarch_muon_b200 import MonarchMuonOptimizer
+    from oracle import muon_oracle
+    gen = torch.Generator().manual_seed(21)
+    w2 = (0.02 * torch.randn(256, 384, generator=gen)).bfloat16()
+    w3 = (0.02 * torch.randn(2, 256, 384, generator=gen)).bfloat16()
+    g2 = (1e-3 * torch.randn(256, 384, generator=gen)).bfloat16()
+    g3 = (1e-3 * torch.randn(2, 256, 384, generator=gen)).bfloat16()
+    p2, p3 = torch.nn.Parameter(w2.cuda()), torch.nn.Parameter(w3.cuda())
+    opt = MonarchMuonOptimizer([p2, p3], [], lr=0.02)
+    p2.grad, p3.grad = g2.cuda(), g3.cuda()
+    opt.step()
+    assert opt.state[p2]["momentum_buffer"].shape == p2.shape
+    o2 = muon_oracle.newton_schulz(g2[None])[0]
+    want = w2.float() - 0.02 * (256 / 384) ** 0.5 * o2.float()
+    assert relf(p2.data, want) < TOL_W
+    o3 = muon_oracle.newton_schulz(g3)
+    assert relf(p3.data, w3.float() - 0.02 * (256 / 384) ** 0.5 * o3.float()) < TOL_W
