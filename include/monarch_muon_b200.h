@@ -66,7 +66,7 @@ int64_t mmb_launch_count(void);
 
 /* ------------------------------------------------------------------------
  * Heavy-ball momentum with optimizer-state codec, fused:
- *   dequantise -> m = beta*m (rounded) -> m = m + grad_scale*g (rounded)
+ *   dequantise -> m = beta*m (rounded) -> m = m + round_gradtype(grad_scale*g) (rounded)
  *   -> requantise; also writes bf16(m) for Newton-Schulz and the per-block
  *   sum of squares of m.
  * Replaces: momentum update   pretrain/src/models/monarch/monarch_muon.py:146-148
@@ -208,6 +208,29 @@ typedef struct mmb_adamw_seg {
 
 int mmb_adamw_step(const mmb_adamw_seg* segs, int nseg, int dtype, float lr, float beta1, float beta2,
                    float weight_decay, float eps, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Global gradient norm and clip coefficient, computed on the device with no
+ * host round trip.  Replaces torch.nn.utils.clip_grad_norm_ in the training
+ * loop (pretrain/src/optim/base.py:121-122: the norm's .item() is a host sync,
+ * and the in-place scaling of every gradient is two more passes over them).
+ *   out_dev[0] = ||all gradients||_2, out_dev[1] = min(1, max_norm/(norm+1e-6)).
+ * mmb_set_device_grad_scale(&out_dev[1]) then makes the following
+ * mmb_momentum_step / mmb_adamw_step calls of this thread multiply every
+ * gradient by that device scalar as they read it (NULL switches it off), so the
+ * gradients themselves are never rewritten.
+ * ---------------------------------------------------------------------- */
+typedef struct mmb_grad_seg {
+  const void* grad; /* device */
+  int64_t numel;
+  int32_t dtype;    /* MMB_BF16 or MMB_F32 */
+  int32_t pad_;
+} mmb_grad_seg;
+
+int64_t mmb_grad_norm_scratch_floats(void);
+int mmb_grad_norm_clip(const mmb_grad_seg* segs, int nseg, float max_norm, float* out_dev,
+                       float* scratch_dev, int64_t scratch_floats, void* stream);
+int mmb_set_device_grad_scale(const float* scale_dev);
 
 /* ------------------------------------------------------------------------
  * Device status word.  Kernels never trap: a bounded wait that expires or a

@@ -31,6 +31,10 @@ class UpdateSeg(C.Structure):
     _fields_ = [("weight", C.c_void_p), ("ortho", C.c_void_p), ("numel", C.c_int64)]
 
 
+class GradSeg(C.Structure):
+    _fields_ = [("grad", C.c_void_p), ("numel", C.c_int64), ("dtype", C.c_int32), ("pad_", C.c_int32)]
+
+
 class AdamWSeg(C.Structure):
     _fields_ = [("param", C.c_void_p), ("grad", C.c_void_p), ("exp_avg", C.c_void_p), ("exp_avg_sq", C.c_void_p),
                 ("numel", C.c_int64), ("step", C.c_int32), ("pad_", C.c_int32)]
@@ -55,6 +59,9 @@ SYMBOLS = {
     "mmb_gemm_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _i, _i, _vp, _vp]),
     "mmb_muon_update": (_i, [C.POINTER(UpdateSeg), _i, _i, _f, _vp]),
     "mmb_adamw_step": (_i, [C.POINTER(AdamWSeg), _i, _i, _f, _f, _f, _f, _f, _vp]),
+    "mmb_grad_norm_scratch_floats": (_i64, []),
+    "mmb_grad_norm_clip": (_i, [C.POINTER(GradSeg), _i, _f, _vp, _vp, _i64, _vp]),
+    "mmb_set_device_grad_scale": (_i, [_vp]),
     "mmb_device_status_create": (_i, [C.POINTER(_vp)]),
     "mmb_device_status_destroy": (_i, [_vp]),
     "mmb_device_status_read": (_i, [_vp, C.POINTER(C.c_int32), _i, _vp]),

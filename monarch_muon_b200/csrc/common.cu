@@ -23,6 +23,10 @@ static std::atomic<long long> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 long long launches() { return g_launches.load(std::memory_order_relaxed); }
 
+static thread_local const float* t_grad_scale = nullptr;
+const float* device_grad_scale() { return t_grad_scale; }
+void set_device_grad_scale(const float* p) { t_grad_scale = p; }
+
 static std::atomic<int> g_sm_limit{0};
 void set_sm_limit(int n) { g_sm_limit.store(n < 0 ? 0 : n, std::memory_order_relaxed); }
 
@@ -47,6 +51,11 @@ int sm_count() {
 extern "C" {
 
 int mmb_version(void) { return 100; }
+
+int mmb_set_device_grad_scale(const float* scale_dev) {
+  mmb::set_device_grad_scale(scale_dev);
+  return MMB_OK;
+}
 
 int mmb_set_sm_limit(int n) {
   mmb::set_sm_limit(n);

@@ -37,6 +37,11 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 int sm_count();
 void set_sm_limit(int n);
 
+// Device scalar that the momentum and AdamW kernels multiply gradients by (mmb_set_device_grad_scale),
+// or null.  Thread local, like the error message.
+const float* device_grad_scale();
+void set_device_grad_scale(const float* p);
+
 // Process-wide count of kernels this library has launched (mmb_launch_count()).
 void count_launch(int n = 1);
 

@@ -160,7 +160,8 @@ struct AdamTable {
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
 adamw_kernel(const __grid_constant__ AdamTable tab, float decay, float beta1, float one_m_beta1, float beta2,
-             float one_m_beta2, float eps) {
+             float one_m_beta2, float eps, const float* __restrict__ grad_scale_dev) {
+  const float gscale = grad_scale_dev != nullptr ? *grad_scale_dev : 1.0f;
   const long long total = tab.vec_start[tab.nseg];
   const long long stride = static_cast<long long>(gridDim.x) * THREADS;
   for (long long v = static_cast<long long>(blockIdx.x) * THREADS + threadIdx.x; v < total; v += stride) {
@@ -176,6 +177,10 @@ adamw_kernel(const __grid_constant__ AdamTable tab, float decay, float beta1, fl
     float p[VEC], g[VEC], m[VEC], q[VEC];
     load_vec<T>(pp, vec, n, p);
     load_vec<T>(static_cast<const T*>(sg.grad) + at, vec, n, g);
+    if (gscale != 1.0f) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) g[i] = rd<T>(__fmul_rn(g[i], gscale));  // like grad.mul_(coef) on the stored type
+    }
     load_vec<T>(mp, vec, n, m);
     load_vec<T>(vp, vec, n, q);
 #pragma unroll
@@ -195,6 +200,70 @@ adamw_kernel(const __grid_constant__ AdamTable tab, float decay, float beta1, fl
     store_vec<T>(pp, vec, n, p);
     store_vec<T>(mp, vec, n, m);
     store_vec<T>(vp, vec, n, q);
+  }
+}
+
+// ---- global gradient norm and clip coefficient, without a host round trip
+struct NormSeg {
+  const void* grad;
+  long long numel;
+  int vec_ok;
+  int pad_;
+};
+struct NormTable {
+  NormSeg seg[MAX_SEG];
+  long long vec_start[MAX_SEG + 1];
+  int nseg;
+};
+
+// One partial sum of squares per CTA (fixed assignment of vectors to threads, tree reduction: reproducible).
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+grad_sumsq_kernel(const __grid_constant__ NormTable tab, float* __restrict__ partials) {
+  __shared__ float warp_sums[THREADS / 32];
+  const long long total = tab.vec_start[tab.nseg];
+  const long long stride = static_cast<long long>(gridDim.x) * THREADS;
+  float acc = 0.0f;
+  for (long long v = static_cast<long long>(blockIdx.x) * THREADS + threadIdx.x; v < total; v += stride) {
+    const int s = find_segment(tab, v);
+    const NormSeg& sg = tab.seg[s];
+    const long long at = (v - tab.vec_start[s]) * VEC;
+    const long long rem = sg.numel - at;
+    const int n = rem >= VEC ? VEC : static_cast<int>(rem);
+    float g[VEC];
+    load_vec<T>(static_cast<const T*>(sg.grad) + at, sg.vec_ok && n == VEC, n, g);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc = fmaf(g[i], g[i], acc);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.0f;
+#pragma unroll
+    for (int i = 0; i < THREADS / 32; ++i) t += warp_sums[i];
+    partials[blockIdx.x] += t;  // partials are zeroed by the caller; several launches accumulate
+  }
+}
+
+// out[0] = sqrt(sum of partials), out[1] = min(1, max_norm / (out[0] + 1e-6))  (torch's clip_grad_norm_ rule)
+__global__ void __launch_bounds__(THREADS)
+clip_coef_kernel(const float* __restrict__ partials, int n, float max_norm, float* __restrict__ out) {
+  __shared__ float warp_sums[THREADS / 32];
+  float acc = 0.0f;
+  for (int i = threadIdx.x; i < n; i += THREADS) acc += partials[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.0f;
+#pragma unroll
+    for (int i = 0; i < THREADS / 32; ++i) t += warp_sums[i];
+    const float norm = __fsqrt_rn(t);
+    out[0] = norm;
+    out[1] = fminf(1.0f, __fdiv_rn(max_norm, __fadd_rn(norm, 1e-6f)));
   }
 }
 
@@ -245,6 +314,58 @@ int mmb_muon_update(const mmb_update_seg* segs, int nseg, int weight_dtype, floa
   return MMB_OK;
 }
 
+int64_t mmb_grad_norm_scratch_floats(void) {
+  const int sms = mmb::sm_count();
+  return static_cast<int64_t>(sms > 0 ? sms : 148) * 8 * 4;
+}
+
+int mmb_grad_norm_clip(const mmb_grad_seg* segs, int nseg, float max_norm, float* out_dev, float* scratch_dev,
+                       int64_t scratch_floats, void* stream) {
+  using namespace mmb;
+  MMB_REQUIRE(nseg >= 0 && (nseg == 0 || segs != nullptr), "mmb_grad_norm_clip: bad segment table");
+  MMB_REQUIRE(out_dev != nullptr && scratch_dev != nullptr, "mmb_grad_norm_clip: null output or scratch");
+  const int sms = sm_count();
+  if (sms <= 0) return fail(MMB_ERR_CUDA, "mmb_grad_norm_clip: no CUDA device");
+  const int max_grid = sms * 8 * 4;
+  MMB_REQUIRE(scratch_floats >= max_grid, "mmb_grad_norm_clip: scratch of %d floats needed, %lld given", max_grid,
+              (long long)scratch_floats);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MMB_CUDA_CHECK(cudaMemsetAsync(scratch_dev, 0, sizeof(float) * max_grid, st));
+  // one table per dtype run of at most MAX_SEG tensors
+  int base = 0;
+  while (base < nseg) {
+    const int dtype = segs[base].dtype;
+    MMB_REQUIRE(dtype == MMB_BF16 || dtype == MMB_F32, "mmb_grad_norm_clip: dtype %d", dtype);
+    NormTable tab;
+    tab.nseg = 0;
+    long long vecs = 0;
+    while (base < nseg && tab.nseg < MAX_SEG && segs[base].dtype == dtype) {
+      const mmb_grad_seg& s = segs[base];
+      MMB_REQUIRE(s.numel > 0 && s.grad != nullptr, "mmb_grad_norm_clip: segment %d empty", base);
+      NormSeg& d = tab.seg[tab.nseg];
+      d.grad = s.grad;
+      d.numel = s.numel;
+      d.vec_ok = aligned16(s.grad);
+      tab.vec_start[tab.nseg] = vecs;
+      vecs += (s.numel + VEC - 1) / VEC;
+      ++tab.nseg;
+      ++base;
+    }
+    tab.vec_start[tab.nseg] = vecs;
+    const int grid = grid_for(vecs, sms);
+    if (dtype == MMB_BF16)
+      grad_sumsq_kernel<__nv_bfloat16><<<grid, THREADS, 0, st>>>(tab, scratch_dev);
+    else
+      grad_sumsq_kernel<float><<<grid, THREADS, 0, st>>>(tab, scratch_dev);
+    MMB_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+  }
+  clip_coef_kernel<<<1, THREADS, 0, st>>>(scratch_dev, max_grid, max_norm, out_dev);
+  MMB_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return MMB_OK;
+}
+
 int mmb_adamw_step(const mmb_adamw_seg* segs, int nseg, int dtype, float lr, float beta1, float beta2,
                    float weight_decay, float eps, void* stream) {
   using namespace mmb;
@@ -287,9 +408,9 @@ int mmb_adamw_step(const mmb_adamw_seg* segs, int nseg, int dtype, float lr, flo
     const int grid = grid_for(vecs, sms);
     const float omb1 = static_cast<float>(1.0 - b1), omb2 = static_cast<float>(1.0 - b2);
     if (dtype == MMB_BF16)
-      adamw_kernel<__nv_bfloat16><<<grid, THREADS, 0, st>>>(tab, decay, beta1, omb1, beta2, omb2, eps);
+      adamw_kernel<__nv_bfloat16><<<grid, THREADS, 0, st>>>(tab, decay, beta1, omb1, beta2, omb2, eps, device_grad_scale());
     else
-      adamw_kernel<float><<<grid, THREADS, 0, st>>>(tab, decay, beta1, omb1, beta2, omb2, eps);
+      adamw_kernel<float><<<grid, THREADS, 0, st>>>(tab, decay, beta1, omb1, beta2, omb2, eps, device_grad_scale());
     MMB_CUDA_CHECK(cudaGetLastError());
   count_launch();
   }

@@ -302,7 +302,8 @@ __device__ __forceinline__ float quotient_markstein(float m, float s, float r) {
 template <int FORMAT, typename GradT, int DIV, bool ALL_FAST>
 __global__ void __launch_bounds__(THREADS, ALL_FAST ? 3 : 1)
 momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_scale, float expand_min,
-                float* __restrict__ partials) {
+                float* __restrict__ partials, const float* __restrict__ grad_scale_dev) {
+  if (grad_scale_dev != nullptr) grad_scale = __fmul_rn(grad_scale, *grad_scale_dev);  // e.g. a clip coefficient
   const int lane = threadIdx.x & 31;
   const int sub = lane & (LANES_PER_GROUP - 1);
   const int grp_in_warp = lane >> 3;
@@ -354,7 +355,10 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
 #pragma unroll
           for (int i = 0; i < ELEMS_PER_LANE; ++i) {
             float g = raw_grad<GradT>(cur, i);
-            if (scaled) g = __fmul_rn(g, grad_scale);
+            if (scaled) {  // like grad.mul_(scale) on the stored gradient: rounded to the gradient's type
+              g = __fmul_rn(g, grad_scale);
+              if (sizeof(GradT) == 2) g = bf16_round(g);
+            }
             float t = __fmul_rn(beta, __fmul_rn(m[i], cur.scale));
             t = __fadd_rn(t, g);
             m[i] = t;
@@ -441,6 +445,7 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
 #pragma unroll
       for (int i = 0; i < ELEMS_PER_LANE; ++i) {
         float gi_f = __fmul_rn(g[i], grad_scale);
+        if (sizeof(GradT) == 2 && grad_scale != 1.0f) gi_f = bf16_round(gi_f);  // as grad.mul_(scale) would leave it
         float t = __fmul_rn(beta, m[i]);
         if (FORMAT == MMB_STATE_BF16) t = bf16_round(t);
         t = __fadd_rn(t, gi_f);
@@ -608,17 +613,17 @@ void launch_momentum(int div_mode, bool all_fast, const SegTable& tab, int grid,
                      float expand_min, float* partials, cudaStream_t st) {
   if (FORMAT == MMB_STATE_FP8_ABSMAX && all_fast) {
     if (div_mode == MMB_DIV_IEEE)
-      momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_IEEE, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
+      momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_IEEE, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
     else if (div_mode == MMB_DIV_IEEE_STRICT)
-      momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_IEEE_STRICT, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
+      momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_IEEE_STRICT, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
     else
-      momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_FULL, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
+      momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_FULL, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
     return;
   }
   if (div_mode != MMB_DIV_FULL)
-    momentum_kernel<FORMAT, GradT, MMB_DIV_IEEE, false><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
+    momentum_kernel<FORMAT, GradT, MMB_DIV_IEEE, false><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
   else
-    momentum_kernel<FORMAT, GradT, MMB_DIV_FULL, false><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials);
+    momentum_kernel<FORMAT, GradT, MMB_DIV_FULL, false><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
 }
 
 template <typename GradT>

@@ -87,6 +87,8 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         self.grad_scale = 1.0            # multiplies Muon gradients inside the momentum kernel
         self._plans: dict = {}           # id(group) -> plan
         self._marks = None               # list of (phase, cuda event) while phase timing is on
+        self._clip_scratch = self._clip_out = None
+        self._clip_pending = False       # clip_grad_norm_ was called: the next step scales gradients on the device
         self._host = None                # {id(param): host gradient} during a step fed from host memory
         self._copy_streams: dict = {}
         _lib.load()                      # fail now, not at the first step, if the library is missing
@@ -107,6 +109,8 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
             with torch.enable_grad():
                 loss = closure()
         self._host = self._host_map(host_grads)
+        if self._clip_pending:
+            _lib.load().mmb_set_device_grad_scale(self._clip_out[1:].data_ptr())
         try:
             for group in self.param_groups:
                 lr = group["lr"]
@@ -115,6 +119,9 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                 else:
                     self._adamw_step(group, lr)
         finally:
+            if self._clip_pending:
+                _lib.load().mmb_set_device_grad_scale(None)
+                self._clip_pending = False
             if self._host is not None:
                 for plan in self._plans.values():          # events belong to this step only
                     if plan is not None:
@@ -156,6 +163,40 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         if self._marks is not None:
             self._marks = []
         return out
+
+    @torch.no_grad()
+    def clip_grad_norm_(self, max_norm: float) -> torch.Tensor:
+        """Global-norm gradient clipping fused into the next step().
+
+        Counterpart of torch.nn.utils.clip_grad_norm_(params, max_norm) as the reference's loop calls it
+        right before step() (pretrain/src/optim/base.py:121-123), without its host synchronisation and
+        without rewriting the gradients: one kernel pass computes the norm of all current gradients and
+        the clip coefficient min(1, max_norm / (norm + 1e-6)) on the device, and the next step() multiplies
+        every gradient by it as it is read.  Returns the total norm as a 0-dim device tensor."""
+        grads = [p.grad for g in self.param_groups for p in g["params"] if p.grad is not None]
+        if not grads:
+            return torch.zeros((), device="cuda")
+        _lib.require_cuda(*grads)
+        dev = grads[0].device
+        lib = _lib.load()
+        segs = (_lib.GradSeg * len(grads))()
+        keep = []
+        for k, g in enumerate(sorted(grads, key=lambda t: str(t.dtype))):    # one table run per dtype
+            if not g.is_contiguous():
+                g = g.contiguous()
+                keep.append(g)
+            segs[k].grad = g.data_ptr()
+            segs[k].numel = g.numel()
+            segs[k].dtype = _lib.dtype_code(g.dtype)
+        with torch.cuda.device(dev):
+            need = int(lib.mmb_grad_norm_scratch_floats())
+            if self._clip_scratch is None or self._clip_scratch.numel() < need or self._clip_scratch.device != dev:
+                self._clip_scratch = torch.empty(need, dtype=torch.float32, device=dev)
+                self._clip_out = torch.empty(2, dtype=torch.float32, device=dev)
+            _lib.check(lib.mmb_grad_norm_clip(segs, len(grads), float(max_norm), self._clip_out.data_ptr(),
+                                              self._clip_scratch.data_ptr(), need, _lib.stream_ptr()), "grad_norm_clip")
+        self._clip_pending = True
+        return self._clip_out[0]
 
     def block_sumsq(self, group_index: int = 0):
         """fp32 sums of squares of bf16(momentum) per block from the last step (device tensor)."""

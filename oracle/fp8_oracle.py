@@ -119,9 +119,12 @@ def absmax_momentum_step(codes_u8, scales, grad, beta: float, grad_scale: float 
     """
     m = absmax_dequant(codes_u8, scales)
     m = m * torch.tensor(beta, dtype=torch.float32)
-    g = grad.reshape(-1).to(torch.float32)
+    g = grad.reshape(-1)
     if grad_scale != 1.0:
-        g = g * torch.tensor(grad_scale, dtype=torch.float32)
+        # a scaled gradient is what grad.mul_(scale) leaves behind (clip_grad_norm_, DDP averaging):
+        # computed in fp32, rounded to the gradient's own dtype
+        g = (g.to(torch.float32) * torch.tensor(grad_scale, dtype=torch.float32)).to(grad.dtype)
+    g = g.to(torch.float32)
     m = m + g
     new_codes, new_scales = absmax_quant(m)
     return new_codes, new_scales, m, m.to(torch.bfloat16)

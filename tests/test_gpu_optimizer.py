@@ -305,3 +305,41 @@ def test_dense_2d_matrices_take_the_muon_update_as_single_blocks():
     assert relf(p2.data, want) < TOL_W
     o3 = muon_oracle.newton_schulz(g3)
     assert relf(p3.data, w3.float() - 0.02 * (256 / 384) ** 0.5 * o3.float()) < TOL_W
+
+
+@pytest.mark.parametrize("case", ["fp32", "bf16"])
+def test_fused_gradient_clipping_matches_clip_then_step(case):
+    """clip_grad_norm_ + step() must equal torch.nn.utils.clip_grad_norm_ followed by the oracle's step."""
+    from oracle import muon_oracle
+    ref, rmuon, radamw = _oracle(case)
+    opt, muon, adamw = _ours(case)
+    max_norm = 0.05                                   # the seeded gradients have a global norm of about 0.3
+    for step in range(2):
+        mg, ag = gi.opt_grads(case, step + 1)
+        _feed(muon, adamw, mg, ag)
+        cpu_params = [torch.nn.Parameter(t.clone()) for t in mg + ag]
+        for q, g in zip(cpu_params, mg + ag):
+            q.grad = g.clone()
+        want_norm = torch.nn.utils.clip_grad_norm_(cpu_params, max_norm)
+        clipped = [q.grad for q in cpu_params]
+        ref.step(clipped[:len(mg)], clipped[len(mg):])
+        got_norm = opt.clip_grad_norm_(max_norm)
+        opt.step()
+        assert float(got_norm) == pytest.approx(float(want_norm), rel=4e-3 if case == "bf16" else 1e-5)
+        assert float(want_norm) > max_norm            # the clip is active
+    # with bf16 gradients torch keeps the total norm and the coefficient in bf16 (up to 0.4 % off the
+    # fp32 value used here), which carries straight into the momentum
+    tol = 1e-6 if case == "fp32" else 1e-2
+    for p, r in zip(muon, rmuon):
+        assert relf(p.data, r) < TOL_W
+        assert relf(opt.state[p]["momentum_buffer"], ref.state[id(r)]["momentum_buffer"]) < tol
+    for p, r in zip(adamw, radamw):
+        assert relf(p.data, r) < tol
+    # without a new clip_grad_norm_ call the next step is unscaled again
+    mg, ag = gi.opt_grads(case, 2)
+    _feed(muon, adamw, mg, ag)
+    before = [opt.state[p]["momentum_buffer"].float().clone() for p in muon]
+    opt.step()
+    for p, b, g in zip(muon, before, mg):
+        want = (b.cpu() * 0.95).to(p.dtype).float() + g.float() if case == "bf16" else b.cpu() * 0.95 + g.float()
+        assert relf(opt.state[p]["momentum_buffer"], want.to(p.dtype)) < 1e-6
