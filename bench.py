@@ -194,7 +194,7 @@ def main():
                          "128+64+64 block set; fp8: isolated FP8 momentum kernel on a flat buffer")
     ap.add_argument("--ns-blocks", type=int, default=128, help="square blocks in --case ns (tall/wide get half each)")
     ap.add_argument("--fp8-elems", type=int, default=1_600_000_000)
-    ap.add_argument("--comm-sms", type=int, default=16, help="SMs left to NCCL during the sharded step")
+    ap.add_argument("--comm-sms", type=int, default=0, help="SMs left to NCCL during the sharded step")
     ap.add_argument("--chunks", type=int, default=4, help="pipeline chunks of the sharded (multi-GPU) step")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
