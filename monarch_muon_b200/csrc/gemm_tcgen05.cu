@@ -228,6 +228,31 @@ __device__ __forceinline__ void tcgen05_mma_f16(uint32_t d_tmem, uint64_t adesc,
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same instructions with the 64-bit shared-memory descriptors passed as (low, high) halves: only the low
+// half (start address) changes inside the K loop, so the issuing thread does 32-bit adds only.
+template <bool PAIR>
+__device__ __forceinline__ void tcgen05_mma_f16_split(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                      uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  if (PAIR) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
 __device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t* v) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -424,6 +449,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
     if (lane == 0 && cta_rank == 0) {
       constexpr uint32_t K_STEP = (UMMA_K * 2) >> 4;     // K-major: 32 bytes per K=16, in 16-byte units
       constexpr uint32_t MN_STEP = (UMMA_K * 128) >> 4;  // MN-major: 16 rows of 128 bytes
+      constexpr uint32_t LBO_MN = CHUNK_BYTES >> 4;
+      constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);  // bits 32-63 of make_desc()
+      constexpr uint32_t IDESC_BASE = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                      (static_cast<uint32_t>(TILE_M >> 4) << 24);
       const bool a_fixed = args.a_mode != GEMM_SYM, b_fixed = args.b_mode != GEMM_SYM;
       uint32_t stage = 0, phase = 0;
       uint32_t local = 0;
@@ -444,27 +473,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
         for (int kt = 0; kt < num_k_tiles; ++kt) {
           if (!a_fixed) ak = fetch_kmajor(GEMM_SYM, m0, kt * BK);
           if (!b_fixed) bk = fetch_kmajor(GEMM_SYM, n0, kt * BK);
-          const uint32_t sa = tiles_addr + stage * C::STAGE_BYTES;
-          const uint64_t adesc = make_desc(sa, ak);
-          const uint64_t bdesc = make_desc(sa + A_TILE_BYTES, bk);
-          const uint32_t idesc = make_idesc<BN, TILE_M>(ak, bk);
+          // descriptor halves (see make_desc): high = stride offset | version | swizzle, low = address | leading offset
+          const uint32_t sa = (tiles_addr + stage * C::STAGE_BYTES) >> 4;
+          const uint32_t a_lo = sa | ((ak ? 1u : LBO_MN) << 16);
+          const uint32_t b_lo = (sa + (A_TILE_BYTES >> 4)) | ((bk ? 1u : LBO_MN) << 16);
+          const uint32_t idesc = IDESC_BASE | ((ak ? 0u : 1u) << 15) | ((bk ? 0u : 1u) << 16);
           const uint32_t a_step = ak ? K_STEP : MN_STEP;
           const uint32_t b_step = bk ? K_STEP : MN_STEP;
           if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, args.status, STATUS_WAIT_MMA_FULL)) {
             ok = false;
             break;
           }
-          if (PAIR) {
-            tcgen05_mma_f16_pair(d_tmem, adesc, bdesc, idesc, accumulate);
+          tcgen05_mma_f16_split<PAIR>(d_tmem, a_lo, DESC_HI, b_lo, DESC_HI, idesc, accumulate);
 #pragma unroll
-            for (int k = 1; k < BK / UMMA_K; ++k) tcgen05_mma_f16_pair(d_tmem, adesc + k * a_step, bdesc + k * b_step, idesc, 1u);
-            tcgen05_commit_pair(empty_bar + 8 * stage);  // frees the stage in both CTAs once these MMAs have read it
-          } else {
-            tcgen05_mma_f16(d_tmem, adesc, bdesc, idesc, accumulate);
-#pragma unroll
-            for (int k = 1; k < BK / UMMA_K; ++k) tcgen05_mma_f16(d_tmem, adesc + k * a_step, bdesc + k * b_step, idesc, 1u);
-            tcgen05_commit(empty_bar + 8 * stage);
-          }
+          for (uint32_t k = 1; k < BK / UMMA_K; ++k)
+            tcgen05_mma_f16_split<PAIR>(d_tmem, a_lo + k * a_step, DESC_HI, b_lo + k * b_step, DESC_HI, idesc, 1u);
+          // frees the stage (in both CTAs of a pair) once these MMAs have read it
+          if (PAIR) tcgen05_commit_pair(empty_bar + 8 * stage); else tcgen05_commit(empty_bar + 8 * stage);
           accumulate = 1u;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
