@@ -196,6 +196,8 @@ def main():
     ap.add_argument("--fp8-elems", type=int, default=1_600_000_000)
     ap.add_argument("--comm-sms", type=int, default=0, help="SMs left to NCCL during the sharded step")
     ap.add_argument("--chunks", type=int, default=4, help="pipeline chunks of the sharded (multi-GPU) step")
+    ap.add_argument("--state-format", default="fp8_absmax", choices=["fp8_absmax", "fp8_expand", "param"],
+                    help="momentum state: FP8 absmax (headline), COAT range expansion, or the parameter dtype")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -233,7 +235,10 @@ def main():
 
     muon, adamw = build_workload(dev, args.nblocks)
     opt = MonarchMuonOptimizer(muon, adamw, lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95),
-                               adamw_weight_decay=0.1, adamw_eps=1e-8, state_format="fp8_absmax")
+                               adamw_weight_decay=0.1, adamw_eps=1e-8, state_format=args.state_format)
+    if args.state_format != "fp8_absmax":
+        config["workload"] = config["workload"].replace("FP8 E4M3 absmax momentum state",
+                                                        f"momentum state format {args.state_format}")
     flops, muon_elems, adamw_elems = workload_counts(args.nblocks)
     pk = peaks()
 
