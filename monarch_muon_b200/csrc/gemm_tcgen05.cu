@@ -101,11 +101,6 @@ struct GemmArgs {
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -210,26 +205,8 @@ __device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {  // arrives 
                ::"r"(bar), "h"(mask)
                : "memory");
 }
-__device__ __forceinline__ void tcgen05_mma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                                     uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                                uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Same instructions with the 64-bit shared-memory descriptors passed as (low, high) halves: only the low
-// half (start address) changes inside the K loop, so the issuing thread does 32-bit adds only.
+// tcgen05.mma kind::f16 with the 64-bit shared-memory descriptors passed as (low, high) halves: only the
+// low half (start address) changes inside the K loop, so the issuing thread does 32-bit adds only.
 template <bool PAIR>
 __device__ __forceinline__ void tcgen05_mma_f16_split(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
                                                       uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
@@ -267,7 +244,7 @@ __device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t* 
 }
 __device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle.
+// Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle (built in the MMA issue loop):
 //   bits  0-13  start address >> 4
 //   bits 16-29  leading-dimension byte offset >> 4
 //   bits 32-45  stride-dimension byte offset >> 4
@@ -278,20 +255,10 @@ __device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::
 // MN-major tile ([64 k][64 rows] chunks of 8 KiB): the 8-k groups of one
 // chunk are 1024 bytes apart (stride offset) and the 64-row chunks are 8 KiB
 // apart (leading offset).
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, bool k_major) {
-  const uint64_t lbo = k_major ? 1ull : static_cast<uint64_t>(CHUNK_BYTES >> 4);
-  const uint64_t sbo = 1024ull >> 4;
-  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (lbo << 16) | (sbo << 32) | (1ull << 46) | (2ull << 61);
-}
-
+//
 // Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B.
 //   bits 4-5 D format (1 = f32); 7-9 A format (1 = bf16); 10-12 B format;
 //   bit 15 / 16: A / B is MN-major; bits 17-22 N>>3; bits 24-28 M>>4.
-template <int BN, int MMA_M>
-__device__ __forceinline__ uint32_t make_idesc(bool a_kmajor, bool b_kmajor) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_kmajor ? 0u : 1u) << 15) | ((b_kmajor ? 0u : 1u) << 16) |
-         (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(MMA_M >> 4) << 24);
-}
 
 // Is the operand tile with first row r0 and first k k0 fetched K-major?
 __device__ __forceinline__ bool fetch_kmajor(int mode, int r0, int k0) {
@@ -450,7 +417,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
       constexpr uint32_t K_STEP = (UMMA_K * 2) >> 4;     // K-major: 32 bytes per K=16, in 16-byte units
       constexpr uint32_t MN_STEP = (UMMA_K * 128) >> 4;  // MN-major: 16 rows of 128 bytes
       constexpr uint32_t LBO_MN = CHUNK_BYTES >> 4;
-      constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);  // bits 32-63 of make_desc()
+      constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);  // bits 32-63 of the descriptor
       constexpr uint32_t IDESC_BASE = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
                                       (static_cast<uint32_t>(TILE_M >> 4) << 24);
       const bool a_fixed = args.a_mode != GEMM_SYM, b_fixed = args.b_mode != GEMM_SYM;
@@ -473,7 +440,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
         for (int kt = 0; kt < num_k_tiles; ++kt) {
           if (!a_fixed) ak = fetch_kmajor(GEMM_SYM, m0, kt * BK);
           if (!b_fixed) bk = fetch_kmajor(GEMM_SYM, n0, kt * BK);
-          // descriptor halves (see make_desc): high = stride offset | version | swizzle, low = address | leading offset
+          // descriptor halves: high = stride offset | version | swizzle, low = address | leading offset
           const uint32_t sa = (tiles_addr + stage * C::STAGE_BYTES) >> 4;
           const uint32_t a_lo = sa | ((ak ? 1u : LBO_MN) << 16);
           const uint32_t b_lo = (sa + (A_TILE_BYTES >> 4)) | ((bk ? 1u : LBO_MN) << 16);
@@ -581,8 +548,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
   __syncthreads();
   if (*abort_flag) {
     // let bulk copies that were already issued land before shared memory is released
-    const unsigned long long t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 400000ll) __nanosleep(1000);  // about 200 microseconds
     __syncthreads();
   }
   if (PAIR) cluster_sync();  // neither CTA leaves (or frees TMEM) while its peer may still signal or write to it
@@ -687,7 +654,9 @@ int gemm_trace_read(long long* host) {  // DEV TRACE
 int gemm_occupancy(int pair, int* out) {
   using namespace tc;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(pair ? 2 * 74 : 148, 1, 1);
+  const int sms = sm_count();
+  if (sms <= 0) return fail(MMB_ERR_CUDA, "mmb_gemm_occupancy: no CUDA device");
+  cfg.gridDim = dim3(pair ? 2 * (sms / 2) : sms, 1, 1);
   cfg.blockDim = dim3(NUM_THREADS, 1, 1);
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
