@@ -300,7 +300,7 @@ __device__ __forceinline__ float quotient_markstein(float m, float s, float r) {
 // ALL_FAST: the host has checked that every unit of the launch qualifies for the
 // fast path, so the general path is compiled out (fewer registers, more warps).
 template <int FORMAT, typename GradT, int DIV, bool ALL_FAST>
-__global__ void __launch_bounds__(THREADS, ALL_FAST ? 3 : 1)
+__global__ void __launch_bounds__(THREADS, ALL_FAST ? 4 : 1)
 momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_scale, float expand_min,
                 float* __restrict__ partials, const float* __restrict__ grad_scale_dev) {
   if (grad_scale_dev != nullptr) grad_scale = __fmul_rn(grad_scale, *grad_scale_dev);  // e.g. a clip coefficient
