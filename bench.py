@@ -198,6 +198,7 @@ def main():
     ap.add_argument("--chunks", type=int, default=4, help="pipeline chunks of the sharded (multi-GPU) step")
     ap.add_argument("--state-format", default="fp8_absmax", choices=["fp8_absmax", "fp8_expand", "param"],
                     help="momentum state: FP8 absmax (headline), COAT range expansion, or the parameter dtype")
+    ap.add_argument("--ns-max-batch", type=int, default=256, help="blocks per Newton-Schulz slice")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -235,7 +236,8 @@ def main():
 
     muon, adamw = build_workload(dev, args.nblocks)
     opt = MonarchMuonOptimizer(muon, adamw, lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95),
-                               adamw_weight_decay=0.1, adamw_eps=1e-8, state_format=args.state_format)
+                               adamw_weight_decay=0.1, adamw_eps=1e-8, state_format=args.state_format,
+                               ns_max_batch=args.ns_max_batch)
     if args.state_format != "fp8_absmax":
         config["workload"] = config["workload"].replace("FP8 E4M3 absmax momentum state",
                                                         f"momentum state format {args.state_format}")

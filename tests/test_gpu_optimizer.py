@@ -343,3 +343,44 @@ def test_fused_gradient_clipping_matches_clip_then_step(case):
     for p, b, g in zip(muon, before, mg):
         want = (b.cpu() * 0.95).to(p.dtype).float() + g.float() if case == "bf16" else b.cpu() * 0.95 + g.float()
         assert relf(opt.state[p]["momentum_buffer"], want.to(p.dtype)) < 1e-6
+
+
+def test_edge_cases_zero_nan_and_empty_groups():
+    from monarch_muon_b200 import MonarchMuonOptimizer, _lib, newton_schulz_batched
+    from oracle import muon_oracle
+    # Newton-Schulz: an all-zero block stays zero (0 / (0 + 1e-7)), a block with a NaN/Inf poisons only itself
+    x = torch.randn(4, 256, 384, generator=torch.Generator().manual_seed(8)).bfloat16()
+    x[1].zero_()
+    x[2, 5, 7] = float("nan")
+    x[3, 0, 0] = float("inf")
+    out = newton_schulz_batched(x.cuda()).cpu()
+    ref = muon_oracle.newton_schulz(x)
+    assert relf(out[0], ref[0]) < 5e-2
+    assert torch.all(out[1] == 0) and torch.all(ref[1] == 0)
+    assert torch.isnan(out[2]).all() and torch.isnan(ref[2]).all()
+    assert not torch.isfinite(out[3]).any()
+    assert _lib.read_status(torch.device("cuda", 0)) == 0           # non-finite data is not a device error
+    # the optimizer accepts an empty Muon group, an empty AdamW group, and a step with no gradients at all
+    w = torch.nn.Parameter(torch.ones(2, 64, 64, device="cuda"))
+    v = torch.nn.Parameter(torch.ones(10, device="cuda"))
+    only_adamw = MonarchMuonOptimizer([], [v], lr=1e-2)
+    v.grad = torch.ones_like(v)
+    only_adamw.step()
+    assert float(v.data[0]) < 1.0
+    only_muon = MonarchMuonOptimizer([w], [], lr=1e-2)
+    only_muon.step()                                                # no gradient anywhere: nothing happens
+    assert torch.all(w.data == 1.0) and len(only_muon.state) == 0
+    w.grad = torch.zeros_like(w)                                    # zero gradient: zero momentum, zero update
+    only_muon.step()
+    assert torch.all(w.data == 1.0) and torch.all(only_muon.state[w]["momentum_buffer"] == 0)
+    # FP8 state with an Inf gradient: the group saturates/poisons without faulting, the rest is unaffected
+    p = torch.nn.Parameter(torch.zeros(1, 128, 128, device="cuda", dtype=torch.bfloat16))
+    opt = MonarchMuonOptimizer([p], [], lr=1e-2, state_format="fp8_absmax")
+    g = torch.full((1, 128, 128), 1e-3, dtype=torch.bfloat16)
+    g[0, 3, 0] = float("inf")
+    p.grad = g.cuda()
+    opt.step()
+    torch.cuda.synchronize()
+    codes = opt.state[p]["momentum_buffer"].view(torch.uint8).cpu().reshape(-1, 128)
+    assert torch.all(codes[0] == codes[0, 0]) and int(codes[0, 0]) != 0x7F      # untouched group: all equal finite codes
+    assert _lib.read_status(torch.device("cuda", 0)) == 0
