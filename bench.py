@@ -181,6 +181,48 @@ def cpu_reference_step_ms(nblocks: int, steps: int, warmup: int, threads: int | 
     return sum(times) / len(times), desc, threads
 
 
+def gpu_reference_step(args, config) -> int:
+    """The reference step's torch-op sequence (bf16 twin: _foreach momentum, cat, bmm-based
+    Newton-Schulz, per-tensor add_, _foreach AdamW) on the full workload on cuda:0, timed with
+    CUDA events.  It is the restatement used as the parity checker, here only timed: it shows
+    what the reference's own GPU path (cuBLAS batched GEMMs + elementwise torch kernels) costs
+    on the same box."""
+    from oracle import muon_oracle
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    torch.backends.cuda.matmul.allow_tf32 = True     # as the reference's harness sets it
+    muon, adamw = build_workload(dev, args.nblocks)
+    ref = muon_oracle.OracleMonarchMuon([p.data for p in muon], [p.data for p in adamw], lr=0.02, momentum=0.95,
+                                        adamw_betas=(0.9, 0.95), adamw_weight_decay=0.1, adamw_eps=1e-8,
+                                        ns_dtype=torch.bfloat16, foreach_cpu=True)
+    mg, ag = [p.grad for p in muon], [p.grad for p in adamw]
+    sampler = ClockSampler(0)
+    sampler.start()
+    for _ in range(max(3, args.warmup)):
+        ref.step(mg, ag)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin = time.time()
+    e0.record()
+    for _ in range(args.steps):
+        ref.step(mg, ag)
+    e1.record()
+    torch.cuda.synchronize()
+    t_end = time.time()
+    ms = e0.elapsed_time(e1) / args.steps
+    line = {"impl": "reference", "reference_device": "cuda", "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": ms / H100_PUBLISHED_MS, "dtype": "bf16", "data": "synthetic",
+            "config": dict(config, workload=config["workload"].replace("FP8 E4M3 absmax momentum state",
+                                                                       "bf16 momentum state (the reference's)")),
+            "note": "torch-op restatement of the reference's bf16 step on the GPU (cuBLAS bmm + elementwise kernels), "
+                    "full workload, gradients resident",
+            "peak_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
+            "clocks": sampler.stop(t_begin, t_end), "gpu_launches": 0}
+    print(json.dumps(line))
+    return 0
+
+
 # ------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
@@ -199,6 +241,9 @@ def main():
     ap.add_argument("--state-format", default="fp8_absmax", choices=["fp8_absmax", "fp8_expand", "param"],
                     help="momentum state: FP8 absmax (headline), COAT range expansion, or the parameter dtype")
     ap.add_argument("--ns-max-batch", type=int, default=256, help="blocks per Newton-Schulz slice")
+    ap.add_argument("--reference-device", default="cpu", choices=["cpu", "cuda"],
+                    help="--impl reference only: cpu (default; the reference's CPU step on host cores) or cuda (the "
+                         "same torch-op restatement run on the GPU, i.e. what the reference's own step costs on this box)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -212,6 +257,8 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return 0
+        if args.reference_device == "cuda":
+            return gpu_reference_step(args, config)
         ms, desc, threads = cpu_reference_step_ms(args.nblocks, max(1, args.steps), max(0, args.warmup))
         line = {"impl": "reference", "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
