@@ -50,7 +50,12 @@ extern "C" {
 #define MMB_DIV_IEEE 0
 #define MMB_DIV_FULL 1
 #define MMB_DIV_IEEE_STRICT 2 /* IEEE results through the compiler's division everywhere: slower, same bits
-                                 as MMB_DIV_IEEE; exists to verify the fast exact quotient against */
+                                 as MMB_DIV_IEEE for the absmax format; exists to verify the fast exact
+                                 quotient against.  For the range-expansion format MMB_DIV_IEEE also forms
+                                 pow() as 2^(y*log2 x) on the special-function unit when the exponent is at
+                                 most 4 (result within ~1e-6 of the library powf: about one E4M3 code in
+                                 10^5 moves by one step), while STRICT and FULL call the library powf, as
+                                 the reference's kernels do */
 
 /* Newton-Schulz GEMM back ends */
 #define MMB_NS_TCGEN05 0 /* tcgen05.mma + TMEM + TMA (the product)             */
@@ -208,6 +213,39 @@ typedef struct mmb_adamw_seg {
 
 int mmb_adamw_step(const mmb_adamw_seg* segs, int nseg, int dtype, float lr, float beta1, float beta2,
                    float weight_decay, float eps, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Steps on fp32 master weights with a bf16 copy for the model, as the
+ * reference's fine-tuning optimizer keeps them (finetune/sft_optimizer.py:33-59:
+ * state["master"] is updated, then `p.copy_(master)`).  Update and down-cast
+ * are one pass.  `shadow` may be NULL (no copy written).
+ *   mmb_muon_update_master: master <- master + alpha*O       (:48-49)
+ *   mmb_adamw_master_step : torch.optim AdamW on the master  (:51-55); moments
+ *     are fp32, the gradient is read in its own dtype (`p.grad.float()`, :44),
+ *     `step` is the already-incremented count.
+ * ---------------------------------------------------------------------- */
+typedef struct mmb_master_update_seg {
+  void* master;       /* device, fp32, [numel]              */
+  void* shadow;       /* device, bf16, [numel] or NULL      */
+  const void* ortho;  /* device, bf16, [numel]              */
+  int64_t numel;
+} mmb_master_update_seg;
+
+int mmb_muon_update_master(const mmb_master_update_seg* segs, int nseg, float alpha, void* stream);
+
+typedef struct mmb_master_adamw_seg {
+  void* master;       /* device, fp32                       */
+  void* shadow;       /* device, bf16 or NULL               */
+  const void* grad;   /* device, grad_dtype                 */
+  void* exp_avg;      /* device, fp32                       */
+  void* exp_avg_sq;   /* device, fp32                       */
+  int64_t numel;
+  int32_t step;
+  int32_t pad_;
+} mmb_master_adamw_seg;
+
+int mmb_adamw_master_step(const mmb_master_adamw_seg* segs, int nseg, int grad_dtype, float lr, float beta1,
+                          float beta2, float weight_decay, float eps, void* stream);
 
 /* ------------------------------------------------------------------------
  * Global gradient norm and clip coefficient, computed on the device with no

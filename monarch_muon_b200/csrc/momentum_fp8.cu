@@ -79,6 +79,25 @@ __device__ __forceinline__ uint16_t float2_to_e4m3x2(float lo, float hi) {
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
+// pow(x, y) for normal x > 0 through the special-function unit: 2^(y*log2 x) with lg2.approx and
+// ex2.approx (absolute error of the logarithm about 2^-22.6, relative error of the exponential about
+// 2^-22), the product's rounding error carried into the result.  For |y| <= 4 the result is within about
+// 1e-6 of the true power, which moves an E4M3 code (relative spacing 2^-3) in roughly one element out of
+// 10^5.  Callers use it only in that range; larger exponents take the library powf.
+__device__ __forceinline__ float pow_hw(float x, float y) {
+  float l, r;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(l) : "f"(x));
+  const float th = __fmul_rn(l, y);
+  const float tl = __fmaf_rn(l, y, -th);
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(th));
+  return __fmaf_rn(r, __fmul_rn(tl, 0.6931471806f), r);
+}
+__device__ __noinline__ float pow_lib(float x, float y) { return powf(x, y); }
+__device__ __forceinline__ float with_sign_of(float magnitude, float s) {  // magnitude >= 0; -0.0 counts as >= 0
+  return s >= 0.0f ? magnitude : -magnitude;
+}
+constexpr float POW_HW_MAX_EXPONENT = 4.0f;
+
 __device__ __forceinline__ float group_max(float v) {
   v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
   v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
@@ -104,7 +123,7 @@ struct ExpandParams {
   float scale, expand, sqrt_mm;
 };
 
-template <int DIV>
+template <int DIV, bool HW_POW = false>
 __device__ __forceinline__ ExpandParams expand_group_params(float absmax, float absmin_nz, bool any_nz,
                                                             float expand_min) {
   const float eps = 1e-30f;
@@ -121,7 +140,8 @@ __device__ __forceinline__ ExpandParams expand_group_params(float absmax, float 
   p.expand = (ratio <= one_eps) ? 1.0f : fmaxf(raw, min_expand);
   p.sqrt_mm = fmaxf(fsqrt<DIV>(absmax) * fsqrt<DIV>(absmin), eps);
   float scale_base = fmaxf(fdiv<DIV>(absmax, p.sqrt_mm), eps);
-  p.scale = fmaxf(fdiv<DIV>(powf(scale_base, p.expand), 448.0f), eps);
+  const float pw = (HW_POW && p.expand <= POW_HW_MAX_EXPONENT) ? pow_hw(scale_base, p.expand) : powf(scale_base, p.expand);
+  p.scale = fmaxf(fdiv<DIV>(pw, 448.0f), eps);
   return p;
 }
 
@@ -134,6 +154,15 @@ __device__ __forceinline__ float expand_normalize(float m, bool valid, const Exp
   float sgn = (m >= 0.0f) ? 1.0f : -1.0f;
   float n = (valid && a > 0.0f) ? (is_signed ? sgn * pw : pw) : 0.0f;
   return fdiv<DIV>(n, p.scale);
+}
+
+// Out-of-line twin of expand_normalize for the fused kernel's rare groups (huge exponent, a scale whose
+// reciprocal cannot be corrected exactly, denormal inputs).
+template <int DIV>
+__device__ __noinline__ float expand_normalize_general(float m, float sqrt_mm, float expand, float scale) {
+  ExpandParams p;
+  p.scale = scale; p.expand = expand; p.sqrt_mm = sqrt_mm;
+  return expand_normalize<DIV>(m, true, p, true);
 }
 
 template <int DIV>
@@ -258,15 +287,20 @@ struct RawGroup {
   uint4 codes;
   uint4 grad[sizeof(GradT) == 2 ? 2 : 4];
   float scale;
+  float expand, sqrt_mm;  // range-expansion codec only
 };
 
-template <typename GradT>
+template <int FORMAT, typename GradT>
 __device__ __forceinline__ void load_raw(RawGroup<GradT>& r, const SegDev& sg, long long at) {
   r.codes = __ldcs(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(sg.state) + at));
   const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const GradT*>(sg.grad) + at);
 #pragma unroll
   for (int i = 0; i < (sizeof(GradT) == 2 ? 2 : 4); ++i) r.grad[i] = __ldcs(gp + i);
   r.scale = __ldg(sg.scale + at / GROUP);
+  if (FORMAT == MMB_STATE_FP8_EXPAND) {
+    r.expand = __ldg(sg.expand + at / GROUP);
+    r.sqrt_mm = __ldg(sg.sqrt_mm + at / GROUP);
+  }
 }
 
 template <typename GradT>
@@ -300,7 +334,9 @@ __device__ __forceinline__ float quotient_markstein(float m, float s, float r) {
 // ALL_FAST: the host has checked that every unit of the launch qualifies for the
 // fast path, so the general path is compiled out (fewer registers, more warps).
 template <int FORMAT, typename GradT, int DIV, bool ALL_FAST>
-__global__ void __launch_bounds__(THREADS, ALL_FAST ? 4 : 1)
+// resident CTAs per SM asked of the compiler: 4 (64 registers) for the absmax fast path, 3 (80) for the
+// range-expansion fast path, which carries more live values per group
+__global__ void __launch_bounds__(THREADS, ALL_FAST ? (FORMAT == MMB_STATE_FP8_ABSMAX ? 4 : 3) : 1)
 momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_scale, float expand_min,
                 float* __restrict__ partials, const float* __restrict__ grad_scale_dev) {
   if (grad_scale_dev != nullptr) grad_scale = __fmul_rn(grad_scale, *grad_scale_dev);  // e.g. a clip coefficient
@@ -331,18 +367,19 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
 
     // Fast path: FP8 absmax state, aligned pointers, only full groups.  One group of loads is kept in
     // flight ahead of the arithmetic.
-    const bool fast = ALL_FAST || (FORMAT == MMB_STATE_FP8_ABSMAX && sg.vec_ok && ((e1 - e0) % GROUP) == 0);
+    const bool fast = ALL_FAST || ((FORMAT == MMB_STATE_FP8_ABSMAX || FORMAT == MMB_STATE_FP8_EXPAND) && sg.vec_ok &&
+                                   ((e1 - e0) % GROUP) == 0);
     if (fast) {
       RawGroup<GradT> cur, nxt;
       bool cur_ok = grp_in_warp < ngroups;
-      if (cur_ok) load_raw<GradT>(cur, sg, e0 + static_cast<long long>(grp_in_warp) * GROUP + sub * ELEMS_PER_LANE);
+      if (cur_ok) load_raw<FORMAT, GradT>(cur, sg, e0 + static_cast<long long>(grp_in_warp) * GROUP + sub * ELEMS_PER_LANE);
       for (int g0 = 0; g0 < ngroups; g0 += 4) {
         const int gi_next = g0 + 4 + grp_in_warp;
         const bool nxt_ok = gi_next < ngroups;
-        if (nxt_ok) load_raw<GradT>(nxt, sg, e0 + static_cast<long long>(gi_next) * GROUP + sub * ELEMS_PER_LANE);
+        if (nxt_ok) load_raw<FORMAT, GradT>(nxt, sg, e0 + static_cast<long long>(gi_next) * GROUP + sub * ELEMS_PER_LANE);
         const long long at = e0 + static_cast<long long>(g0 + grp_in_warp) * GROUP + sub * ELEMS_PER_LANE;
         float m[ELEMS_PER_LANE];
-        float amax = 0.0f;
+        float amax = 0.0f, amin = 3.4028235e38f;
         if (cur_ok) {
           const uint16_t* h = reinterpret_cast<const uint16_t*>(&cur.codes);
 #pragma unroll
@@ -352,6 +389,12 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
             m[2 * i + 1] = f.y;
           }
           const bool scaled = grad_scale != 1.0f;
+          float inv_expand = 1.0f, sq_old = 1.0f;
+          if (FORMAT == MMB_STATE_FP8_EXPAND) {  // the clamps of expand_decode, once per group
+            inv_expand = fdiv<DIV>(1.0f, fmaxf(cur.expand, 1e-30f));
+            sq_old = fmaxf(cur.sqrt_mm, 1e-30f);
+          }
+          const bool dec_hw = DIV == MMB_DIV_IEEE && inv_expand <= POW_HW_MAX_EXPONENT;  // uniform over the group
 #pragma unroll
           for (int i = 0; i < ELEMS_PER_LANE; ++i) {
             float g = raw_grad<GradT>(cur, i);
@@ -359,20 +402,55 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
               g = __fmul_rn(g, grad_scale);
               if (sizeof(GradT) == 2) g = bf16_round(g);
             }
-            float t = __fmul_rn(beta, __fmul_rn(m[i], cur.scale));
+            float dec = __fmul_rn(m[i], cur.scale);
+            if (FORMAT == MMB_STATE_FP8_EXPAND) {  // expand_decode(raw, s, expand, sqrt_mm, signed)
+              const float a = fabsf(dec);
+              const float pw = dec_hw ? pow_hw(fmaxf(a, 1e-30f), inv_expand) : pow_lib(fmaxf(a, 1e-30f), inv_expand);
+              dec = a > 0.0f ? __fmul_rn(with_sign_of(pw, dec), sq_old) : 0.0f;
+            }
+            float t = __fmul_rn(beta, dec);
             t = __fadd_rn(t, g);
             m[i] = t;
-            amax = fmaxf(amax, fabsf(t));
+            const float a = fabsf(t);
+            amax = fmaxf(amax, a);
+            if (FORMAT == MMB_STATE_FP8_EXPAND && a > 0.0f) amin = fminf(amin, a);
           }
         } else {
 #pragma unroll
           for (int i = 0; i < ELEMS_PER_LANE; ++i) m[i] = 0.0f;
         }
         amax = group_max(amax);
-        const float s_new = fdiv<DIV>(__fadd_rn(amax, 1e-20f), 448.0f);
+        float s_new;
+        ExpandParams ep;
+        if (FORMAT == MMB_STATE_FP8_EXPAND) {
+          amin = group_min(amin);
+          ep = expand_group_params<DIV, DIV == MMB_DIV_IEEE>(amax, amin, amin < 3.4028235e38f, expand_min);
+          s_new = ep.scale;
+        } else {
+          s_new = fdiv<DIV>(__fadd_rn(amax, 1e-20f), 448.0f);
+        }
         if (cur_ok) {
           float q[ELEMS_PER_LANE];
-          if (DIV == MMB_DIV_IEEE && markstein_ok(s_new)) {   // uniform over the group
+          if (FORMAT == MMB_STATE_FP8_EXPAND) {
+            // expand_normalize per element.  Both divisions are by group constants; when the group's
+            // numbers allow it (uniform over the group) they are formed exactly from a reciprocal, and
+            // the power goes through the special-function unit; otherwise the general helpers run.
+            const bool quick = DIV == MMB_DIV_IEEE && ep.expand <= POW_HW_MAX_EXPONENT && markstein_ok(ep.sqrt_mm) &&
+                               markstein_ok(s_new) && amin >= 1e-30f && ep.sqrt_mm >= 1e-30f;
+            if (quick) {
+              const float r_sq = __frcp_rn(ep.sqrt_mm), r_s = __frcp_rn(s_new);
+#pragma unroll
+              for (int i = 0; i < ELEMS_PER_LANE; ++i) {
+                const float a = fabsf(m[i]);
+                const float base = fmaxf(quotient_markstein(a, ep.sqrt_mm, r_sq), 1e-30f);
+                const float pw = with_sign_of(pow_hw(base, ep.expand), m[i]);
+                q[i] = quotient_markstein(a > 0.0f ? pw : 0.0f, s_new, r_s);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < ELEMS_PER_LANE; ++i) q[i] = expand_normalize_general<DIV>(m[i], ep.sqrt_mm, ep.expand, s_new);
+            }
+          } else if (DIV == MMB_DIV_IEEE && markstein_ok(s_new)) {   // uniform over the group
             const float r = __frcp_rn(s_new);
 #pragma unroll
             for (int i = 0; i < ELEMS_PER_LANE; ++i) q[i] = quotient_markstein(m[i], s_new, r);
@@ -385,7 +463,10 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
 #pragma unroll
           for (int i = 0; i < 8; ++i) ch[i] = float2_to_e4m3x2(q[2 * i], q[2 * i + 1]);
           *reinterpret_cast<uint4*>(static_cast<uint8_t*>(sg.state) + at) = cv;
-          if (sub == 0) sg.scale[at / GROUP] = s_new;
+          if (sub == 0) {
+            sg.scale[at / GROUP] = s_new;
+            if (FORMAT == MMB_STATE_FP8_EXPAND) { sg.expand[at / GROUP] = ep.expand; sg.sqrt_mm[at / GROUP] = ep.sqrt_mm; }
+          }
 #pragma unroll
           for (int i = 0; i < ELEMS_PER_LANE; ++i) ss = fmaf(m[i], m[i], ss);
           if (sg.m_out != nullptr) {
@@ -620,6 +701,15 @@ void launch_momentum(int div_mode, bool all_fast, const SegTable& tab, int grid,
       momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_FULL, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
     return;
   }
+  if (FORMAT == MMB_STATE_FP8_EXPAND && all_fast) {
+    if (div_mode == MMB_DIV_IEEE_STRICT)
+      momentum_kernel<MMB_STATE_FP8_EXPAND, GradT, MMB_DIV_IEEE_STRICT, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
+    else if (div_mode != MMB_DIV_FULL)
+      momentum_kernel<MMB_STATE_FP8_EXPAND, GradT, MMB_DIV_IEEE, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
+    else
+      momentum_kernel<MMB_STATE_FP8_EXPAND, GradT, MMB_DIV_FULL, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
+    return;
+  }
   if (div_mode != MMB_DIV_FULL)
     momentum_kernel<FORMAT, GradT, MMB_DIV_IEEE, false><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
   else
@@ -634,7 +724,7 @@ void launch_momentum_format(int format, int div_mode, bool all_fast, const SegTa
       launch_momentum<MMB_STATE_FP8_ABSMAX, GradT>(div_mode, all_fast, tab, grid, beta, grad_scale, expand_min, partials, st);
       break;
     case MMB_STATE_FP8_EXPAND:
-      launch_momentum<MMB_STATE_FP8_EXPAND, GradT>(div_mode, false, tab, grid, beta, grad_scale, expand_min, partials, st);
+      launch_momentum<MMB_STATE_FP8_EXPAND, GradT>(div_mode, all_fast, tab, grid, beta, grad_scale, expand_min, partials, st);
       break;
     case MMB_STATE_BF16:
       launch_momentum<MMB_STATE_BF16, GradT>(MMB_DIV_IEEE, false, tab, grid, beta, grad_scale, expand_min, partials, st);
@@ -821,9 +911,9 @@ int mmb_fp8_quantize(const float* value_dev, uint8_t* codes_dev, float* scale_de
 #define MMB_Q(F, D) \
   quantize_kernel<F, D><<<grid, THREADS, 0, st>>>(value_dev, codes_dev, scale_dev, expand_dev, sqrt_minmax_dev, numel, is_signed, em)
   if (state_format == MMB_STATE_FP8_ABSMAX) {
-    if (div_mode == MMB_DIV_IEEE) MMB_Q(MMB_STATE_FP8_ABSMAX, MMB_DIV_IEEE); else MMB_Q(MMB_STATE_FP8_ABSMAX, MMB_DIV_FULL);
+    if (div_mode != MMB_DIV_FULL) MMB_Q(MMB_STATE_FP8_ABSMAX, MMB_DIV_IEEE); else MMB_Q(MMB_STATE_FP8_ABSMAX, MMB_DIV_FULL);
   } else {
-    if (div_mode == MMB_DIV_IEEE) MMB_Q(MMB_STATE_FP8_EXPAND, MMB_DIV_IEEE); else MMB_Q(MMB_STATE_FP8_EXPAND, MMB_DIV_FULL);
+    if (div_mode != MMB_DIV_FULL) MMB_Q(MMB_STATE_FP8_EXPAND, MMB_DIV_IEEE); else MMB_Q(MMB_STATE_FP8_EXPAND, MMB_DIV_FULL);
   }
 #undef MMB_Q
   MMB_CUDA_CHECK(cudaGetLastError());

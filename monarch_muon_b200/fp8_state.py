@@ -126,15 +126,22 @@ def scratch_floats(segs, nseg: int) -> int:
 def fp8_momentum_flat(codes: torch.Tensor, scales: torch.Tensor, grad: torch.Tensor, beta: float, *,
                       m_bf16: torch.Tensor | None = None, block_elems: int | None = None,
                       block_sumsq: torch.Tensor | None = None, grad_scale: float = 1.0,
-                      div_mode: int = _lib.DIV_IEEE) -> None:
-    """One absmax-codec heavy-ball step on a flat buffer, in place:
-    codes (uint8/E4M3 [n]), scales (fp32 [ceil(n/128)]), grad (bf16/fp32 [n])."""
+                      div_mode: int = _lib.DIV_IEEE, expand: torch.Tensor | None = None,
+                      sqrt_minmax: torch.Tensor | None = None, expand_min: int = 16) -> None:
+    """One FP8-state heavy-ball step on a flat buffer, in place:
+    codes (uint8/E4M3 [n]), scales (fp32 [ceil(n/128)]), grad (bf16/fp32 [n]).
+    With `expand` and `sqrt_minmax` (fp32, one per group) the state is in the
+    range-expansion format, else in the absmax format."""
     _lib.require_cuda(codes, scales, grad)
+    if (expand is None) != (sqrt_minmax is None):
+        raise ValueError("expand and sqrt_minmax go together")
     n = codes.numel()
     seg = (_lib.MomentumSeg * 1)()
     seg[0].grad = grad.data_ptr()
     seg[0].state = codes.data_ptr()
     seg[0].scale = scales.data_ptr()
+    seg[0].expand = _lib.ptr(expand)
+    seg[0].sqrt_minmax = _lib.ptr(sqrt_minmax)
     seg[0].m_bf16 = _lib.ptr(m_bf16)
     seg[0].numel = n
     seg[0].block_elems = block_elems if block_elems else n
@@ -143,5 +150,7 @@ def fp8_momentum_flat(codes: torch.Tensor, scales: torch.Tensor, grad: torch.Ten
     if block_sumsq is not None:
         scratch = torch.empty(scratch_floats(seg, 1), dtype=torch.float32, device=codes.device)
     with torch.cuda.device(codes.device):
-        momentum_step(seg, 1, grad_dtype=grad.dtype, state_format=_lib.STATE_FP8_ABSMAX, beta=beta,
-                      grad_scale=grad_scale, div_mode=div_mode, block_sumsq=block_sumsq, scratch=scratch)
+        momentum_step(seg, 1, grad_dtype=grad.dtype,
+                      state_format=_lib.STATE_FP8_ABSMAX if expand is None else _lib.STATE_FP8_EXPAND, beta=beta,
+                      grad_scale=grad_scale, div_mode=div_mode, expand_min=expand_min, block_sumsq=block_sumsq,
+                      scratch=scratch)

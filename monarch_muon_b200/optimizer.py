@@ -58,7 +58,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
     state_format : "param" keeps `momentum_buffer` in the parameter dtype like
         the reference; "fp8_absmax" / "fp8_expand" store it as E4M3 codes with
         per-128-group side arrays (absmax scale, or COAT range expansion).
-    fp8_div : "ieee" or "full" - division used by the FP8 quantiser.
+    fp8_div : "ieee", "full" or "ieee_strict" - arithmetic of the FP8 quantiser (MMB_DIV_* in the header).
     ns_backend : "tcgen05" (tensor cores) or "simt" (cross-check kernel).
     ns_max_batch : slice Newton-Schulz into at most this many blocks per call
         to bound its workspace.
@@ -80,7 +80,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         ]
         super().__init__(param_groups, defaults)
         self.state_format = state_format
-        self.fp8_div = {"ieee": _lib.DIV_IEEE, "full": _lib.DIV_FULL}[fp8_div]
+        self.fp8_div = {"ieee": _lib.DIV_IEEE, "full": _lib.DIV_FULL, "ieee_strict": _lib.DIV_IEEE_STRICT}[fp8_div]
         self.ns_backend = {"tcgen05": _lib.NS_TCGEN05, "simt": _lib.NS_SIMT}[ns_backend]
         self.ns_max_batch = ns_max_batch
         self.expand_min = expand_min

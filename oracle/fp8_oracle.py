@@ -190,3 +190,15 @@ def expand_dequant(codes_u8, scale, expand, sqrt_mm, signed: bool = True):
         power = torch.pow(torch.maximum(scaled, eps), 1.0 / ex)
         out = torch.where(scaled > 0, power * sq, torch.zeros((), dtype=f32))
     return out.reshape(-1)[:n]
+
+
+def expand_momentum_step(codes_u8, scale, expand, sqrt_mm, grad, beta: float, expand_min: int = 16):
+    """One heavy-ball step on range-expansion-coded momentum: what
+    CoatStateMonarchMuon.step does to a momentum buffer (coat_state_muon.py:126-139
+    around monarch_muon.py:148): dequantise to fp32, m = beta*m, m = m + g,
+    quantise again.  Returns (codes, scale, expand, sqrt_minmax, m_fp32)."""
+    m = expand_dequant(codes_u8, scale, expand, sqrt_mm, signed=True)
+    m = m * torch.tensor(beta, dtype=torch.float32)
+    m = m + grad.reshape(-1).to(torch.float32)
+    c, s, e, q = expand_quant(m, signed=True, expand_min=expand_min)
+    return c, s, e, q, m
