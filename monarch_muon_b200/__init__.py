@@ -15,6 +15,7 @@ from .optimizer import MonarchMuonOptimizer  # noqa: F401
 from .coat_state import CoatStateMonarchMuon  # noqa: F401
 from .newton_schulz import newton_schulz_batched, gemm_bf16  # noqa: F401
 from .fp8_state import quantize_, dequantize  # noqa: F401
+from .sft import SFTOptimizer  # noqa: F401
 
-__all__ = ["MonarchMuonOptimizer", "CoatStateMonarchMuon", "newton_schulz_batched", "gemm_bf16",
+__all__ = ["MonarchMuonOptimizer", "CoatStateMonarchMuon", "SFTOptimizer", "newton_schulz_batched", "gemm_bf16",
            "quantize_", "dequantize"]

@@ -23,6 +23,8 @@ coat_absmax.npz  COAT's plain FP8 AdamW kernel (third_party/coat/optimizer/
                (g=0, beta=0.5).  The interpreter's fp8 cast drops the carry
                when rounding reaches the next power of two, so its codes are a
                pin only away from those carries; its scales are exact.
+sft.npz        3 steps of finetune/sft_optimizer.py's SFTOptimizer (fp32 master
+               weights, bf16 parameters; a Muon group and an AdamW group)
 """
 from __future__ import annotations
 
@@ -126,6 +128,30 @@ def make_coat(ref_root, out):
     np.savez_compressed(out, **data)
 
 
+def make_sft(ref_root, out):
+    sft = _load("ref_sft_optimizer", os.path.join(ref_root, "finetune/sft_optimizer.py"))
+    h = gi.SFT_HYPER
+    muon, adamw = gi.sft_params()
+    opt = sft.SFTOptimizer([{"params": muon, "algorithm": "muon", "lr": h["muon_lr"], "weight_decay": 0.0},
+                            {"params": adamw, "algorithm": "adamw", "lr": h["adamw_lr"]}],
+                           momentum=h["momentum"], betas=h["betas"], eps=h["eps"], weight_decay=h["weight_decay"])
+    data = {"checksum_params": np.array(sum(gi.checksum(p.data) for p in muon + adamw))}
+    for step in range(gi.SFT_STEPS):
+        mg, ag = gi.sft_grads(step)
+        for p, g in zip(muon + adamw, mg + ag):
+            p.grad = g
+        opt.step()
+        for i, p in enumerate(muon + adamw):
+            data[f"s{step}_p{i}"] = _np(p.data.clone())
+    for i, p in enumerate(muon + adamw):
+        st = opt.state[p]
+        data[f"final_master_{i}"] = _np(st["master"])
+        data[f"final_momentum_{i}"] = _np(st["momentum"])
+        if "variance" in st:
+            data[f"final_variance_{i}"] = _np(st["variance"])
+    np.savez_compressed(out, **data)
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: make_golden.py /path/to/reference-checkout")
@@ -138,6 +164,7 @@ def main():
     run_opt(pre, "fp32", os.path.join(HERE, "opt_fp32.npz"))
     run_opt(mem, "bf16", os.path.join(HERE, "opt_bf16.npz"))
     make_coat(ref_root, os.path.join(HERE, "coat_absmax.npz"))
+    make_sft(ref_root, os.path.join(HERE, "sft.npz"))
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

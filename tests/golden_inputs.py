@@ -82,3 +82,27 @@ def coat_input() -> torch.Tensor:
     g[128 * 3:128 * 4] = 0.0          # an all-zero group
     g[128 * 5 + 7] = 0.0
     return g
+
+
+# fine-tuning optimizer (fp32 master weights, bf16 parameters): a Monarch factor, two dense matrices
+# (one taller than wide) under Muon; an embedding-like matrix and a norm vector under AdamW
+SFT_STEPS = 3
+SFT_MUON_SHAPES = ((2, 128, 128), (96, 64), (64, 160))
+SFT_ADAMW_SHAPES = ((256, 64), (64,))
+SFT_HYPER = dict(muon_lr=1e-3, adamw_lr=3e-5, momentum=0.95, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+
+
+def sft_params():
+    muon = [torch.nn.Parameter((0.02 * torch.randn(s, generator=_gen("sft", "m", i))).bfloat16())
+            for i, s in enumerate(SFT_MUON_SHAPES)]
+    adamw = [torch.nn.Parameter((0.02 * torch.randn(s, generator=_gen("sft", "a", i))).bfloat16())
+             for i, s in enumerate(SFT_ADAMW_SHAPES)]
+    return muon, adamw
+
+
+def sft_grads(step: int):
+    mg = [(1e-2 * torch.randn(s, generator=_gen("sftg", "m", i, step))).bfloat16() for i, s in enumerate(SFT_MUON_SHAPES)]
+    ag = [(1e-2 * torch.randn(s, generator=_gen("sftg", "a", i, step))).bfloat16() for i, s in enumerate(SFT_ADAMW_SHAPES)]
+    if step == 0:
+        mg[-1] = None          # skipped on the first step: state is created lazily on the second
+    return mg, ag

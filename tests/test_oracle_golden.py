@@ -137,3 +137,29 @@ def test_shape_book_keeping_matches_reference_counts():
     assert abs(flops / 1e12 - 71.640) < 0.01
     small = muon_oracle.llama_monarch_muon_shapes(256, 4, 688, 2)
     assert sum(s[0] * s[1] * s[2] for s in small) == 2_498_560
+
+
+def test_sft_optimizer_three_steps_bit_exact():
+    """oracle/sft_oracle.py against the reference's SFTOptimizer (fp32 master weights, bf16 parameters,
+    Muon on a Monarch factor and on 2-D matrices, AdamW on the rest)."""
+    from oracle import sft_oracle
+    gold = np.load(os.path.join(GOLD, "sft.npz"))
+    h = gi.SFT_HYPER
+    muon, adamw = gi.sft_params()
+    assert sum(gi.checksum(p.data) for p in muon + adamw) == int(gold["checksum_params"]), "CPU generator drifted"
+    muon = [p.data for p in muon]
+    adamw = [p.data for p in adamw]
+    opt = sft_oracle.OracleSFT([{"params": muon, "algorithm": "muon", "lr": h["muon_lr"], "weight_decay": 0.0},
+                                {"params": adamw, "algorithm": "adamw", "lr": h["adamw_lr"]}],
+                               momentum=h["momentum"], betas=h["betas"], eps=h["eps"], weight_decay=h["weight_decay"])
+    for step in range(gi.SFT_STEPS):
+        mg, ag = gi.sft_grads(step)
+        opt.step([mg, ag])
+        for i, p in enumerate(muon + adamw):
+            assert torch.equal(p, _t(gold[f"s{step}_p{i}"], torch.bfloat16)), (step, i)
+    for i, p in enumerate(muon + adamw):
+        st = opt.state[id(p)]
+        assert torch.equal(st["master"], _t(gold[f"final_master_{i}"], torch.float32)), i
+        assert torch.equal(st["momentum"], _t(gold[f"final_momentum_{i}"], torch.float32)), i
+        if "variance" in st:
+            assert torch.equal(st["variance"], _t(gold[f"final_variance_{i}"], torch.float32)), i
