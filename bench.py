@@ -399,23 +399,25 @@ def run_isolated(args, dev):
                              "traffic": None}}
     else:
         n = args.fp8_elems // 128 * 128
-        codes = torch.zeros(n, dtype=torch.uint8, device=dev)
-        scales = torch.zeros(n // 128, dtype=torch.float32, device=dev)
+        expand_fmt = args.state_format == "fp8_expand"
         m0 = torch.empty(n, dtype=torch.float32, device=dev).normal_(0, 1e-3, generator=gen)
         st = {}
-        fp8_state.quantize_(st, "momentum_buffer", m0, codec="absmax")
-        codes.copy_(st["momentum_buffer"].view(torch.uint8))
-        scales.copy_(st["scale_momentum_buffer"])
-        del m0, st
+        fp8_state.quantize_(st, "momentum_buffer", m0, codec="expand" if expand_fmt else "absmax")
+        codes = st["momentum_buffer"].view(torch.uint8)
+        scales = st["scale_momentum_buffer"]
+        side = dict(expand=st["expand_momentum_buffer"], sqrt_minmax=st["sqrt_minmax_momentum_buffer"]) if expand_fmt else {}
+        del m0
         g = torch.empty(n, dtype=torch.bfloat16, device=dev).normal_(0, 1e-3, generator=gen)
         m16 = torch.empty(n, dtype=torch.bfloat16, device=dev)
 
         def fn():
-            fp8_state.fp8_momentum_flat(codes, scales, g, 0.95, m_bf16=m16)
+            fp8_state.fp8_momentum_flat(codes, scales, g, 0.95, m_bf16=m16, **side)
         ms, tb, te = _timed(fn, args.steps, args.warmup)
-        ach = n * S.FP8_ABSMAX_BYTES_PER_ELEM / (ms * 1e-3) / 1e9
+        per_elem = S.FP8_ABSMAX_BYTES_PER_ELEM + (2 * 2 * 4 / 128 if expand_fmt else 0.0)   # two more fp32 per group, in and out
+        ach = n * per_elem / (ms * 1e-3) / 1e9
+        name = "range-expansion" if expand_fmt else "absmax"
         line = {"metric": "fp8_momentum_gbs", "value": ach, "unit": "GB/s", "higher_is_better": True,
-                "ms_per_step": ms, "config": {"workload": f"isolated FP8 absmax momentum kernel, flat buffer of {n} "
+                "ms_per_step": ms, "config": {"workload": f"isolated FP8 {name} momentum kernel, flat buffer of {n} "
                                               "elements, bf16 gradients N(0,1e-3), groups of 128",
                                               "cache": "inputs_larger_than_l2"},
                 "roofline": {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",

@@ -61,3 +61,54 @@ def test_sharded_step_is_bitwise_the_serial_step(tmp_path):
                           "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
                          env=env, capture_output=True, text=True, timeout=600)
     assert "SHARDED_EQUALS_SERIAL" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+
+
+ZERO_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["MMB_ROOT"])
+from torch.distributed.optim import ZeroRedundancyOptimizer
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+dist.init_process_group("nccl", device_id=dev)
+from monarch_muon_b200.sft import SFTOptimizer
+ok = True
+for algorithm in ("adamw", "muon"):
+    gen = torch.Generator().manual_seed(29)
+    shapes = [(64, 128), (128, 64), (2, 64, 128), (2, 128, 64)]
+    params = [torch.nn.Parameter(torch.randn(s, generator=gen).bfloat16().to(dev)) for s in shapes]
+    refs = [torch.nn.Parameter(p.detach().clone()) for p in params]
+    zero = ZeroRedundancyOptimizer([{"params": params, "algorithm": algorithm}], optimizer_class=SFTOptimizer, lr=1e-3)
+    serial = SFTOptimizer([{"params": refs, "algorithm": algorithm}], lr=1e-3)
+    for step in range(4):
+        for p, r in zip(params, refs):
+            p.grad = torch.randn(p.shape, generator=gen).bfloat16().to(dev)
+            r.grad = p.grad.clone()
+        zero.step()
+        serial.step()
+        ok = ok and all(torch.equal(p.data, r.data) for p, r in zip(params, refs))
+    owned = sum(p.numel() for g in zero.optim.param_groups for p in g["params"])
+    ok = ok and owned < sum(p.numel() for p in params)
+torch.cuda.synchronize()
+flag = torch.tensor([1 if ok else 0], device=dev); dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+if rank == 0: print("ZERO_EQUALS_SERIAL" if int(flag) == 1 else "ZERO_DIFFERS")
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sft_optimizer_under_zero_redundancy_wrapper(tmp_path):
+    """The reference shards its fine-tuning optimizer with torch's ZeroRedundancyOptimizer
+    (finetune/train_sft.py:69-72; finetune/test_sft_distributed.py:15-36 checks it against the serial
+    optimizer bit for bit).  Same check with this library's SFTOptimizer as the wrapped class."""
+    script = tmp_path / "zero_worker.py"
+    script.write_text(ZERO_WORKER)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, MMB_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+               NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
+                         env=env, capture_output=True, text=True, timeout=600)
+    assert "ZERO_EQUALS_SERIAL" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
