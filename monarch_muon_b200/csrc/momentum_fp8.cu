@@ -93,8 +93,10 @@ __device__ __forceinline__ float pow_hw(float x, float y) {
   return __fmaf_rn(r, __fmul_rn(tl, 0.6931471806f), r);
 }
 __device__ __noinline__ float pow_lib(float x, float y) { return powf(x, y); }
-__device__ __forceinline__ float with_sign_of(float magnitude, float s) {  // magnitude >= 0; -0.0 counts as >= 0
-  return s >= 0.0f ? magnitude : -magnitude;
+// magnitude (>= 0) with the sign bit of s: one logic instruction.  The callers replace the result by 0
+// when s is +-0, so the sign given to a zero does not matter.
+__device__ __forceinline__ float with_sign_of(float magnitude, float s) {
+  return __uint_as_float(__float_as_uint(magnitude) | (__float_as_uint(s) & 0x80000000u));
 }
 constexpr float POW_HW_MAX_EXPONENT = 4.0f;
 
@@ -436,13 +438,16 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
             // numbers allow it (uniform over the group) they are formed exactly from a reciprocal, and
             // the power goes through the special-function unit; otherwise the general helpers run.
             const bool quick = DIV == MMB_DIV_IEEE && ep.expand <= POW_HW_MAX_EXPONENT && markstein_ok(ep.sqrt_mm) &&
-                               markstein_ok(s_new) && amin >= 1e-30f && ep.sqrt_mm >= 1e-30f;
+                               markstein_ok(s_new) && amin >= 1e-30f && ep.sqrt_mm >= 1e-30f && amax <= amin * 1e30f;
             if (quick) {
               const float r_sq = __frcp_rn(ep.sqrt_mm), r_s = __frcp_rn(s_new);
 #pragma unroll
               for (int i = 0; i < ELEMS_PER_LANE; ++i) {
                 const float a = fabsf(m[i]);
-                const float base = fmaxf(quotient_markstein(a, ep.sqrt_mm, r_sq), 1e-30f);
+                // absmax/absmin <= 1e30 (checked in `quick`) keeps the quotient of a non-zero element above
+                // 1e-15, so the reference's clamp at 1e-30 never acts; a == 0 yields a NaN power that the
+                // select below discards
+                const float base = quotient_markstein(a, ep.sqrt_mm, r_sq);
                 const float pw = with_sign_of(pow_hw(base, ep.expand), m[i]);
                 q[i] = quotient_markstein(a > 0.0f ? pw : 0.0f, s_new, r_s);
               }
