@@ -85,7 +85,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, smax, reasons = [], None, set()
+        sm, smax, reasons, watts = [], None, set(), []
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for ts, r in self.rows:
             if len(r) < 8 or ts < t_begin or ts > t_end + 0.15:
@@ -93,13 +93,14 @@ class ClockSampler:
             try:
                 sm.append(float(r[0]))
                 smax = float(r[1])
+                watts.append(float(r[2]))
             except ValueError:
                 continue
             for name, v in zip(names, r[4:8]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "samples": len(sm),
-                "reasons": sorted(reasons)}
+                "power_w": statistics.median(watts) if watts else None, "reasons": sorted(reasons)}
 
 
 # ------------------------------------------------------------------ the workload
@@ -231,14 +232,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--nblocks", type=int, default=4, choices=[2, 4])
-    ap.add_argument("--case", default="step", choices=["step", "ns", "fp8"],
+    ap.add_argument("--case", default="step", choices=["step", "ns", "fp8", "gemm"],
                     help="step: the full optimizer step (headline); ns: isolated batched Newton-Schulz on the "
-                         "128+64+64 block set; fp8: isolated FP8 momentum kernel on a flat buffer")
+                         "128+64+64 block set; fp8: isolated FP8 momentum kernel on a flat buffer; gemm: the library's "
+                         "batched GEMM beside cuBLAS (torch.bmm) on the Newton-Schulz shapes, each run back to "
+                         "back for seconds so that the power cap is in force")
     ap.add_argument("--ns-blocks", type=int, default=128, help="square blocks in --case ns (tall/wide get half each)")
     ap.add_argument("--fp8-elems", type=int, default=1_600_000_000)
     ap.add_argument("--comm-sms", type=int, default=0, help="SMs left to NCCL during the sharded step")
     ap.add_argument("--chunks", type=int, default=4, help="pipeline chunks of the sharded (multi-GPU) step")
-    ap.add_argument("--state-format", default="fp8_absmax", choices=["fp8_absmax", "fp8_expand", "param"],
+    ap.add_argument("--state-format", default="fp8_absmax", choices=["fp8_absmax", "fp8_expand", "param", "coat"],
                     help="momentum state: FP8 absmax (headline), COAT range expansion, or the parameter dtype")
     ap.add_argument("--ns-max-batch", type=int, default=256, help="blocks per Newton-Schulz slice")
     ap.add_argument("--reference-device", default="cpu", choices=["cpu", "cuda"],
@@ -278,13 +281,20 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     from monarch_muon_b200 import MonarchMuonOptimizer, _lib
+    if args.case == "gemm":
+        return run_gemm_comparison(args, dev)
     if args.case != "step":
         return run_isolated(args, dev)
 
     muon, adamw = build_workload(dev, args.nblocks)
-    opt = MonarchMuonOptimizer(muon, adamw, lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95),
-                               adamw_weight_decay=0.1, adamw_eps=1e-8, state_format=args.state_format,
-                               ns_max_batch=args.ns_max_batch)
+    if args.state_format == "coat":
+        from monarch_muon_b200 import CoatStateMonarchMuon
+        opt = CoatStateMonarchMuon(muon, adamw, lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95),
+                                   adamw_weight_decay=0.1, adamw_eps=1e-8, ns_max_batch=args.ns_max_batch)
+    else:
+        opt = MonarchMuonOptimizer(muon, adamw, lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95),
+                                   adamw_weight_decay=0.1, adamw_eps=1e-8, state_format=args.state_format,
+                                   ns_max_batch=args.ns_max_batch)
     if args.state_format != "fp8_absmax":
         config["workload"] = config["workload"].replace("FP8 E4M3 absmax momentum state",
                                                         f"momentum state format {args.state_format}")
@@ -365,6 +375,55 @@ def _timed(fn, steps: int, warmup: int, sampler=None):
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / steps, t_begin, time.time()
+
+
+def run_gemm_comparison(args, dev):
+    """Sustained throughput of mmb_gemm_bf16 and of cuBLAS (torch.bmm) on the GEMM shapes of one
+    Newton-Schulz iteration at the 4-block model (Gram K=1024 and K=2752, Apply N=2752) and on a large
+    square GEMM, each run back to back for ~3 s with clocks and power sampled: the yardstick for what a
+    library GEMM reaches on these shapes under the power cap.  Last line: the symmetric Gram as the step
+    runs it (only block-upper tiles computed), in algorithmic FLOPs."""
+    from monarch_muon_b200 import gemm_bf16
+    gen = torch.Generator(device=dev).manual_seed(3)
+
+    def sustained(fn, flops, secs=3.0):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(dev.index)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0, n = time.time(), 0
+        e0.record()
+        while time.time() - t0 < secs:
+            for _ in range(20):
+                fn()
+            n += 20
+            torch.cuda.synchronize()
+        e1.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop(t0 + 1.0, time.time())
+        ms = e0.elapsed_time(e1) / n
+        return {"us": ms * 1e3, "tflops": flops / ms / 1e9, "sm_mhz": clocks["sm_mhz"], "power_w": clocks.get("power_w"),
+                "reasons": clocks["reasons"]}
+
+    rows = []
+    for (b, M, N, K) in [(256, 1024, 1024, 1024), (128, 1024, 1024, 2752), (128, 1024, 2752, 1024), (8, 8192, 8192, 8192)]:
+        a = torch.empty(b, M, K, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=gen)
+        bb = torch.empty(b, N, K, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=gen)
+        out = torch.empty(b, M, N, dtype=torch.bfloat16, device=dev)
+        bt = bb.transpose(1, 2)
+        fl = 2.0 * b * M * N * K
+        rows.append({"shape": f"{b}x{M}x{N}x{K}", "cublas": sustained(lambda: torch.bmm(a, bt, out=out), fl),
+                     "ours": sustained(lambda: gemm_bf16(a, bb, out=out), fl)})
+        del a, bb, out, bt
+    x = torch.empty(256, 1024, 1024, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=gen)
+    out = torch.empty(256, 1024, 1024, dtype=torch.bfloat16, device=dev)
+    rows.append({"shape": "256x1024x1024x1024 Gram, block-upper tiles only, algorithmic FLOPs",
+                 "ours": sustained(lambda: gemm_bf16(x, x, sym_out=True, out=out), 2.0 * 256 * 1024 ** 3)})
+    print(json.dumps({"metric": "sustained_batched_gemm_tflops", "unit": "TFLOP/s", "n_gpus": 1, "dtype": "bf16",
+                      "data": "synthetic", "rows": rows}))
+    return 0
 
 
 def run_isolated(args, dev):

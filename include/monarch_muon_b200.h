@@ -215,6 +215,35 @@ int mmb_adamw_step(const mmb_adamw_seg* segs, int nseg, int dtype, float lr, flo
                    float weight_decay, float eps, void* stream);
 
 /* ------------------------------------------------------------------------
+ * AdamW with both moments stored as E4M3 codes + per-128-group side arrays,
+ * decoded, stepped and re-encoded in one pass.  Replaces the AdamW part of
+ * CoatStateMonarchMuon.step, pretrain/src/models/monarch/coat_state_muon.py:
+ * 126-139 (dequantize every state -> _adamw_step, monarch_muon.py:171-201,
+ * with fp32 moments -> quantize_): exp_avg is a signed state, exp_avg_sq an
+ * unsigned one (:19).  state_format is MMB_STATE_FP8_EXPAND (the reference's
+ * codec; expand_* and sqrt_minmax_* required) or MMB_STATE_FP8_ABSMAX (they
+ * may be NULL).  Fresh states are all-zero codes with side arrays set to 1.
+ * ---------------------------------------------------------------------- */
+typedef struct mmb_adamw_fp8_seg {
+  void* param;                   /* device, dtype                     */
+  const void* grad;              /* device, dtype                     */
+  void* exp_avg;                 /* device, E4M3 codes [numel]        */
+  float* scale_exp_avg;          /* device, fp32 [ceil(numel/128)]    */
+  float* expand_exp_avg;
+  float* sqrt_minmax_exp_avg;
+  void* exp_avg_sq;              /* device, E4M3 codes [numel]        */
+  float* scale_exp_avg_sq;
+  float* expand_exp_avg_sq;
+  float* sqrt_minmax_exp_avg_sq;
+  int64_t numel;
+  int32_t step;                  /* already-incremented count         */
+  int32_t pad_;
+} mmb_adamw_fp8_seg;
+
+int mmb_adamw_fp8_step(const mmb_adamw_fp8_seg* segs, int nseg, int dtype, int state_format, int div_mode, float lr,
+                       float beta1, float beta2, float weight_decay, float eps, int expand_min, void* stream);
+
+/* ------------------------------------------------------------------------
  * Steps on fp32 master weights with a bf16 copy for the model, as the
  * reference's fine-tuning optimizer keeps them (finetune/sft_optimizer.py:33-59:
  * state["master"] is updated, then `p.copy_(master)`).  Update and down-cast

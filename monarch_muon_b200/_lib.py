@@ -40,6 +40,15 @@ class AdamWSeg(C.Structure):
                 ("numel", C.c_int64), ("step", C.c_int32), ("pad_", C.c_int32)]
 
 
+class AdamWFp8Seg(C.Structure):
+    _fields_ = [("param", C.c_void_p), ("grad", C.c_void_p),
+                ("exp_avg", C.c_void_p), ("scale_exp_avg", C.c_void_p), ("expand_exp_avg", C.c_void_p),
+                ("sqrt_minmax_exp_avg", C.c_void_p),
+                ("exp_avg_sq", C.c_void_p), ("scale_exp_avg_sq", C.c_void_p), ("expand_exp_avg_sq", C.c_void_p),
+                ("sqrt_minmax_exp_avg_sq", C.c_void_p),
+                ("numel", C.c_int64), ("step", C.c_int32), ("pad_", C.c_int32)]
+
+
 class MasterUpdateSeg(C.Structure):
     _fields_ = [("master", C.c_void_p), ("shadow", C.c_void_p), ("ortho", C.c_void_p), ("numel", C.c_int64)]
 
@@ -68,6 +77,7 @@ SYMBOLS = {
     "mmb_gemm_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _i, _i, _vp, _vp]),
     "mmb_muon_update": (_i, [C.POINTER(UpdateSeg), _i, _i, _f, _vp]),
     "mmb_adamw_step": (_i, [C.POINTER(AdamWSeg), _i, _i, _f, _f, _f, _f, _f, _vp]),
+    "mmb_adamw_fp8_step": (_i, [C.POINTER(AdamWFp8Seg), _i, _i, _i, _i, _f, _f, _f, _f, _f, _i, _vp]),
     "mmb_muon_update_master": (_i, [C.POINTER(MasterUpdateSeg), _i, _f, _vp]),
     "mmb_adamw_master_step": (_i, [C.POINTER(MasterAdamWSeg), _i, _i, _f, _f, _f, _f, _f, _vp]),
     "mmb_grad_norm_scratch_floats": (_i64, []),

@@ -2,16 +2,15 @@
 
 Reference: pretrain/src/models/monarch/coat_state_muon.py:117-151.  The
 reference dequantises every state tensor to fp32, runs the unchanged step and
-quantises back.  Here the Muon momentum never leaves FP8 between steps: the
-fused momentum kernel decodes, updates and re-encodes in one pass.  The
-embedded AdamW's two moments (a small share of the state) follow the
-reference's scheme: decode, step, encode, with the stand-alone codec kernels.
+quantises back.  Here no state leaves FP8 between steps: the fused momentum
+kernel and the fused FP8 AdamW kernel decode, update and re-encode a group of
+128 elements in registers, one pass each.
 """
 from __future__ import annotations
 
 import torch
 
-from . import fp8_state
+from . import _lib, fp8_state
 from .optimizer import MonarchMuonOptimizer
 
 
@@ -38,21 +37,49 @@ class CoatStateMonarchMuon(MonarchMuonOptimizer):
         kwargs.setdefault("expand_min", expand_min)
         super().__init__(*args, **kwargs)
 
+    def _adamw_new_state(self, p, state) -> None:
+        """Both moments start as all-zero codes (they decode to 0 whatever the side arrays hold)."""
+        n = p.numel()
+        groups = fp8_state.groups_of(n)
+        state["step"] = 0
+        keys = ("scale",) if self.codec == "absmax" else ("scale", "expand", "sqrt_minmax")
+        for name in ("exp_avg", "exp_avg_sq"):
+            state[name] = torch.zeros(p.shape, dtype=torch.uint8, device=p.device).view(torch.float8_e4m3fn)
+            for key in keys:
+                state[f"{key}_{name}"] = torch.ones(groups, dtype=torch.float32, device=p.device)
+
     def _adamw_step(self, group, lr: float) -> None:
-        live = [p for p in group["params"] if p.grad is not None]
-        packed = []
-        for p in live:
-            st = self.state[p]
-            for name in ("exp_avg", "exp_avg_sq"):
-                if name in st and st[name].dtype == torch.float8_e4m3fn:
-                    st[name] = fp8_state.dequantize(st, name, fp8_state.STATES[name], codec=self.codec).to(p.dtype)
-            packed.append(st)
-        super()._adamw_step(group, lr)
-        for st in packed:
-            for name in ("exp_avg", "exp_avg_sq"):
-                value = st.pop(name)
-                fp8_state.quantize_(st, name, value.float(), fp8_state.STATES[name], torch.float8_e4m3fn,
-                                    self.expand_min, codec=self.codec, div_mode=self.fp8_div)
+        """One fused pass per parameter dtype: decode both moments, AdamW in fp32, encode them again."""
+        beta1, beta2 = group["betas"]
+        by_dtype = self._adamw_collect(group)
+        if not by_dtype:
+            return
+        lib = _lib.load()
+        fmt = _lib.STATE_FP8_EXPAND if self.codec == "expand" else _lib.STATE_FP8_ABSMAX
+        self._mark("begin")
+        for dtype, items in by_dtype.items():
+            segs = (_lib.AdamWFp8Seg * len(items))()
+            for k, (p, g, st) in enumerate(items):
+                if st["exp_avg"].dtype != torch.float8_e4m3fn:      # state restored from a non-FP8 checkpoint
+                    for name in ("exp_avg", "exp_avg_sq"):
+                        value = st.pop(name)
+                        fp8_state.quantize_(st, name, value.float(), fp8_state.STATES[name], torch.float8_e4m3fn,
+                                            self.expand_min, codec=self.codec, div_mode=self.fp8_div)
+                s = segs[k]
+                s.param, s.grad = p.data.data_ptr(), g.data_ptr()
+                s.exp_avg, s.exp_avg_sq = st["exp_avg"].data_ptr(), st["exp_avg_sq"].data_ptr()
+                s.scale_exp_avg, s.scale_exp_avg_sq = st["scale_exp_avg"].data_ptr(), st["scale_exp_avg_sq"].data_ptr()
+                s.expand_exp_avg = _lib.ptr(st.get("expand_exp_avg"))
+                s.sqrt_minmax_exp_avg = _lib.ptr(st.get("sqrt_minmax_exp_avg"))
+                s.expand_exp_avg_sq = _lib.ptr(st.get("expand_exp_avg_sq"))
+                s.sqrt_minmax_exp_avg_sq = _lib.ptr(st.get("sqrt_minmax_exp_avg_sq"))
+                s.numel = p.numel()
+                s.step = st["step"]
+            with torch.cuda.device(items[0][0].device):
+                _lib.check(lib.mmb_adamw_fp8_step(segs, len(items), _lib.dtype_code(dtype), fmt, self.fp8_div, lr,
+                                                  beta1, beta2, group["weight_decay"], group["eps"],
+                                                  self.expand_min, _lib.stream_ptr()), "adamw_fp8_step")
+        self._mark("adamw")
 
     def load_state_dict(self, state_dict):
         # keep FP8 payloads and fp32 side arrays of the AdamW moments out of torch's dtype cast

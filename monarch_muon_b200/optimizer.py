@@ -435,8 +435,15 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                 sl["event"] = ev
 
     # ----------------------------------------------------------------- AdamW
-    def _adamw_step(self, group, lr: float) -> None:
-        beta1, beta2 = group["betas"]
+    def _adamw_new_state(self, p, state) -> None:
+        """Lazy state of one AdamW parameter (monarch_muon.py:181-185)."""
+        state["step"] = 0
+        state["exp_avg"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+        state["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+
+    def _adamw_collect(self, group):
+        """Parameters of the AdamW group that step now, by dtype: (parameter, gradient, state) with the
+        state created and its step count already incremented; host-fed gradients are copied in first."""
         by_dtype: "OrderedDict[torch.dtype, list]" = OrderedDict()
         host = self._host
         if host is not None:
@@ -456,9 +463,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
             _lib.require_cuda(p)
             state = self.state[p]
             if len(state) == 0:
-                state["step"] = 0
-                state["exp_avg"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
-                state["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+                self._adamw_new_state(p, state)
             state["step"] += 1
             g = p.grad
             if g.dtype != p.dtype:
@@ -468,6 +473,11 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
             if not p.data.is_contiguous():
                 raise ValueError("AdamW parameters must be contiguous")
             by_dtype.setdefault(p.dtype, []).append((p, g, state))
+        return by_dtype
+
+    def _adamw_step(self, group, lr: float) -> None:
+        beta1, beta2 = group["betas"]
+        by_dtype = self._adamw_collect(group)
         if not by_dtype:
             return
         lib = _lib.load()

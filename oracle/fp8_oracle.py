@@ -202,3 +202,33 @@ def expand_momentum_step(codes_u8, scale, expand, sqrt_mm, grad, beta: float, ex
     m = m + grad.reshape(-1).to(torch.float32)
     c, s, e, q = expand_quant(m, signed=True, expand_min=expand_min)
     return c, s, e, q, m
+
+
+def adamw_fp8_step(p, grad, m_state, v_state, step: int, *, lr, betas, weight_decay, eps, codec: str = "expand",
+                   expand_min: int = 16):
+    """One AdamW step with both moments held in FP8: what CoatStateMonarchMuon.step does to an AdamW
+    parameter (coat_state_muon.py:126-139): dequantise exp_avg (signed) and exp_avg_sq (unsigned) to fp32,
+    run the reference's AdamW (monarch_muon.py:186-201: decay first, eps after sqrt(v)/sqrt(bc2)) with
+    those fp32 moments, quantise them again.  `p` is updated in place in its own dtype; `m_state` and
+    `v_state` are tuples (codes, scale[, expand, sqrt_minmax]).  Returns (m_state', v_state', m_fp32, v_fp32)."""
+    import math
+    beta1, beta2 = betas
+    if codec == "expand":
+        m = expand_dequant(*m_state, signed=True).view(p.shape)
+        v = expand_dequant(*v_state, signed=False).view(p.shape)
+    else:
+        m = absmax_dequant(*m_state).view(p.shape)
+        v = absmax_dequant(*v_state).view(p.shape)
+    g32 = grad.to(torch.float32)
+    if weight_decay > 0:
+        p.mul_(1.0 - lr * weight_decay)
+    m.mul_(beta1).add_(g32, alpha=1.0 - beta1)
+    v.mul_(beta2).addcmul_(g32, g32, value=1.0 - beta2)
+    bc1 = 1.0 - beta1 ** step
+    bc2 = 1.0 - beta2 ** step
+    denom = (v.sqrt() / math.sqrt(bc2)).add_(eps)
+    p.copy_(p.to(torch.float32).addcdiv_(m, denom, value=-(lr / bc1)))
+    if codec == "expand":
+        return (expand_quant(m, signed=True, expand_min=expand_min), expand_quant(v, signed=False, expand_min=expand_min),
+                m, v)
+    return absmax_quant(m), absmax_quant(v), m, v

@@ -47,11 +47,13 @@ def test_struct_layouts_match_the_header():
     assert ctypes.sizeof(_lib.AdamWSeg) == 5 * 8 + 8
     assert ctypes.sizeof(_lib.GradSeg) == 2 * 8 + 8
     assert ctypes.sizeof(_lib.MasterUpdateSeg) == 4 * 8
+    assert ctypes.sizeof(_lib.AdamWFp8Seg) == 11 * 8 + 8
     assert ctypes.sizeof(_lib.MasterAdamWSeg) == 6 * 8 + 8
     text = open(HEADER).read()
     for struct, cls in (("mmb_momentum_seg", _lib.MomentumSeg), ("mmb_update_seg", _lib.UpdateSeg),
                         ("mmb_adamw_seg", _lib.AdamWSeg), ("mmb_grad_seg", _lib.GradSeg),
                         ("mmb_master_update_seg", _lib.MasterUpdateSeg),
+                        ("mmb_adamw_fp8_seg", _lib.AdamWFp8Seg),
                         ("mmb_master_adamw_seg", _lib.MasterAdamWSeg)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (struct, struct), text, flags=re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)

@@ -384,3 +384,54 @@ def test_edge_cases_zero_nan_and_empty_groups():
     codes = opt.state[p]["momentum_buffer"].view(torch.uint8).cpu().reshape(-1, 128)
     assert torch.all(codes[0] == codes[0, 0]) and int(codes[0, 0]) != 0x7F      # untouched group: all equal finite codes
     assert _lib.read_status(torch.device("cuda", 0)) == 0
+
+
+@pytest.mark.parametrize("codec", ["expand", "absmax"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_fp8_adamw_against_oracle(codec, dtype):
+    """CoatStateMonarchMuon's AdamW group: both moments stay E4M3 between steps and one kernel decodes,
+    steps and re-encodes them.  Against the oracle's dequantise -> AdamW with fp32 moments -> quantise
+    (the reference's sequence), three steps, a tensor with a ragged tail and a short vector."""
+    from monarch_muon_b200 import CoatStateMonarchMuon
+    from oracle import fp8_oracle
+    gen = torch.Generator().manual_seed(41)
+    shapes = [(300, 77), (64,), (128 * 40,)]
+    w = [(0.05 * torch.randn(s, generator=gen)).to(dtype) for s in shapes]
+    ours = [torch.nn.Parameter(t.clone().cuda()) for t in w]
+    ref = [t.clone() for t in w]
+    hyper = dict(lr=3e-3, betas=(0.9, 0.95), weight_decay=0.1, eps=1e-8)
+    opt = CoatStateMonarchMuon([], ours, lr=hyper["lr"], adamw_betas=hyper["betas"],
+                               adamw_weight_decay=hyper["weight_decay"], adamw_eps=hyper["eps"], codec=codec)
+    nside = 3 if codec == "expand" else 1
+    zero_state = lambda n: (torch.zeros(n, dtype=torch.uint8),) + tuple(torch.ones(-(-n // 128)) for _ in range(nside))
+    states = [(zero_state(t.numel()), zero_state(t.numel())) for t in w]
+    for step in range(1, 4):
+        grads = [(1e-2 * torch.randn(s, generator=gen) * torch.logspace(-2, 0, int(torch.Size(s).numel())).view(s)).to(dtype)
+                 for s in shapes]
+        for p, g in zip(ours, grads):
+            p.grad = g.cuda()
+        opt.step()
+        for i, (p, r, g) in enumerate(zip(ours, ref, grads)):
+            ms, vs, m32, v32 = fp8_oracle.adamw_fp8_step(r, g, states[i][0], states[i][1], step, codec=codec, **hyper)
+            st = opt.state[p]
+            assert st["exp_avg"].dtype == torch.float8_e4m3fn and st["exp_avg_sq"].dtype == torch.float8_e4m3fn
+            assert st["step"] == step
+            assert relf(p.data.float(), r.float()) < (1e-6 if dtype == torch.float32 else 4e-3), (step, i)
+            for name, want, signed in (("exp_avg", ms, True), ("exp_avg_sq", vs, False)):
+                codes = st[name].view(torch.uint8).cpu().view(-1)
+                if codec == "absmax" and step == 1:
+                    # from exact zeros both sides do the same fp32 arithmetic: scales to the last bit or two
+                    # (FMA vs separate multiply-add), codes equal except on rounding boundaries
+                    assert torch.allclose(st[f"scale_{name}"].cpu(), want[1], rtol=1e-6)
+                assert (codes != want[0]).float().mean() < 2e-2, (step, i, name)
+                back = fp8_oracle.expand_dequant(codes, *[st[f"{k}_{name}"].cpu() for k in ("scale", "expand", "sqrt_minmax")],
+                                                 signed=signed) if codec == "expand" else \
+                    fp8_oracle.absmax_dequant(codes, st[f"scale_{name}"].cpu())
+                exact = m32 if name == "exp_avg" else v32
+                assert relf(back, exact.view(-1)) < 0.08, (step, i, name)          # FP8 resolution
+            # carry OUR state into the oracle's next step so that single-step arithmetic is compared,
+            # not the drift of two FP8 trajectories
+            pick = lambda name: (st[name].view(torch.uint8).cpu().view(-1),) + tuple(
+                st[f"{k}_{name}"].cpu() for k in (("scale", "expand", "sqrt_minmax") if codec == "expand" else ("scale",)))
+            states[i] = (pick("exp_avg"), pick("exp_avg_sq"))
+            r.copy_(p.data.cpu())
