@@ -241,6 +241,8 @@ def main():
     ap.add_argument("--fp8-elems", type=int, default=1_600_000_000)
     ap.add_argument("--comm-sms", type=int, default=0, help="SMs left to NCCL during the sharded step")
     ap.add_argument("--chunks", type=int, default=4, help="pipeline chunks of the sharded (multi-GPU) step")
+    ap.add_argument("--dynamic-schedule", type=int, default=0, choices=[0, 1],
+                    help="Newton-Schulz GEMM tiles drawn from a counter (1) or fixed round-robin (0)")
     ap.add_argument("--state-format", default="fp8_absmax", choices=["fp8_absmax", "fp8_expand", "param", "coat"],
                     help="momentum state: FP8 absmax (headline), COAT range expansion, or the parameter dtype")
     ap.add_argument("--ns-max-batch", type=int, default=256, help="blocks per Newton-Schulz slice")
@@ -281,6 +283,8 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     from monarch_muon_b200 import MonarchMuonOptimizer, _lib
+    if args.dynamic_schedule:
+        _lib.set_gemm_schedule(True)
     if args.case == "gemm":
         return run_gemm_comparison(args, dev)
     if args.case != "step":

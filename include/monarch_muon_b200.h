@@ -66,6 +66,11 @@ const char* mmb_last_error(void);
 /* Size every kernel's grid for at most n SMs (0 = all).  Leaving a few SMs
  * free lets communication kernels (NCCL) run beside the persistent GEMMs. */
 int mmb_set_sm_limit(int n);
+/* Tile schedule of the Newton-Schulz GEMMs (no counterpart in the reference).  0 (default): every CTA pair
+ * takes tiles round-robin, fixed at launch.  1: pairs draw tile numbers from a counter in the workspace, so
+ * a pair whose SMs are shared with another kernel (a collective running beside the step) takes fewer tiles
+ * instead of delaying the launch.  Results do not depend on the schedule. */
+int mmb_set_gemm_schedule(int dynamic);
 /* Kernels launched by this library in this process so far. */
 int64_t mmb_launch_count(void);
 

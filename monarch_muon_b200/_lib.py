@@ -65,6 +65,7 @@ SYMBOLS = {
     "mmb_last_error": (C.c_char_p, []),
     "mmb_launch_count": (_i64, []),
     "mmb_set_sm_limit": (_i, [_i]),
+    "mmb_set_gemm_schedule": (_i, [_i]),
     "mmb_momentum_scratch_floats": (_i64, [C.POINTER(MomentumSeg), _i]),
     "mmb_momentum_step": (_i, [C.POINTER(MomentumSeg), _i, _i, _i, _i, _f, _f, _i, _vp, _vp, _i64, _vp]),
     "mmb_momentum_static_max_floats": (_i64, []),
@@ -166,6 +167,11 @@ def read_status(device: torch.device, reset: bool = True) -> int:
 def launch_count() -> int:
     """Kernels launched by the library in this process so far."""
     return int(load().mmb_launch_count())
+
+
+def set_gemm_schedule(dynamic: bool) -> None:
+    """Newton-Schulz GEMM tiles: drawn from a counter (True) or fixed round-robin (False, default)."""
+    check(load().mmb_set_gemm_schedule(1 if dynamic else 0), "set_gemm_schedule")
 
 
 def set_sm_limit(n: int) -> None:

@@ -30,6 +30,10 @@ void set_device_grad_scale(const float* p) { t_grad_scale = p; }
 static std::atomic<int> g_sm_limit{0};
 void set_sm_limit(int n) { g_sm_limit.store(n < 0 ? 0 : n, std::memory_order_relaxed); }
 
+static std::atomic<int> g_gemm_dynamic{0};
+void set_gemm_schedule_dynamic(bool on) { g_gemm_dynamic.store(on ? 1 : 0, std::memory_order_relaxed); }
+bool gemm_schedule_dynamic() { return g_gemm_dynamic.load(std::memory_order_relaxed) != 0; }
+
 int sm_count() {
   static thread_local int cached_dev = -1;
   static thread_local int cached_sms = 0;
@@ -59,6 +63,11 @@ int mmb_set_device_grad_scale(const float* scale_dev) {
 
 int mmb_set_sm_limit(int n) {
   mmb::set_sm_limit(n);
+  return MMB_OK;
+}
+
+int mmb_set_gemm_schedule(int dynamic) {
+  mmb::set_gemm_schedule_dynamic(dynamic != 0);
   return MMB_OK;
 }
 

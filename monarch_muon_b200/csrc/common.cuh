@@ -37,6 +37,11 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 int sm_count();
 void set_sm_limit(int n);
 
+// Tile schedule of the Newton-Schulz GEMMs: static round-robin (default) or drawn from a counter
+// (mmb_set_gemm_schedule).
+void set_gemm_schedule_dynamic(bool on);
+bool gemm_schedule_dynamic();
+
 // Device scalar that the momentum and AdamW kernels multiply gradients by (mmb_set_device_grad_scale),
 // or null.  Thread local, like the error message.
 const float* device_grad_scale();
@@ -52,6 +57,8 @@ enum : int32_t {
   STATUS_WAIT_MMA_FULL = 0x102,        // MMA issuer waited too long for operands
   STATUS_WAIT_MMA_TMEM_EMPTY = 0x103,  // MMA issuer waited too long for a drained accumulator
   STATUS_WAIT_EPI_TMEM_FULL = 0x104,   // epilogue waited too long for an accumulator
+  STATUS_WAIT_SCHED_FULL = 0x105,      // a role waited too long for its next tile number
+  STATUS_WAIT_SCHED_EMPTY = 0x106,     // the tile scheduler waited too long for a slot to be returned
 };
 
 }  // namespace mmb

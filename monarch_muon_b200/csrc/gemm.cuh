@@ -19,6 +19,7 @@ struct GemmCall {
   float alpha, diag;
   const float* inv_norm;  // per batch, may be null
   int sigma_pow;          // sigma_b = inv_norm[b]^sigma_pow, 0..2
+  int* sched = nullptr;   // two zeroed ints in device memory for the dynamic tile schedule (null: static schedule)
 };
 
 int gemm_tcgen05(const GemmCall& g, int32_t* status, cudaStream_t st);

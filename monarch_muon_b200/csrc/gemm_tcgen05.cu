@@ -74,6 +74,8 @@ constexpr int EPI_WARP_BYTES = 32 * 64 * 2;   // one epilogue warp's staging buf
 constexpr int EPI_BYTES = NUM_EPI_WARPS * EPI_WARP_BYTES;
 constexpr int SYM_SHIFT = 8;                  // symmetric storage granularity: 256
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;
+constexpr int SCHED_DEPTH = 4;                // tile numbers a pair may hold ahead of its consumers (dynamic schedule)
+constexpr int SCHED_CONSUMERS_PER_CTA = 2 * PRODUCERS_PER_OPERAND + NUM_EPI_WARPS;  // plus the MMA thread in the even CTA
 
 template <int BN, bool PAIR>
 struct Cfg {
@@ -95,6 +97,7 @@ struct GemmArgs {
   const float* inv_norm;
   int sigma_pow;
   int32_t* status;
+  int* sched;  // dynamic schedule: [0] next tile number, [1] pairs that have seen the end; both 0 at launch
 };
 
 // ------------------------------------------------------------------ PTX glue
@@ -120,6 +123,22 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "r"(bar), "r"(parity)
       : "memory");
   return done;
+}
+// Same test with acquire semantics at cluster scope: for barriers whose arrival publishes data written
+// into this CTA's shared memory by the peer CTA.
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done;
+}
+__device__ __forceinline__ void st_shared_cluster_s32(uint32_t cluster_addr, int v) {
+  asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -152,11 +171,12 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
 // thread for a while), because reading a timer on every miss sits on the
 // critical path of each producer/consumer hand-off.  The limit is counted in SM
 // cycles (clock64): 4e9 cycles is about two seconds at 2 GHz.
+template <bool CLUSTER_ACQUIRE = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
                                           int32_t code) {
   long long t0 = 0;
   for (uint32_t spin = 1;; ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (CLUSTER_ACQUIRE ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
     if ((spin & 255u) == 0u) {
       if (*abort_flag) return false;
       const long long now = clock64();
@@ -291,8 +311,27 @@ __device__ __forceinline__ void tile_coords(long long t, const GemmArgs& a, int&
   }
 }
 
+// Dynamic schedule (pairs only).  Lane 0 of warp 1 of the odd CTA - idle otherwise - draws tile numbers
+// from a global counter and publishes each into a ring of SCHED_DEPTH slots in both CTAs' shared memory
+// (own slot: plain store + arrive; peer's slot: st.shared::cluster + arrive.release.cluster).  Every
+// consumer (4 producer lanes and 8 epilogue warps per CTA, the MMA lane of the even CTA) walks the ring
+// with its own cursor and returns each slot by arriving at the odd CTA's `sched_empty` barrier.  A pair
+// that starts late or shares its SMs with another kernel simply draws fewer tiles.  -1 ends the walk.
+struct TileCursor {
+  uint32_t n = 0;  // tiles drawn so far by this consumer
+};
+__device__ __forceinline__ long long draw_tile(TileCursor& c, uint32_t sched_full, uint32_t sched_empty,
+                                               const volatile int* slots, volatile int* abort_flag, int32_t* status) {
+  const uint32_t q = c.n % SCHED_DEPTH, ph = (c.n / SCHED_DEPTH) & 1u;
+  if (!mbar_wait<true>(sched_full + 8 * q, ph, abort_flag, status, STATUS_WAIT_SCHED_FULL)) return -1;
+  const int t = slots[q];
+  mbar_arrive_cluster(mapa(sched_empty + 8 * q, 1));   // the ring's owner is the odd CTA (also when that is us)
+  ++c.n;
+  return t;
+}
+
 // -------------------------------------------------------------------- kernel
-template <int BN, bool PAIR>
+template <int BN, bool PAIR, bool DYN = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__ CUtensorMap map_a_mn,
             const __grid_constant__ CUtensorMap map_b_k, const __grid_constant__ CUtensorMap map_b_mn,
@@ -314,6 +353,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
   const uint32_t tmem_empty_bar = tmem_full_bar + 16;       // 2 (pair: only the even CTA's are used)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // dynamic schedule: two rings of barriers and the slots, behind the words above
+  const uint32_t sched_full = bars_addr + 8 * (2 * STAGES + 4) + 16;
+  const uint32_t sched_empty = sched_full + 8 * SCHED_DEPTH;
+  volatile int* sched_slots = reinterpret_cast<volatile int*>(bars + 2 * STAGES + 4 + 2 + 2 * SCHED_DEPTH);
+  static_assert(!DYN || PAIR, "the dynamic schedule is built on the idle warp of a pair's odd CTA");
+  static_assert(8 * (2 * STAGES + 4) + 16 + 16 * SCHED_DEPTH + 4 * SCHED_DEPTH <= 256, "barrier area overflow");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -333,6 +378,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
     for (int i = 0; i < 2; ++i) {
       mbar_init(tmem_full_bar + 8 * i, 1);
       mbar_init(tmem_empty_bar + 8 * i, (PAIR ? 2 : 1) * NUM_EPI_WARPS);  // one arrival per epilogue warp (of both CTAs)
+    }
+    if (DYN) {
+      for (int i = 0; i < SCHED_DEPTH; ++i) {
+        mbar_init(sched_full + 8 * i, 1);
+        mbar_init(sched_empty + 8 * i, 2 * SCHED_CONSUMERS_PER_CTA + 1);
+      }
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -373,7 +424,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
       const uint32_t bytes = is_a ? A_TILE_BYTES : C::B_TILE_BYTES;
       const CUtensorMap* map_k = is_a ? &map_a_k : &map_b_k;
       const CUtensorMap* map_mn = is_a ? &map_a_mn : &map_b_mn;
-      for (long long t = first_tile; ok && t < args.total_tiles; t += tile_step) {
+      TileCursor cursor;
+      for (long long t = DYN ? draw_tile(cursor, sched_full, sched_empty, sched_slots, abort_flag, args.status) : first_tile;
+           ok && t >= 0 && t < args.total_tiles;
+           t = DYN ? draw_tile(cursor, sched_full, sched_empty, sched_slots, abort_flag, args.status) : t + tile_step) {
         int b, m0, n0;
         tile_coords<BN, TILE_M>(t, args, b, m0, n0);
         const int r_tile = is_a ? m0 : n0;                       // decides K-major vs mirrored fetch
@@ -424,7 +478,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
       uint32_t stage = 0, phase = 0;
       uint32_t local = 0;
       bool ok = true;
-      for (long long t = first_tile; ok && t < args.total_tiles; t += tile_step, ++local) {
+      TileCursor cursor;
+      for (long long t = DYN ? draw_tile(cursor, sched_full, sched_empty, sched_slots, abort_flag, args.status) : first_tile;
+           ok && t >= 0 && t < args.total_tiles;
+           t = DYN ? draw_tile(cursor, sched_full, sched_empty, sched_slots, abort_flag, args.status) : t + tile_step, ++local) {
         int b, m0, n0;
         tile_coords<BN, TILE_M>(t, args, b, m0, n0);
         const uint32_t acc = local & 1u;
@@ -464,6 +521,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
           if (PAIR) tcgen05_commit_pair(tmem_full_bar + 8 * acc); else tcgen05_commit(tmem_full_bar + 8 * acc);
         }
       }
+    } else if (DYN && lane == 0 && cta_rank == 1) {
+      // ------------------------------------------------------ tile scheduler
+      const int total = static_cast<int>(args.total_tiles);
+      for (uint32_t i = 0;; ++i) {
+        const uint32_t q = i % SCHED_DEPTH, ph = (i / SCHED_DEPTH) & 1u;
+        // every consumer of both CTAs has read the slot's previous tile (immediate on the first lap)
+        if (!mbar_wait<true>(sched_empty + 8 * q, ph ^ 1u, abort_flag, args.status, STATUS_WAIT_SCHED_EMPTY)) break;
+        const int drawn = atomicAdd(args.sched, 1);
+        const int tile = drawn < total ? drawn : -1;
+        sched_slots[q] = tile;
+        st_shared_cluster_s32(mapa(smem_u32(const_cast<int*>(sched_slots + q)), 0), tile);
+        mbar_arrive(sched_full + 8 * q);
+        mbar_arrive_cluster(mapa(sched_full + 8 * q, 0));
+        if (tile < 0) {
+          // The pair that sees the end last (no draw can follow it) rearms the counters for the next launch.
+          const int pairs = static_cast<int>(gridDim.x >> 1);
+          if (atomicAdd(args.sched + 1, 1) == pairs - 1) {
+            args.sched[0] = 0;
+            args.sched[1] = 0;
+            __threadfence();
+          }
+          break;
+        }
+      }
     }
   } else {
     // ------------------------------------------------------------ epilogue
@@ -479,7 +560,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
     const uint32_t my_buf_addr = epi_addr + ew * EPI_WARP_BYTES;
     uint32_t local = 0;
     bool ok = true;
-    for (long long t = first_tile; ok && t < args.total_tiles; t += tile_step, ++local) {
+    TileCursor cursor;
+    auto next_tile = [&](long long prev) -> long long {
+      if (!DYN) return prev < 0 ? first_tile : prev + tile_step;
+      long long t = 0;
+      if (lane == 0) t = draw_tile(cursor, sched_full, sched_empty, sched_slots, abort_flag, args.status);
+      return __shfl_sync(0xffffffffu, t, 0);
+    };
+    for (long long t = next_tile(-1); ok && t >= 0 && t < args.total_tiles; t = next_tile(t), ++local) {
       int b, m0, n0;
       tile_coords<BN, TILE_M>(t, args, b, m0, n0);
       m0 += static_cast<int>(cta_rank) * BM;  // this CTA's half of a pair tile
@@ -622,9 +710,9 @@ int operand_maps(CUtensorMap* k_map, CUtensorMap* mn_map, const void* base, int 
   return MMB_OK;
 }
 
-template <int BN, bool PAIR>
+template <int BN, bool PAIR, bool DYN = false>
 int launch(const CUtensorMap* maps, const GemmArgs& args, int grid, cudaStream_t st) {
-  auto kern = gemm_kernel<BN, PAIR>;
+  auto kern = gemm_kernel<BN, PAIR, DYN>;
   constexpr int smem = Cfg<BN, PAIR>::SMEM_BYTES;
   MMB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   cudaLaunchConfig_t cfg = {};
@@ -719,12 +807,17 @@ int gemm_tcgen05(const GemmCall& g, int32_t* status, cudaStream_t st) {
   args.alpha = g.alpha; args.diag = g.diag;
   args.inv_norm = g.inv_norm; args.sigma_pow = g.inv_norm != nullptr ? g.sigma_pow : 0;
   args.status = status;
+  args.sched = nullptr;
   const int sms = sm_count();
   if (sms <= 0) return fail(MMB_ERR_CUDA, "tcgen05 GEMM: no CUDA device");
   if (args.total_tiles == 0) return MMB_OK;
   if (pair) {
     const long long pairs = sms / 2;
     const int grid = 2 * static_cast<int>(args.total_tiles < pairs ? args.total_tiles : pairs);
+    if (g.sched != nullptr && gemm_schedule_dynamic() && args.total_tiles < (1ll << 30)) {
+      args.sched = g.sched;
+      return launch<256, true, true>(maps, args, grid, st);
+    }
     return launch<256, true>(maps, args, grid, st);
   }
   const int grid = static_cast<int>(args.total_tiles < sms ? args.total_tiles : sms);

@@ -169,7 +169,7 @@ __global__ void inv_norm_kernel(const float* __restrict__ sumsq, float* __restri
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct NsLayout {
-  size_t gram, poly, xa, xb, inv, sumsq, total;
+  size_t gram, poly, xa, xb, inv, sumsq, sched, total;
 };
 
 NsLayout ns_layout(int batch, int rows, int cols) {
@@ -183,6 +183,7 @@ NsLayout ns_layout(int batch, int rows, int cols) {
   l.xb = at;   at = align_up(at + static_cast<size_t>(batch) * blk * 2, 1024);
   l.inv = at;  at = align_up(at + static_cast<size_t>(batch) * 4, 1024);
   l.sumsq = at; at = align_up(at + static_cast<size_t>(batch) * 4, 1024);
+  l.sched = at; at += 1024;  // counters of the dynamic tile schedule
   l.total = at;
   return l;
 }
@@ -230,6 +231,11 @@ int mmb_newton_schulz(const void* x_dev, void* out_dev, const float* block_sumsq
   __nv_bfloat16* xb = reinterpret_cast<__nv_bfloat16*>(ws + l.xb);
   float* inv = reinterpret_cast<float*>(ws + l.inv);
   float* sumsq = reinterpret_cast<float*>(ws + l.sumsq);
+  int* sched = nullptr;
+  if (backend == MMB_NS_TCGEN05 && gemm_schedule_dynamic()) {
+    sched = reinterpret_cast<int*>(ws + l.sched);
+    MMB_CUDA_CHECK(cudaMemsetAsync(sched, 0, 2 * sizeof(int), st));  // each launch leaves them at zero again
+  }
 
   const float* ss = block_sumsq_dev;
   if (ss == nullptr) {
@@ -256,17 +262,17 @@ int mmb_newton_schulz(const void* x_dev, void* out_dev, const float* block_sumsq
     int rc;
     // Gram: wide X X^T (K-major operands, contraction n); tall Y^T Y (MN-major operands, contraction rows)
     const int xmode = tall ? GEMM_MN : GEMM_K;
-    GemmCall gram_call{cur, cur, gram, batch, m, m, n, xmode, xmode, 1, 1.0f, beta, inv, first ? 2 : 0};
+    GemmCall gram_call{cur, cur, gram, batch, m, m, n, xmode, xmode, 1, 1.0f, beta, inv, first ? 2 : 0, sched};
     if ((rc = gemm_dispatch(backend, gram_call, status_dev, st)) != MMB_OK) return rc;
     // Poly: Pp = c Ah Ah + kappa I
-    GemmCall poly_call{gram, gram, poly, batch, m, m, m, GEMM_SYM, GEMM_SYM, 1, c, kappa, nullptr, 0};
+    GemmCall poly_call{gram, gram, poly, batch, m, m, m, GEMM_SYM, GEMM_SYM, 1, c, kappa, nullptr, 0, sched};
     if ((rc = gemm_dispatch(backend, poly_call, status_dev, st)) != MMB_OK) return rc;
     // Apply: wide X' = Pp X (B = X stored [K][N]); tall Y' = Y Pp (A = Y, B = Pp by symmetry)
     if (!tall) {
-      GemmCall ap{poly, cur, nxt, batch, m, n, m, GEMM_SYM, GEMM_MN, 0, 1.0f, 0.0f, inv, first ? 1 : 0};
+      GemmCall ap{poly, cur, nxt, batch, m, n, m, GEMM_SYM, GEMM_MN, 0, 1.0f, 0.0f, inv, first ? 1 : 0, sched};
       rc = gemm_dispatch(backend, ap, status_dev, st);
     } else {
-      GemmCall ap{cur, poly, nxt, batch, n, m, m, GEMM_K, GEMM_SYM, 0, 1.0f, 0.0f, inv, first ? 1 : 0};
+      GemmCall ap{cur, poly, nxt, batch, n, m, m, GEMM_K, GEMM_SYM, 0, 1.0f, 0.0f, inv, first ? 1 : 0, sched};
       rc = gemm_dispatch(backend, ap, status_dev, st);
     }
     if (rc != MMB_OK) return rc;

@@ -48,12 +48,15 @@ class ShardedMonarchMuon:
         that steps the owned views; defaults to MonarchMuonOptimizer (CUDA).
     comm_sms : SMs kept free of this library's kernels during the step, for the
         collectives' kernels.
+    dynamic_schedule : let the Newton-Schulz GEMMs draw their tiles from a counter
+        during the step, so that SMs taken by a collective's kernels cost those
+        SMs' share of the work instead of stalling a whole launch.
     """
 
     def __init__(self, muon_params, adamw_params, *, process_group=None, lr: float = 5e-3, momentum: float = 0.95,
                  adamw_betas=(0.9, 0.95), adamw_weight_decay: float = 0.1, adamw_eps: float = 1e-8,
                  n_chunks: int = 4, average: bool = True, local_factory=None, second_group: bool = True,
-                 comm_sms: int = 0, **local_kwargs):
+                 comm_sms: int = 0, dynamic_schedule: bool = False, **local_kwargs):
         if not dist.is_initialized():
             raise RuntimeError("ShardedMonarchMuon needs an initialised torch.distributed process group")
         self.group = process_group
@@ -80,6 +83,7 @@ class ShardedMonarchMuon:
         # SMs left free during the step so that NCCL's kernels can run beside the persistent GEMMs
         # (which otherwise occupy every SM and serialise with them)
         self.comm_sms = comm_sms
+        self.dynamic_schedule = dynamic_schedule
         n = self.plan.total_elems
         self.w_arena = torch.zeros(n, dtype=self.dtype, device=self.device)
         self.g_arena = torch.zeros(n, dtype=self.dtype, device=self.device)
@@ -171,6 +175,9 @@ class ShardedMonarchMuon:
             from . import _lib
             total = torch.cuda.get_device_properties(self.device).multi_processor_count
             _lib.set_sm_limit(max(2, total - self.comm_sms))
+        if self.dynamic_schedule and self.backend == "nccl":
+            from . import _lib
+            _lib.set_gemm_schedule(True)
         rs = []
         for k in range(nchunks):
             g_whole, g_mine, _, _ = self.chunk_views(k)
@@ -200,6 +207,9 @@ class ShardedMonarchMuon:
         if self.comm_sms > 0 and self.backend == "nccl":
             from . import _lib
             _lib.set_sm_limit(0)
+        if self.dynamic_schedule and self.backend == "nccl":
+            from . import _lib
+            _lib.set_gemm_schedule(False)
 
     def zero_grad(self, set_to_none: bool = False):
         """Gradients are arena views and stay allocated; they are zeroed in place."""

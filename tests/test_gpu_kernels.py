@@ -165,6 +165,26 @@ def test_newton_schulz_in_place_and_sliced(mm):
     assert torch.equal(a, z)                       # run-to-run bit reproducibility
 
 
+def test_dynamic_tile_schedule_gives_the_same_bits(mm):
+    """Newton-Schulz with tiles drawn from a counter instead of the fixed round-robin: every tile is
+    computed exactly once by the same code, so the output is bit-identical; the counters rearm
+    themselves, so repeated calls and several shapes in a row work."""
+    lib = mm["lib"]
+    gen = torch.Generator(device="cuda").manual_seed(12)
+    stacks = [torch.empty(s, dtype=torch.bfloat16, device="cuda").normal_(0, 1, generator=gen)
+              for s in ((40, 1024, 1024), (3, 2752, 1024), (5, 1024, 2752), (2, 512, 256))]
+    ns = mm["ns"].newton_schulz_batched
+    want = [ns(x) for x in stacks]
+    lib.set_gemm_schedule(True)
+    try:
+        for rep in range(3):
+            for x, w in zip(stacks, want):
+                assert torch.equal(ns(x), w), (rep, tuple(x.shape))
+        assert lib.read_status(torch.device("cuda", torch.cuda.current_device())) == 0
+    finally:
+        lib.set_gemm_schedule(False)
+
+
 # ------------------------------------------------------------------ FP8 momentum
 @pytest.mark.parametrize("n,block", [(128 * 40 + 5, None), (4 * 128 * 128, 128 * 128), (2 * 344 * 128, 344 * 128),
                                      (1 << 22, 1 << 20), (17, None)])
