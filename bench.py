@@ -241,8 +241,9 @@ def main():
     ap.add_argument("--fp8-elems", type=int, default=1_600_000_000)
     ap.add_argument("--comm-sms", type=int, default=0, help="SMs left to NCCL during the sharded step")
     ap.add_argument("--chunks", type=int, default=4, help="pipeline chunks of the sharded (multi-GPU) step")
-    ap.add_argument("--dynamic-schedule", type=int, default=0, choices=[0, 1],
-                    help="Newton-Schulz GEMM tiles drawn from a counter (1) or fixed round-robin (0)")
+    ap.add_argument("--dynamic-schedule", type=int, default=None, choices=[0, 1],
+                    help="Newton-Schulz GEMM tiles drawn from a counter (1) or fixed round-robin (0); default: 1 in "
+                         "the sharded (multi-GPU) step, 0 on one GPU")
     ap.add_argument("--state-format", default="fp8_absmax", choices=["fp8_absmax", "fp8_expand", "param", "coat"],
                     help="momentum state: FP8 absmax (headline), COAT range expansion, or the parameter dtype")
     ap.add_argument("--ns-max-batch", type=int, default=256, help="blocks per Newton-Schulz slice")

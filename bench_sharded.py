@@ -52,7 +52,7 @@ def run_sharded(args, rank, world, local_rank, config, metric):
         p.grad = None
     opt = ShardedMonarchMuon(muon, adamw, lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95),
                              adamw_weight_decay=0.1, adamw_eps=1e-8, n_chunks=args.chunks, comm_sms=args.comm_sms,
-                             dynamic_schedule=bool(args.dynamic_schedule),
+                             dynamic_schedule=args.dynamic_schedule != 0,
                              state_format="fp8_absmax")
     gen = torch.Generator(device=dev).manual_seed(4321 + rank)           # each rank's own gradients
     opt.g_arena.normal_(0.0, 1e-3, generator=gen)
@@ -131,7 +131,7 @@ def run_sharded(args, rank, world, local_rank, config, metric):
                 "config": dict(config, parallelism=f"owner-computes dp{world}: bf16 grad reduce-scatter, local "
                                                    "momentum/Newton-Schulz/update/AdamW, weight all-gather; "
                                                    f"{args.chunks} chunks pipelined, {args.comm_sms} SMs left to NCCL, "
-                                                   f"{'dynamic' if args.dynamic_schedule else 'static'} GEMM tile schedule"),
+                                                   f"{'dynamic' if args.dynamic_schedule != 0 else 'static'} GEMM tile schedule"),
                 "phases_ms": {"step": ms, "compute_only": ms_compute, "communication_only": ms_comm,
                               "exposed_communication": max(0.0, ms - ms_compute)},
                 "roofline": {"kernel": "gemm_kernel (tcgen05 Newton-Schulz GEMMs)", "bound": "tensor",

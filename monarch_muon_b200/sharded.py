@@ -56,7 +56,7 @@ class ShardedMonarchMuon:
     def __init__(self, muon_params, adamw_params, *, process_group=None, lr: float = 5e-3, momentum: float = 0.95,
                  adamw_betas=(0.9, 0.95), adamw_weight_decay: float = 0.1, adamw_eps: float = 1e-8,
                  n_chunks: int = 4, average: bool = True, local_factory=None, second_group: bool = True,
-                 comm_sms: int = 0, dynamic_schedule: bool = False, **local_kwargs):
+                 comm_sms: int = 0, dynamic_schedule: bool = True, **local_kwargs):
         if not dist.is_initialized():
             raise RuntimeError("ShardedMonarchMuon needs an initialised torch.distributed process group")
         self.group = process_group
