@@ -66,6 +66,10 @@ const char* mmb_last_error(void);
 /* Size every kernel's grid for at most n SMs (0 = all).  Leaving a few SMs
  * free lets communication kernels (NCCL) run beside the persistent GEMMs. */
 int mmb_set_sm_limit(int n);
+/* Cap the grids of the bandwidth-bound kernels (momentum, update, AdamW) at n CTAs of 256 threads per SM
+ * (0 = default, 32).  With n = 1 they fit beside the persistent GEMM CTAs, so work issued on a second stream
+ * overlaps Newton-Schulz.  No counterpart in the reference. */
+int mmb_set_stream_ctas_per_sm(int n);
 /* Tile schedule of the Newton-Schulz GEMMs (no counterpart in the reference).  0 (default): every CTA pair
  * takes tiles round-robin, fixed at launch.  1: pairs draw tile numbers from a counter in the workspace, so
  * a pair whose SMs are shared with another kernel (a collective running beside the step) takes fewer tiles

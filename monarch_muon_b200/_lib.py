@@ -66,6 +66,7 @@ SYMBOLS = {
     "mmb_launch_count": (_i64, []),
     "mmb_set_sm_limit": (_i, [_i]),
     "mmb_set_gemm_schedule": (_i, [_i]),
+    "mmb_set_stream_ctas_per_sm": (_i, [_i]),
     "mmb_momentum_scratch_floats": (_i64, [C.POINTER(MomentumSeg), _i]),
     "mmb_momentum_step": (_i, [C.POINTER(MomentumSeg), _i, _i, _i, _i, _f, _f, _i, _vp, _vp, _i64, _vp]),
     "mmb_momentum_static_max_floats": (_i64, []),
@@ -167,6 +168,11 @@ def read_status(device: torch.device, reset: bool = True) -> int:
 def launch_count() -> int:
     """Kernels launched by the library in this process so far."""
     return int(load().mmb_launch_count())
+
+
+def set_stream_ctas_per_sm(n: int) -> None:
+    """Cap the grids of the bandwidth-bound kernels at n CTAs per SM (0 = default)."""
+    check(load().mmb_set_stream_ctas_per_sm(int(n)), "set_stream_ctas_per_sm")
 
 
 def set_gemm_schedule(dynamic: bool) -> None:

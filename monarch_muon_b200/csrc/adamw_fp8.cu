@@ -263,7 +263,7 @@ int mmb_adamw_fp8_step(const mmb_adamw_fp8_seg* segs, int nseg, int dtype, int s
     tab.unit_start[tab.nseg] = units;
     const long long warps_per_cta = THREADS / 32;
     long long want = (units + warps_per_cta - 1) / warps_per_cta;
-    const long long cap = static_cast<long long>(sms) * 8;
+    const long long cap = stream_grid_cap(sms) < static_cast<long long>(sms) * 8 ? stream_grid_cap(sms) : static_cast<long long>(sms) * 8;
     const int grid = static_cast<int>(want < cap ? (want < 1 ? 1 : want) : cap);
     const float em = static_cast<float>(expand_min);
 #define MMB_LAUNCH(F, T, D) \

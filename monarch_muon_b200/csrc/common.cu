@@ -34,6 +34,14 @@ static std::atomic<int> g_gemm_dynamic{0};
 void set_gemm_schedule_dynamic(bool on) { g_gemm_dynamic.store(on ? 1 : 0, std::memory_order_relaxed); }
 bool gemm_schedule_dynamic() { return g_gemm_dynamic.load(std::memory_order_relaxed) != 0; }
 
+static std::atomic<int> g_stream_ctas_per_sm{0};
+void set_stream_ctas_per_sm(int n) { g_stream_ctas_per_sm.store(n < 0 ? 0 : n, std::memory_order_relaxed); }
+bool stream_kernels_share_sms() { return g_stream_ctas_per_sm.load(std::memory_order_relaxed) > 0; }
+long long stream_grid_cap(int sms) {
+  const int n = g_stream_ctas_per_sm.load(std::memory_order_relaxed);
+  return static_cast<long long>(sms) * (n > 0 ? n : 32);
+}
+
 int sm_count() {
   static thread_local int cached_dev = -1;
   static thread_local int cached_sms = 0;
@@ -63,6 +71,11 @@ int mmb_set_device_grad_scale(const float* scale_dev) {
 
 int mmb_set_sm_limit(int n) {
   mmb::set_sm_limit(n);
+  return MMB_OK;
+}
+
+int mmb_set_stream_ctas_per_sm(int n) {
+  mmb::set_stream_ctas_per_sm(n);
   return MMB_OK;
 }
 

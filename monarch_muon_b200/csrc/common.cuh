@@ -37,6 +37,17 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 int sm_count();
 void set_sm_limit(int n);
 
+// Largest grid of the streaming (bandwidth-bound) kernels: 32 CTAs of 256 threads per SM by default,
+// fewer after mmb_set_stream_ctas_per_sm(n) - used when they run beside the persistent GEMMs, whose
+// CTAs leave room for one small CTA per SM.
+void set_stream_ctas_per_sm(int n);
+long long stream_grid_cap(int sms);
+
+// True while mmb_set_stream_ctas_per_sm() is in force: streaming kernels then ask for the same shared
+// memory carve-out as the persistent GEMMs (the maximum), because an SM cannot hold kernels of two
+// different carve-outs at once and would otherwise drain the GEMM CTA before admitting them.
+bool stream_kernels_share_sms();
+
 // Tile schedule of the Newton-Schulz GEMMs: static round-robin (default) or drawn from a counter
 // (mmb_set_gemm_schedule).
 void set_gemm_schedule_dynamic(bool on);
@@ -60,5 +71,16 @@ enum : int32_t {
   STATUS_WAIT_SCHED_FULL = 0x105,      // a role waited too long for its next tile number
   STATUS_WAIT_SCHED_EMPTY = 0x106,     // the tile scheduler waited too long for a slot to be returned
 };
+
+#ifdef __CUDACC__
+// Launch of a bandwidth-bound kernel (no dynamic shared memory) with the carve-out that fits the mode.
+template <typename... KArgs, typename... Args>
+inline void launch_stream_kernel(void (*kernel)(KArgs...), int grid, int threads, cudaStream_t st, Args... args) {
+  cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel), cudaFuncAttributePreferredSharedMemoryCarveout,
+                       stream_kernels_share_sms() ? static_cast<int>(cudaSharedmemCarveoutMaxShared)
+                                                  : static_cast<int>(cudaSharedmemCarveoutDefault));
+  kernel<<<grid, threads, 0, st>>>(args...);
+}
+#endif
 
 }  // namespace mmb

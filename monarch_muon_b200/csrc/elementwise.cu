@@ -269,7 +269,7 @@ clip_coef_kernel(const float* __restrict__ partials, int n, float max_norm, floa
 
 int grid_for(long long total_vecs, int sms) {
   long long want = (total_vecs + THREADS - 1) / THREADS;
-  long long cap = static_cast<long long>(sms) * 8 * 4;
+  long long cap = stream_grid_cap(sms);
   long long g = want < cap ? want : cap;
   return static_cast<int>(g < 1 ? 1 : g);
 }
@@ -305,9 +305,9 @@ int mmb_muon_update(const mmb_update_seg* segs, int nseg, int weight_dtype, floa
     tab.vec_start[tab.nseg] = vecs;
     const int grid = grid_for(vecs, sms);
     if (weight_dtype == MMB_BF16)
-      muon_update_kernel<__nv_bfloat16><<<grid, THREADS, 0, st>>>(tab, alpha);
+      launch_stream_kernel(muon_update_kernel<__nv_bfloat16>, grid, THREADS, st, tab, alpha);
     else
-      muon_update_kernel<float><<<grid, THREADS, 0, st>>>(tab, alpha);
+      launch_stream_kernel(muon_update_kernel<float>, grid, THREADS, st, tab, alpha);
     MMB_CUDA_CHECK(cudaGetLastError());
   count_launch();
   }
@@ -408,9 +408,9 @@ int mmb_adamw_step(const mmb_adamw_seg* segs, int nseg, int dtype, float lr, flo
     const int grid = grid_for(vecs, sms);
     const float omb1 = static_cast<float>(1.0 - b1), omb2 = static_cast<float>(1.0 - b2);
     if (dtype == MMB_BF16)
-      adamw_kernel<__nv_bfloat16><<<grid, THREADS, 0, st>>>(tab, decay, beta1, omb1, beta2, omb2, eps, device_grad_scale());
+      launch_stream_kernel(adamw_kernel<__nv_bfloat16>, grid, THREADS, st, tab, decay, beta1, omb1, beta2, omb2, eps, device_grad_scale());
     else
-      adamw_kernel<float><<<grid, THREADS, 0, st>>>(tab, decay, beta1, omb1, beta2, omb2, eps, device_grad_scale());
+      launch_stream_kernel(adamw_kernel<float>, grid, THREADS, st, tab, decay, beta1, omb1, beta2, omb2, eps, device_grad_scale());
     MMB_CUDA_CHECK(cudaGetLastError());
   count_launch();
   }

@@ -331,8 +331,11 @@ __device__ __forceinline__ long long draw_tile(TileCursor& c, uint32_t sched_ful
 }
 
 // -------------------------------------------------------------------- kernel
+// 112 registers per thread (13 warps: 46,592 of the SM's 65,536) leave room for one 256-thread CTA of a
+// streaming kernel (64 registers) on the same SM, so momentum / update / AdamW launches on another
+// stream run beside the GEMMs instead of queueing behind them.
 template <int BN, bool PAIR, bool DYN = false>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __maxnreg__(112)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__ CUtensorMap map_a_mn,
             const __grid_constant__ CUtensorMap map_b_k, const __grid_constant__ CUtensorMap map_b_mn,
             const __grid_constant__ CUtensorMap map_d, const GemmArgs args) {

@@ -151,7 +151,7 @@ adamw_master_kernel(const __grid_constant__ Table tab, float decay, float one_m_
 
 int grid_for(long long total_vecs, int sms) {
   const long long want = (total_vecs + THREADS - 1) / THREADS;
-  const long long cap = static_cast<long long>(sms) * 8 * 4;
+  const long long cap = stream_grid_cap(sms);
   const long long g = want < cap ? want : cap;
   return static_cast<int>(g < 1 ? 1 : g);
 }

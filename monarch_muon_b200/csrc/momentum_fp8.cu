@@ -448,26 +448,26 @@ void launch_momentum(int div_mode, bool all_fast, const SegTable& tab, int grid,
                      float expand_min, float* partials, cudaStream_t st) {
   if (FORMAT == MMB_STATE_FP8_ABSMAX && all_fast) {
     if (div_mode == MMB_DIV_IEEE)
-      momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_IEEE, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
+      launch_stream_kernel(momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_IEEE, true>, grid, THREADS, st, tab, beta, grad_scale, expand_min, partials, device_grad_scale());
     else if (div_mode == MMB_DIV_IEEE_STRICT)
-      momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_IEEE_STRICT, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
+      launch_stream_kernel(momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_IEEE_STRICT, true>, grid, THREADS, st, tab, beta, grad_scale, expand_min, partials, device_grad_scale());
     else
-      momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_FULL, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
+      launch_stream_kernel(momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_FULL, true>, grid, THREADS, st, tab, beta, grad_scale, expand_min, partials, device_grad_scale());
     return;
   }
   if (FORMAT == MMB_STATE_FP8_EXPAND && all_fast) {
     if (div_mode == MMB_DIV_IEEE_STRICT)
-      momentum_kernel<MMB_STATE_FP8_EXPAND, GradT, MMB_DIV_IEEE_STRICT, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
+      launch_stream_kernel(momentum_kernel<MMB_STATE_FP8_EXPAND, GradT, MMB_DIV_IEEE_STRICT, true>, grid, THREADS, st, tab, beta, grad_scale, expand_min, partials, device_grad_scale());
     else if (div_mode != MMB_DIV_FULL)
-      momentum_kernel<MMB_STATE_FP8_EXPAND, GradT, MMB_DIV_IEEE, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
+      launch_stream_kernel(momentum_kernel<MMB_STATE_FP8_EXPAND, GradT, MMB_DIV_IEEE, true>, grid, THREADS, st, tab, beta, grad_scale, expand_min, partials, device_grad_scale());
     else
-      momentum_kernel<MMB_STATE_FP8_EXPAND, GradT, MMB_DIV_FULL, true><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
+      launch_stream_kernel(momentum_kernel<MMB_STATE_FP8_EXPAND, GradT, MMB_DIV_FULL, true>, grid, THREADS, st, tab, beta, grad_scale, expand_min, partials, device_grad_scale());
     return;
   }
   if (div_mode != MMB_DIV_FULL)
-    momentum_kernel<FORMAT, GradT, MMB_DIV_IEEE, false><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
+    launch_stream_kernel(momentum_kernel<FORMAT, GradT, MMB_DIV_IEEE, false>, grid, THREADS, st, tab, beta, grad_scale, expand_min, partials, device_grad_scale());
   else
-    momentum_kernel<FORMAT, GradT, MMB_DIV_FULL, false><<<grid, THREADS, 0, st>>>(tab, beta, grad_scale, expand_min, partials, device_grad_scale());
+    launch_stream_kernel(momentum_kernel<FORMAT, GradT, MMB_DIV_FULL, false>, grid, THREADS, st, tab, beta, grad_scale, expand_min, partials, device_grad_scale());
 }
 
 template <typename GradT>
@@ -554,7 +554,7 @@ int momentum_step_impl(const mmb_momentum_seg* segs, int nseg, int grad_dtype, i
     tab.block_start[tab.nseg] = blocks;
     const long long warps_per_cta = THREADS / 32;
     long long want = (units + warps_per_cta - 1) / warps_per_cta;
-    long long cap = static_cast<long long>(sms) * 8 * 4;  // a few waves of 8 resident CTAs per SM
+    long long cap = stream_grid_cap(sms);  // a few waves of 8 resident CTAs per SM unless capped
     int grid = static_cast<int>(want < cap ? want : cap);
     if (grid < 1) grid = 1;
     if (grad_dtype == MMB_BF16)
@@ -569,7 +569,7 @@ int momentum_step_impl(const mmb_momentum_seg* segs, int nseg, int grad_dtype, i
       long long g2 = (blocks + warps_per_cta - 1) / warps_per_cta;
       if (g2 > sms * 4) g2 = sms * 4;
       if (g2 < 1) g2 = 1;
-      block_sumsq_kernel<<<static_cast<int>(g2), THREADS, 0, st>>>(tab, partials, block_sumsq_dev);
+      launch_stream_kernel(block_sumsq_kernel, static_cast<int>(g2), THREADS, st, tab, partials, block_sumsq_dev);
       MMB_CUDA_CHECK(cudaGetLastError());
   count_launch();
     }
