@@ -14,7 +14,11 @@ muon_oracle   heavy-ball momentum, batched quintic Newton-Schulz, the Muon
 fp8_oracle    the two FP8 (E4M3, groups of 128) optimizer-state codecs:
               plain absmax (pretrain/third_party/coat/optimizer/
               triton_kernels.py:34-36,51-63) and COAT dynamic-range expansion
-              (pretrain/src/models/monarch/coat_state_muon.py:22-91).
+              (pretrain/src/models/monarch/coat_state_muon.py:22-91); the
+              momentum and AdamW steps on states held in those formats.
+sft_oracle    the fine-tuning optimizer on fp32 master weights
+              (finetune/sft_optimizer.py), pinned bit-exactly to the
+              reference's own run.
 
 Parity pin: the restatement is checked in tests/test_oracle_golden.py against
 vectors produced by importing and running the reference's own Python on CPU
