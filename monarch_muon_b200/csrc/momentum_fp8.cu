@@ -81,13 +81,86 @@ __device__ __forceinline__ float raw_grad(const RawGroup<GradT>& r, int i) {
   return reinterpret_cast<const float*>(r.grad)[i];
 }
 
+// Plain bf16 state (the reference's own format with bf16 parameters), aligned pointers, full groups: the
+// same two-groups-in-flight pipeline without a codec.  m = bf16(beta*m), m = bf16(m + g): the two
+// roundings of mul_ followed by add_ on a bf16 tensor.  Returns this lane's share of sum(m^2).
+template <typename GradT>
+__device__ __forceinline__ float bf16_state_unit(const SegDev& sg, long long e0, int ngroups, int grp_in_warp, int sub,
+                                                 float beta, float grad_scale) {
+  struct Raw {
+    uint4 st[2];
+    uint4 grad[sizeof(GradT) == 2 ? 2 : 4];
+  };
+  auto load = [&](Raw& r, long long at) {
+    const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(sg.state) + at);
+    r.st[0] = __ldcs(sp);
+    r.st[1] = __ldcs(sp + 1);
+    const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const GradT*>(sg.grad) + at);
+#pragma unroll
+    for (int i = 0; i < (sizeof(GradT) == 2 ? 2 : 4); ++i) r.grad[i] = __ldcs(gp + i);
+  };
+  const bool scaled = grad_scale != 1.0f;
+  const bool separate_out = sg.m_out != nullptr && static_cast<void*>(sg.m_out) != sg.state;
+  float ss = 0.0f;
+  Raw cur, nxt;
+  bool cur_ok = grp_in_warp < ngroups;
+  if (cur_ok) load(cur, e0 + static_cast<long long>(grp_in_warp) * GROUP + sub * ELEMS_PER_LANE);
+  for (int g0 = 0; g0 < ngroups; g0 += 4) {
+    const int gi_next = g0 + 4 + grp_in_warp;
+    const bool nxt_ok = gi_next < ngroups;
+    if (nxt_ok) load(nxt, e0 + static_cast<long long>(gi_next) * GROUP + sub * ELEMS_PER_LANE);
+    if (cur_ok) {
+      const long long at = e0 + static_cast<long long>(g0 + grp_in_warp) * GROUP + sub * ELEMS_PER_LANE;
+      uint4 mv[2];
+      __nv_bfloat162* mh = reinterpret_cast<__nv_bfloat162*>(mv);
+      const uint32_t* sw = reinterpret_cast<const uint32_t*>(cur.st);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float t[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int e = 2 * i + j;
+          const float m = __uint_as_float(j ? (sw[i] & 0xffff0000u) : (sw[i] << 16));
+          float g;
+          if (sizeof(GradT) == 2) {
+            const uint32_t w = reinterpret_cast<const uint32_t*>(cur.grad)[e >> 1];
+            g = __uint_as_float((e & 1) ? (w & 0xffff0000u) : (w << 16));
+          } else {
+            g = reinterpret_cast<const float*>(cur.grad)[e];
+          }
+          if (scaled) {
+            g = __fmul_rn(g, grad_scale);
+            if (sizeof(GradT) == 2) g = bf16_round(g);
+          }
+          float x = bf16_round(__fmul_rn(beta, m));
+          x = bf16_round(__fadd_rn(x, g));
+          t[j] = x;
+          ss = fmaf(x, x, ss);
+        }
+        mh[i] = __floats2bfloat162_rn(t[0], t[1]);   // exact: both are bf16 values already
+      }
+      uint4* sp = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(sg.state) + at);
+      sp[0] = mv[0];
+      sp[1] = mv[1];
+      if (separate_out) {
+        uint4* mp = reinterpret_cast<uint4*>(sg.m_out + at);
+        mp[0] = mv[0];
+        mp[1] = mv[1];
+      }
+    }
+    cur = nxt;
+    cur_ok = nxt_ok;
+  }
+  return ss;
+}
+
 // -------------------------------------------------------------- fused kernel
 // ALL_FAST: the host has checked that every unit of the launch qualifies for the
 // fast path, so the general path is compiled out (fewer registers, more warps).
 template <int FORMAT, typename GradT, int DIV, bool ALL_FAST>
 // resident CTAs per SM asked of the compiler: 4 (64 registers) for the absmax fast path, 3 (80) for the
 // range-expansion fast path, which carries more live values per group
-__global__ void __launch_bounds__(THREADS, ALL_FAST ? (FORMAT == MMB_STATE_FP8_ABSMAX ? 4 : 3) : 1)
+__global__ void __launch_bounds__(THREADS, ALL_FAST ? ((FORMAT == MMB_STATE_FP8_ABSMAX || FORMAT == MMB_STATE_BF16) ? 4 : 3) : 1)
 momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_scale, float expand_min,
                 float* __restrict__ partials, const float* __restrict__ grad_scale_dev) {
   if (grad_scale_dev != nullptr) grad_scale = __fmul_rn(grad_scale, *grad_scale_dev);  // e.g. a clip coefficient
@@ -118,9 +191,11 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
 
     // Fast path: FP8 absmax state, aligned pointers, only full groups.  One group of loads is kept in
     // flight ahead of the arithmetic.
-    const bool fast = ALL_FAST || ((FORMAT == MMB_STATE_FP8_ABSMAX || FORMAT == MMB_STATE_FP8_EXPAND) && sg.vec_ok &&
-                                   ((e1 - e0) % GROUP) == 0);
-    if (fast) {
+    const bool fast = ALL_FAST || ((FORMAT == MMB_STATE_FP8_ABSMAX || FORMAT == MMB_STATE_FP8_EXPAND ||
+                                    FORMAT == MMB_STATE_BF16) && sg.vec_ok && ((e1 - e0) % GROUP) == 0);
+    if (FORMAT == MMB_STATE_BF16 && fast) {
+      ss = bf16_state_unit<GradT>(sg, e0, ngroups, grp_in_warp, sub, beta, grad_scale);
+    } else if (fast) {
       RawGroup<GradT> cur, nxt;
       bool cur_ok = grp_in_warp < ngroups;
       if (cur_ok) load_raw<FORMAT, GradT>(cur, sg, e0 + static_cast<long long>(grp_in_warp) * GROUP + sub * ELEMS_PER_LANE);
@@ -455,6 +530,10 @@ void launch_momentum(int div_mode, bool all_fast, const SegTable& tab, int grid,
       launch_stream_kernel(momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_FULL, true>, grid, THREADS, st, tab, beta, grad_scale, expand_min, partials, device_grad_scale());
     return;
   }
+  if (FORMAT == MMB_STATE_BF16 && all_fast) {
+    launch_stream_kernel(momentum_kernel<MMB_STATE_BF16, GradT, MMB_DIV_IEEE, true>, grid, THREADS, st, tab, beta, grad_scale, expand_min, partials, device_grad_scale());
+    return;
+  }
   if (FORMAT == MMB_STATE_FP8_EXPAND && all_fast) {
     if (div_mode == MMB_DIV_IEEE_STRICT)
       launch_stream_kernel(momentum_kernel<MMB_STATE_FP8_EXPAND, GradT, MMB_DIV_IEEE_STRICT, true>, grid, THREADS, st, tab, beta, grad_scale, expand_min, partials, device_grad_scale());
@@ -481,7 +560,7 @@ void launch_momentum_format(int format, int div_mode, bool all_fast, const SegTa
       launch_momentum<MMB_STATE_FP8_EXPAND, GradT>(div_mode, all_fast, tab, grid, beta, grad_scale, expand_min, partials, st);
       break;
     case MMB_STATE_BF16:
-      launch_momentum<MMB_STATE_BF16, GradT>(MMB_DIV_IEEE, false, tab, grid, beta, grad_scale, expand_min, partials, st);
+      launch_momentum<MMB_STATE_BF16, GradT>(MMB_DIV_IEEE, all_fast, tab, grid, beta, grad_scale, expand_min, partials, st);
       break;
     default:
       launch_momentum<MMB_STATE_F32, GradT>(MMB_DIV_IEEE, false, tab, grid, beta, grad_scale, expand_min, partials, st);
