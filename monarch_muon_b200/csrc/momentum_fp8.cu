@@ -154,6 +154,72 @@ __device__ __forceinline__ float bf16_state_unit(const SegDev& sg, long long e0,
   return ss;
 }
 
+// Plain fp32 state (the reference's pretraining recipe: fp32 parameters and momentum), same pipeline:
+// m = rn(beta*m), m = rn(m + g) in fp32, bf16 copy for Newton-Schulz, sum of squares of the fp32 values.
+template <typename GradT>
+__device__ __forceinline__ float f32_state_unit(const SegDev& sg, long long e0, int ngroups, int grp_in_warp, int sub,
+                                                float beta, float grad_scale) {
+  struct Raw {
+    uint4 st[4];
+    uint4 grad[sizeof(GradT) == 2 ? 2 : 4];
+  };
+  auto load = [&](Raw& r, long long at) {
+    const uint4* sp = reinterpret_cast<const uint4*>(static_cast<const float*>(sg.state) + at);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) r.st[i] = __ldcs(sp + i);
+    const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const GradT*>(sg.grad) + at);
+#pragma unroll
+    for (int i = 0; i < (sizeof(GradT) == 2 ? 2 : 4); ++i) r.grad[i] = __ldcs(gp + i);
+  };
+  const bool scaled = grad_scale != 1.0f;
+  float ss = 0.0f;
+  Raw cur, nxt;
+  bool cur_ok = grp_in_warp < ngroups;
+  if (cur_ok) load(cur, e0 + static_cast<long long>(grp_in_warp) * GROUP + sub * ELEMS_PER_LANE);
+  for (int g0 = 0; g0 < ngroups; g0 += 4) {
+    const int gi_next = g0 + 4 + grp_in_warp;
+    const bool nxt_ok = gi_next < ngroups;
+    if (nxt_ok) load(nxt, e0 + static_cast<long long>(gi_next) * GROUP + sub * ELEMS_PER_LANE);
+    if (cur_ok) {
+      const long long at = e0 + static_cast<long long>(g0 + grp_in_warp) * GROUP + sub * ELEMS_PER_LANE;
+      uint4 sv[4], mv[2];
+      float* sf = reinterpret_cast<float*>(sv);
+      __nv_bfloat162* mh = reinterpret_cast<__nv_bfloat162*>(mv);
+      const float* old = reinterpret_cast<const float*>(cur.st);
+#pragma unroll
+      for (int e = 0; e < ELEMS_PER_LANE; ++e) {
+        float g;
+        if (sizeof(GradT) == 2) {
+          const uint32_t w = reinterpret_cast<const uint32_t*>(cur.grad)[e >> 1];
+          g = __uint_as_float((e & 1) ? (w & 0xffff0000u) : (w << 16));
+        } else {
+          g = reinterpret_cast<const float*>(cur.grad)[e];
+        }
+        if (scaled) {
+          g = __fmul_rn(g, grad_scale);
+          if (sizeof(GradT) == 2) g = bf16_round(g);
+        }
+        const float x = __fadd_rn(__fmul_rn(beta, old[e]), g);
+        sf[e] = x;
+        ss = fmaf(x, x, ss);
+      }
+      uint4* sp = reinterpret_cast<uint4*>(static_cast<float*>(sg.state) + at);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sp[i] = sv[i];
+      if (sg.m_out != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mh[i] = __floats2bfloat162_rn(sf[2 * i], sf[2 * i + 1]);
+        uint4* mp = reinterpret_cast<uint4*>(sg.m_out + at);
+        mp[0] = mv[0];
+        mp[1] = mv[1];
+      }
+    }
+    cur = nxt;
+    cur_ok = nxt_ok;
+  }
+  return ss;
+}
+
 // -------------------------------------------------------------- fused kernel
 // ALL_FAST: the host has checked that every unit of the launch qualifies for the
 // fast path, so the general path is compiled out (fewer registers, more warps).
@@ -191,10 +257,11 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
 
     // Fast path: FP8 absmax state, aligned pointers, only full groups.  One group of loads is kept in
     // flight ahead of the arithmetic.
-    const bool fast = ALL_FAST || ((FORMAT == MMB_STATE_FP8_ABSMAX || FORMAT == MMB_STATE_FP8_EXPAND ||
-                                    FORMAT == MMB_STATE_BF16) && sg.vec_ok && ((e1 - e0) % GROUP) == 0);
+    const bool fast = ALL_FAST || (sg.vec_ok && ((e1 - e0) % GROUP) == 0);
     if (FORMAT == MMB_STATE_BF16 && fast) {
       ss = bf16_state_unit<GradT>(sg, e0, ngroups, grp_in_warp, sub, beta, grad_scale);
+    } else if (FORMAT == MMB_STATE_F32 && fast) {
+      ss = f32_state_unit<GradT>(sg, e0, ngroups, grp_in_warp, sub, beta, grad_scale);
     } else if (fast) {
       RawGroup<GradT> cur, nxt;
       bool cur_ok = grp_in_warp < ngroups;
@@ -530,8 +597,8 @@ void launch_momentum(int div_mode, bool all_fast, const SegTable& tab, int grid,
       launch_stream_kernel(momentum_kernel<MMB_STATE_FP8_ABSMAX, GradT, MMB_DIV_FULL, true>, grid, THREADS, st, tab, beta, grad_scale, expand_min, partials, device_grad_scale());
     return;
   }
-  if (FORMAT == MMB_STATE_BF16 && all_fast) {
-    launch_stream_kernel(momentum_kernel<MMB_STATE_BF16, GradT, MMB_DIV_IEEE, true>, grid, THREADS, st, tab, beta, grad_scale, expand_min, partials, device_grad_scale());
+  if ((FORMAT == MMB_STATE_BF16 || FORMAT == MMB_STATE_F32) && all_fast) {
+    launch_stream_kernel(momentum_kernel<FORMAT, GradT, MMB_DIV_IEEE, true>, grid, THREADS, st, tab, beta, grad_scale, expand_min, partials, device_grad_scale());
     return;
   }
   if (FORMAT == MMB_STATE_FP8_EXPAND && all_fast) {
@@ -563,7 +630,7 @@ void launch_momentum_format(int format, int div_mode, bool all_fast, const SegTa
       launch_momentum<MMB_STATE_BF16, GradT>(MMB_DIV_IEEE, all_fast, tab, grid, beta, grad_scale, expand_min, partials, st);
       break;
     default:
-      launch_momentum<MMB_STATE_F32, GradT>(MMB_DIV_IEEE, false, tab, grid, beta, grad_scale, expand_min, partials, st);
+      launch_momentum<MMB_STATE_F32, GradT>(MMB_DIV_IEEE, all_fast, tab, grid, beta, grad_scale, expand_min, partials, st);
       break;
   }
 }
