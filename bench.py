@@ -232,11 +232,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--nblocks", type=int, default=4, choices=[2, 4])
-    ap.add_argument("--case", default="step", choices=["step", "ns", "fp8", "gemm"],
+    ap.add_argument("--case", default="step", choices=["step", "ns", "fp8", "gemm", "adamw"],
                     help="step: the full optimizer step (headline); ns: isolated batched Newton-Schulz on the "
                          "128+64+64 block set; fp8: isolated FP8 momentum kernel on a flat buffer; gemm: the library's "
                          "batched GEMM beside cuBLAS (torch.bmm) on the Newton-Schulz shapes, each run back to "
-                         "back for seconds so that the power cap is in force")
+                         "back for seconds so that the power cap is in force; adamw: the AdamW kernel alone on a flat bf16 "
+                         "tensor of --fp8-elems elements (FP8 moments with --state-format coat)")
     ap.add_argument("--ns-blocks", type=int, default=128, help="square blocks in --case ns (tall/wide get half each)")
     ap.add_argument("--fp8-elems", type=int, default=1_600_000_000)
     ap.add_argument("--comm-sms", type=int, default=0, help="SMs left to NCCL during the sharded step")
@@ -291,6 +292,8 @@ def main():
         _lib.set_gemm_schedule(True)
     if args.case == "gemm":
         return run_gemm_comparison(args, dev)
+    if args.case == "adamw":
+        return run_adamw_isolated(args, dev)
     if args.case != "step":
         return run_isolated(args, dev)
 
@@ -401,6 +404,38 @@ def _timed(fn, steps: int, warmup: int, sampler=None):
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / steps, t_begin, time.time()
+
+
+def run_adamw_isolated(args, dev):
+    """The AdamW kernel alone: one flat bf16 parameter of --fp8-elems elements stepped through the optimizer
+    (no Muon group), with plain bf16 moments or, with --state-format coat, both moments in the range-expansion
+    FP8 format.  Algorithmic bytes per element: 14 (p, g, m, v in; p, m, v out) or 10 + 48/128."""
+    from monarch_muon_b200 import CoatStateMonarchMuon, MonarchMuonOptimizer, _lib
+    n = args.fp8_elems // 128 * 128
+    gen = torch.Generator(device=dev).manual_seed(5)
+    p = torch.nn.Parameter(torch.empty(n, dtype=torch.bfloat16, device=dev).normal_(0, 0.02, generator=gen))
+    p.grad = torch.empty(n, dtype=torch.bfloat16, device=dev).normal_(0, 1e-3, generator=gen)
+    coat = args.state_format == "coat"
+    opt = (CoatStateMonarchMuon if coat else MonarchMuonOptimizer)([], [p], lr=3e-4, adamw_betas=(0.9, 0.95),
+                                                                  adamw_weight_decay=0.1, adamw_eps=1e-8)
+    pk = peaks()
+    l0 = _lib.launch_count()
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    ms, tb, te = _timed(opt.step, args.steps, args.warmup)
+    per_elem = 10 + 48 / 128 if coat else 14
+    ach = n * per_elem / (ms * 1e-3) / 1e9
+    line = {"metric": "adamw_gbs", "value": ach, "unit": "GB/s", "higher_is_better": True, "ms_per_step": ms,
+            "config": {"workload": f"isolated AdamW kernel, flat bf16 tensor of {n} elements, "
+                                   + ("E4M3 range-expansion moments" if coat else "bf16 moments"),
+                       "cache": "inputs_larger_than_l2"},
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"],
+                         "peak_kind": f"{pk['source']}, copy bandwidth", "traffic": None},
+            "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "dtype": "bf16", "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None, "gpu_launches": _lib.launch_count() - l0,
+            "clocks": sampler.stop(tb, te), "device_status": _lib.read_status(dev)}
+    print(json.dumps(line))
+    return 0
 
 
 def run_gemm_comparison(args, dev):
