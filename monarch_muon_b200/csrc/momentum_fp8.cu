@@ -116,28 +116,28 @@ __device__ __forceinline__ float bf16_state_unit(const SegDev& sg, long long e0,
       const uint32_t* sw = reinterpret_cast<const uint32_t*>(cur.st);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        float t[2];
+        float g[2];
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const int e = 2 * i + j;
-          const float m = __uint_as_float(j ? (sw[i] & 0xffff0000u) : (sw[i] << 16));
-          float g;
           if (sizeof(GradT) == 2) {
             const uint32_t w = reinterpret_cast<const uint32_t*>(cur.grad)[e >> 1];
-            g = __uint_as_float((e & 1) ? (w & 0xffff0000u) : (w << 16));
+            g[j] = __uint_as_float((e & 1) ? (w & 0xffff0000u) : (w << 16));
           } else {
-            g = reinterpret_cast<const float*>(cur.grad)[e];
+            g[j] = reinterpret_cast<const float*>(cur.grad)[e];
           }
           if (scaled) {
-            g = __fmul_rn(g, grad_scale);
-            if (sizeof(GradT) == 2) g = bf16_round(g);
+            g[j] = __fmul_rn(g[j], grad_scale);
+            if (sizeof(GradT) == 2) g[j] = bf16_round(g[j]);
           }
-          float x = bf16_round(__fmul_rn(beta, m));
-          x = bf16_round(__fadd_rn(x, g));
-          t[j] = x;
-          ss = fmaf(x, x, ss);
         }
-        mh[i] = __floats2bfloat162_rn(t[0], t[1]);   // exact: both are bf16 values already
+        // both roundings as packed conversions of the pair; the second one is also what gets stored
+        const float m0 = __uint_as_float(sw[i] << 16), m1 = __uint_as_float(sw[i] & 0xffff0000u);
+        const float2 x = __bfloat1622float2(__floats2bfloat162_rn(__fmul_rn(beta, m0), __fmul_rn(beta, m1)));
+        mh[i] = __floats2bfloat162_rn(__fadd_rn(x.x, g[0]), __fadd_rn(x.y, g[1]));
+        const float2 y = __bfloat1622float2(mh[i]);
+        ss = fmaf(y.x, y.x, ss);
+        ss = fmaf(y.y, y.y, ss);
       }
       uint4* sp = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(sg.state) + at);
       sp[0] = mv[0];
