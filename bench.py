@@ -16,9 +16,16 @@ step with gradients already in HBM; `e2e` repeats the measurement through the
 public `optimizer.step()` with every gradient copied from pinned host memory
 inside the timed region and the per-block momentum norms read back.
 
-`--impl reference` times the CPU restatement of the reference step (oracle/,
-torch CPU kernels on all host threads) on a bounded sample of blocks and scales
-it to the full step by block and element counts.
+The default line also carries, each with its own clock sample: the two isolated
+kernels of the metric (`isolated_ns`: 128 + 64 + 64 blocks; `isolated_fp8_*`:
+1.6e9 and 2,558,525,440 elements), the reference's own GPU step on the same
+workload (`reference_gpu`), the 2-block model's step (`nblocks2_step`), and
+`peak_memory_gb` / `optimizer_state_gb`.
+
+`--impl reference` times the reference's own optimizer class (the staged copy
+under oracle/_ref/; the oracle's restatement if that copy is absent) on all
+host threads, on a bounded sample of blocks scaled to the full step by block and
+element counts; `--reference-device cuda` runs that class on the GPU instead.
 """
 from __future__ import annotations
 
@@ -104,10 +111,8 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------ the workload
-def build_workload(device, nblocks: int, seed: int = 1234, shard=None):
-    """Parameters and gradients of the 6.89B-reference model's optimizer step.
-    `shard=(rank, world)` keeps every world-th tensor's blocks split evenly: each
-    rank owns 1/world of the blocks of every tensor (used for N > 1)."""
+def build_workload(device, nblocks: int, seed: int = 1234):
+    """Parameters and gradients of the 6.89B-reference model's optimizer step."""
     gen = torch.Generator(device=device).manual_seed(seed)
     m = S.MODEL_689B
     muon_shapes = S.llama_monarch_muon_shapes(m["d_model"], m["n_layers"], m["intermediate"], nblocks)
@@ -134,11 +139,24 @@ def workload_counts(nblocks: int):
 
 
 # ------------------------------------------------------------------ CPU baseline
+def _reference_twin():
+    """The reference's own bf16 optimizer class (membench/src/models/monarch/monarch_muon.py, unmodified,
+    from the staged copy under oracle/_ref/), or None when that copy is absent."""
+    try:
+        from oracle import ref_loader
+        if ref_loader.available():
+            return ref_loader.membench_twin().MonarchMuonOptimizer
+    except Exception:                                          # a broken staging must not take the bench down
+        pass
+    return None
+
+
 def cpu_reference_step_ms(nblocks: int, steps: int, warmup: int, threads: int | None = None):
-    """The oracle's restatement of the reference step (bf16 twin: bf16 state,
-    bf16 Newton-Schulz) on host cores, on a sample of blocks, scaled to the full
-    step.  Returns (ms per full step, description of the sample, threads)."""
-    from oracle import muon_oracle
+    """The reference step (bf16 twin: bf16 state, bf16 Newton-Schulz) on the host cores, on a sample of
+    blocks of every shape and a slice of the AdamW group, each part scaled linearly to the full step
+    (blocks are independent, AdamW is element-wise).  Runs the reference's own class when oracle/_ref/
+    holds it (kind "reference"), else the oracle's restatement of it (kind "port").
+    Returns (ms per full step, description of the sample, threads, kind)."""
     threads = threads or os.cpu_count() or 1
     torch.set_num_threads(threads)
     m = S.MODEL_689B
@@ -150,76 +168,126 @@ def cpu_reference_step_ms(nblocks: int, steps: int, warmup: int, threads: int | 
     frac = 96.0 / max(full.values())
     sample = {k: max(1, int(round(v * frac))) for k, v in full.items()}
     gen = torch.Generator().manual_seed(7)
-    groups = {}
-    for (r, c), nb in sample.items():
-        w = (0.02 * torch.randn(nb, r, c, generator=gen)).bfloat16()
-        g = (1e-3 * torch.randn(nb, r, c, generator=gen)).bfloat16()
-        groups[(r, c)] = (w, g, torch.zeros_like(w))
     _, _, adamw_elems = workload_counts(nblocks)
     a_n = 1 << 23
-    ap = (0.02 * torch.randn(a_n, generator=gen)).bfloat16()
-    ag = (1e-3 * torch.randn(a_n, generator=gen)).bfloat16()
-    am, av = torch.zeros_like(ap), torch.zeros_like(ap)
+    twin = _reference_twin()
+    kw = dict(lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95), adamw_weight_decay=0.1, adamw_eps=1e-8)
+    parts = []                                                 # (callable, scale to the full step)
+    if twin is not None:
+        kind = "reference"
+        for (r, c), nb in sample.items():
+            # tensors of `nblocks` blocks each, like the model's factors
+            ps = [torch.nn.Parameter((0.02 * torch.randn(nblocks, r, c, generator=gen)).bfloat16())
+                  for _ in range(max(1, nb // nblocks))]
+            for p in ps:
+                p.grad = (1e-3 * torch.randn(p.shape, generator=gen)).bfloat16()
+            sample[(r, c)] = len(ps) * nblocks
+            opt = twin(ps, [], **kw)
+            parts.append((opt.step, full[(r, c)] / sample[(r, c)]))
+        ap = torch.nn.Parameter((0.02 * torch.randn(a_n, generator=gen)).bfloat16())
+        ap.grad = (1e-3 * torch.randn(a_n, generator=gen)).bfloat16()
+        aopt = twin([], [ap], **kw)
+        parts.append((aopt.step, adamw_elems / a_n))
+    else:
+        kind = "port"
+        from oracle import muon_oracle
+        for (r, c), nb in sample.items():
+            w = (0.02 * torch.randn(nb, r, c, generator=gen)).bfloat16()
+            g = (1e-3 * torch.randn(nb, r, c, generator=gen)).bfloat16()
+            buf = torch.zeros_like(w)
+            parts.append((lambda w=w, g=g, buf=buf: muon_oracle.muon_group_step([w], [g], [buf], lr=0.02, beta=0.95,
+                                                                                ns_dtype=torch.bfloat16),
+                          full[(r, c)] / nb))
+        ap = (0.02 * torch.randn(a_n, generator=gen)).bfloat16()
+        ag = (1e-3 * torch.randn(a_n, generator=gen)).bfloat16()
+        am, av = torch.zeros_like(ap), torch.zeros_like(ap)
+        count = [0]
 
-    def one_pass(step_no: int) -> float:
+        def adamw_part():
+            count[0] += 1
+            muon_oracle.adamw_tensor_step(ap, ag, am, av, count[0], lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, eps=1e-8)
+        parts.append((adamw_part, adamw_elems / a_n))
+
+    def one_pass() -> float:
         total = 0.0
-        for (r, c), (w, g, buf) in groups.items():
+        for fn, scale in parts:
             t0 = time.perf_counter()
-            muon_oracle.muon_group_step([w], [g], [buf], lr=0.02, beta=0.95, ns_dtype=torch.bfloat16)
-            total += (time.perf_counter() - t0) * full[(r, c)] / sample[(r, c)]
-        t0 = time.perf_counter()
-        muon_oracle.adamw_tensor_step(ap, ag, am, av, step_no, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, eps=1e-8)
-        total += (time.perf_counter() - t0) * adamw_elems / a_n
+            fn()
+            total += (time.perf_counter() - t0) * scale
         return total * 1e3
 
     with torch.no_grad():
-        for i in range(warmup):
-            one_pass(i + 1)
-        times = [one_pass(warmup + i + 1) for i in range(steps)]
-    desc = ("bf16 reference step (momentum, cat, Newton-Schulz, update) on "
-            + ", ".join(f"{nb} of {full[k]} blocks {k[0]}x{k[1]}" for k, nb in sample.items())
-            + f"; AdamW on {a_n} of {adamw_elems} elements; each part scaled linearly to the full count")
-    return sum(times) / len(times), desc, threads
+        for _ in range(warmup):
+            one_pass()
+        times = [one_pass() for _ in range(steps)]
+    desc = (("the reference's own MonarchMuonOptimizer (membench twin, bf16) " if kind == "reference"
+             else "restatement of the reference's bf16 step (momentum, cat, Newton-Schulz, update) ")
+            + "on " + ", ".join(f"{nb} of {full[k]} blocks {k[0]}x{k[1]}" for k, nb in sample.items())
+            + f"; AdamW on {a_n} of {adamw_elems} elements; each part scaled linearly to the full count; "
+            + f"median of {len(times)} passes")
+    return statistics.median(times), desc, threads, kind
+
+
+def gpu_reference_step_ms(dev, nblocks: int, steps: int, warmup: int):
+    """The reference's own GPU step: membench/src/models/monarch/monarch_muon.py's MonarchMuonOptimizer,
+    unmodified (staged under oracle/_ref/), on the full workload with bf16 parameters, gradients and state,
+    timed with CUDA events per step on a side stream as the reference's harness does
+    (membench/scripts/monarch_benchmark/benchmark_train_step.py:297-310, 382-397).  Falls back to the
+    oracle's torch-op restatement when the staged copy is absent.  Returns a dict."""
+    torch.backends.cuda.matmul.allow_tf32 = True     # as the reference's harness sets it (:346)
+    muon, adamw = build_workload(dev, nblocks)
+    twin = _reference_twin()
+    kw = dict(lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95), adamw_weight_decay=0.1, adamw_eps=1e-8)
+    if twin is not None:
+        opt = twin(muon, adamw, **kw)
+        step, kind = opt.step, "reference"
+    else:
+        from oracle import muon_oracle
+        ref = muon_oracle.OracleMonarchMuon([p.data for p in muon], [p.data for p in adamw], ns_dtype=torch.bfloat16,
+                                            foreach_cpu=True, **kw)
+        mg, ag = [p.grad for p in muon], [p.grad for p in adamw]
+        step, kind = (lambda: ref.step(mg, ag)), "port"
+    torch.cuda.reset_peak_memory_stats(dev)
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    times = []
+    with torch.cuda.stream(side):
+        for _ in range(max(3, warmup)):
+            step()
+        torch.cuda.synchronize()
+        t_begin = time.time()
+        for _ in range(steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        t_end = time.time()
+    out = {"value": statistics.median(times), "unit": "ms", "kind": kind, "steps": steps,
+           "min": min(times), "max": max(times), "state": "bf16 momentum and AdamW moments (the reference's format)",
+           "peak_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9, "clocks": sampler.stop(t_begin, t_end)}
+    del muon, adamw
+    torch.cuda.empty_cache()
+    return out
 
 
 def gpu_reference_step(args, config) -> int:
-    """The reference step's torch-op sequence (bf16 twin: _foreach momentum, cat, bmm-based
-    Newton-Schulz, per-tensor add_, _foreach AdamW) on the full workload on cuda:0, timed with
-    CUDA events.  It is the restatement used as the parity checker, here only timed: it shows
-    what the reference's own GPU path (cuBLAS batched GEMMs + elementwise torch kernels) costs
-    on the same box."""
-    from oracle import muon_oracle
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    torch.backends.cuda.matmul.allow_tf32 = True     # as the reference's harness sets it
-    muon, adamw = build_workload(dev, args.nblocks)
-    ref = muon_oracle.OracleMonarchMuon([p.data for p in muon], [p.data for p in adamw], lr=0.02, momentum=0.95,
-                                        adamw_betas=(0.9, 0.95), adamw_weight_decay=0.1, adamw_eps=1e-8,
-                                        ns_dtype=torch.bfloat16, foreach_cpu=True)
-    mg, ag = [p.grad for p in muon], [p.grad for p in adamw]
-    sampler = ClockSampler(0)
-    sampler.start()
-    for _ in range(max(3, args.warmup)):
-        ref.step(mg, ag)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t_begin = time.time()
-    e0.record()
-    for _ in range(args.steps):
-        ref.step(mg, ag)
-    e1.record()
-    torch.cuda.synchronize()
-    t_end = time.time()
-    ms = e0.elapsed_time(e1) / args.steps
+    r = gpu_reference_step_ms(dev, args.nblocks, args.steps, args.warmup)
+    ms = r["value"]
     line = {"impl": "reference", "reference_device": "cuda", "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": 1,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": ms / H100_PUBLISHED_MS, "dtype": "bf16", "data": "synthetic",
             "config": dict(config, workload=config["workload"].replace("FP8 E4M3 absmax momentum state",
                                                                        "bf16 momentum state (the reference's)")),
-            "note": "torch-op restatement of the reference's bf16 step on the GPU (cuBLAS bmm + elementwise kernels), "
-                    "full workload, gradients resident",
-            "peak_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
-            "clocks": sampler.stop(t_begin, t_end), "gpu_launches": 0}
+            "note": ("the reference's own MonarchMuonOptimizer (membench twin) on the GPU" if r["kind"] == "reference" else
+                     "torch-op restatement of the reference's bf16 step on the GPU") + ", full workload, gradients resident, "
+                    "median of per-step CUDA-event times",
+            "reference_kind": r["kind"], "peak_memory_gb": r["peak_memory_gb"], "clocks": r["clocks"], "gpu_launches": 0}
     print(json.dumps(line))
     return 0
 
@@ -254,7 +322,13 @@ def main():
     ap.add_argument("--overlap", type=int, default=0, choices=[0, 1],
                     help="run momentum / update / AdamW on a second stream beside Newton-Schulz (1) or everything on "
                          "one stream (0, the optimizer's default)")
+    ap.add_argument("--fp8-div", default="full", choices=["full", "ieee", "ieee_strict"],
+                    help="arithmetic of the FP8 quantiser: full (default; the reference kernels' GPU instructions, "
+                         "bit-exact with them for the absmax codec), ieee (bit-exact with the CPU oracle)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-subrecords", action="store_true",
+                    help="leave out the extra measurements of the default line (isolated kernels, the reference's "
+                         "GPU step, the 2-block model)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -269,11 +343,11 @@ def main():
             return 0
         if args.reference_device == "cuda":
             return gpu_reference_step(args, config)
-        ms, desc, threads = cpu_reference_step_ms(args.nblocks, max(1, args.steps), max(0, args.warmup))
+        ms, desc, threads, kind = cpu_reference_step_ms(args.nblocks, max(1, args.steps), max(0, args.warmup))
         line = {"impl": "reference", "metric": METRIC, "value": ms, "unit": "ms", "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False,
                 "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
-                "cpu_baseline": {"value": ms, "unit": "ms", "cores": threads, "kind": "port", "sample": desc},
+                "cpu_baseline": {"value": ms, "unit": "ms", "cores": threads, "kind": kind, "sample": desc},
                 "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
         print(json.dumps(line))
@@ -302,11 +376,11 @@ def main():
         from monarch_muon_b200 import CoatStateMonarchMuon
         opt = CoatStateMonarchMuon(muon, adamw, lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95),
                                    adamw_weight_decay=0.1, adamw_eps=1e-8, ns_max_batch=args.ns_max_batch,
-                                   overlap=bool(args.overlap))
+                                   overlap=bool(args.overlap), fp8_div=args.fp8_div)
     else:
         opt = MonarchMuonOptimizer(muon, adamw, lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95),
                                    adamw_weight_decay=0.1, adamw_eps=1e-8, state_format=args.state_format,
-                                   ns_max_batch=args.ns_max_batch, overlap=bool(args.overlap))
+                                   ns_max_batch=args.ns_max_batch, overlap=bool(args.overlap), fp8_div=args.fp8_div)
     if args.state_format != "fp8_absmax":
         config["workload"] = config["workload"].replace("FP8 E4M3 absmax momentum state",
                                                         f"momentum state format {args.state_format}")
@@ -360,24 +434,43 @@ def main():
                 "frac": ach_tf / pk["bf16_tflops_sustained"], "peak_kind": f"{pk['source']}, sustained bf16 GEMM",
                 "achieved_note": "algorithmic FLOPs (5*(4m^2n+2m^3) per block) over the CUDA-event time of all "
                                  "Newton-Schulz launches of the step; symmetric tiles that are skipped count as done",
-                "traffic": 1.0e11,
-                "traffic_note": "DRAM bytes summed over the step's 120 GEMM launches, scaled by block count from the "
-                                "ncu capture of the 32-block case in profiles/gemm_kernel_ns_32blocks.md"}
+                "traffic": None,
+                "traffic_note": "not measured in this run (DRAM counters need a profiler pass); an ncu capture of a "
+                                "32-block launch read at or below the algorithmic operand and result bytes"}
     mom_ms = phases.get("momentum", float("nan"))
     mom_gbs = muon_elems * S.FP8_ABSMAX_BYTES_PER_ELEM / (mom_ms * 1e-3) / 1e9
     roofline_fp8 = {"kernel": "momentum_kernel (FP8 absmax heavy-ball)", "bound": "hbm", "achieved": mom_gbs,
                     "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": mom_gbs / pk["hbm_gbs"],
                     "peak_kind": f"{pk['source']}, copy bandwidth", "traffic": 0.98 * muon_elems * S.FP8_ABSMAX_BYTES_PER_ELEM,
-                    "traffic_note": "0.98 x algorithmic bytes, ncu capture of 4e8 elements in "
-                                    "profiles/momentum_kernel_fp8_400M.md scaled by element count"}
+                    "traffic_note": "0.98 x algorithmic bytes: the ratio an ncu capture of a 4e8-element launch "
+                                    "measured, scaled by element count (traffic grows in proportion)"}
 
+    peak_memory_gb = torch.cuda.max_memory_allocated(dev) / 1e9     # parameters, gradients, state and scratch
+    state_bytes = sum(v.numel() * v.element_size() for st in opt.state.values() for v in st.values() if torch.is_tensor(v))
     e2e = None
     if not args.no_e2e:
         e2e = run_e2e(opt, muon, adamw, args.steps, dev)
     cpu = None
     if not args.no_cpu_baseline:
-        cms, desc, threads = cpu_reference_step_ms(args.nblocks, 1, 1)
-        cpu = {"value": cms, "unit": "ms", "cores": threads, "kind": "port", "sample": desc}
+        cms, desc, threads, kind = cpu_reference_step_ms(args.nblocks, 3, 1)
+        cpu = {"value": cms, "unit": "ms", "cores": threads, "kind": kind, "sample": desc}
+
+    # Further measurements of the same metric family, each with its own clock sample, so that every figure
+    # quoted for this library can be read off one line.
+    sub = {}
+    if not args.no_subrecords and args.state_format == "fp8_absmax" and args.nblocks == 4:
+        del opt, muon, adamw
+        from monarch_muon_b200.newton_schulz import release_workspaces
+        release_workspaces()
+        torch.cuda.empty_cache()
+        sub["isolated_ns"] = measure_isolated_ns(dev, 4, 128, 10, 3)
+        sub["isolated_fp8_1.6e9"] = measure_isolated_fp8(dev, 1_600_000_000, "fp8_absmax", args.fp8_div, 20, 3)
+        sub["isolated_fp8_2558525440"] = measure_isolated_fp8(dev, 2_558_525_440, "fp8_absmax", args.fp8_div, 20, 3)
+        release_workspaces()
+        torch.cuda.empty_cache()
+        sub["reference_gpu"] = gpu_reference_step_ms(dev, 4, 8, 3)
+        sub["reference_gpu"]["speedup_device_timed"] = sub["reference_gpu"]["value"] / ms
+        sub["nblocks2_step"] = measure_nblocks2_step(dev, 5, 3)
 
     line = {"metric": METRIC, "value": ms, "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
             "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
@@ -387,9 +480,46 @@ def main():
             "roofline": roofline, "roofline_fp8_state": roofline_fp8,
             "ns_algorithmic_tflop_per_step": flops / 1e12, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": launches, "clocks": clocks, "device_status": status,
+            "peak_memory_gb": peak_memory_gb, "optimizer_state_gb": state_bytes / 1e9,
             "baseline_note": "vs_baseline divides by the reference's published 304.4 ms on one H100 (bf16 state)"}
+    line.update(sub)
     print(json.dumps(line))
     return 0
+
+
+def measure_nblocks2_step(dev, steps: int, warmup: int) -> dict:
+    """The same optimizer step on the 2-block variant of the model (704 + 128 + 64 blocks of 2048x2048,
+    5504x2048, 2048x5504: twice the Monarch elements, four times the Newton-Schulz FLOPs)."""
+    from monarch_muon_b200 import MonarchMuonOptimizer, _lib
+    from monarch_muon_b200.newton_schulz import release_workspaces
+    muon, adamw = build_workload(dev, 2)
+    opt = MonarchMuonOptimizer(muon, adamw, lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95), adamw_weight_decay=0.1,
+                               adamw_eps=1e-8, state_format="fp8_absmax")
+    flops, muon_elems, _ = workload_counts(2)
+    for _ in range(max(2, warmup)):
+        opt.step()
+    torch.cuda.synchronize()
+    opt.enable_phase_timing(True)
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    tb = time.time()
+    e0.record()
+    for _ in range(steps):
+        opt.step()
+    e1.record()
+    torch.cuda.synchronize()
+    te = time.time()
+    ms = e0.elapsed_time(e1) / steps
+    phases = {k: v / steps for k, v in opt.phase_times_ms().items()}
+    ns_ms = phases.get("newton_schulz", float("nan"))
+    out = {"value": ms, "unit": "ms", "steps": steps, "phases_ms": phases, "monarch_elements": muon_elems,
+           "ns_algorithmic_tflop_per_step": flops / 1e12, "ns_tflops": flops / (ns_ms * 1e-3) / 1e12,
+           "device_status": _lib.read_status(dev), "clocks": sampler.stop(tb, te)}
+    del opt, muon, adamw
+    release_workspaces()
+    torch.cuda.empty_cache()
+    return out
 
 
 def _timed(fn, steps: int, warmup: int, sampler=None):
@@ -487,65 +617,87 @@ def run_gemm_comparison(args, dev):
     return 0
 
 
+def measure_isolated_ns(dev, nblocks: int, ns_blocks: int, steps: int, warmup: int) -> dict:
+    """Batched Newton-Schulz alone on N(0,1) bf16 blocks: `ns_blocks` square blocks and half as many of the
+    tall and of the wide shape (128 + 64 + 64 at the 4-block shapes is the metric's isolated case)."""
+    from monarch_muon_b200 import newton_schulz_batched
+    pk = peaks()
+    gen = torch.Generator(device=dev).manual_seed(99)
+    r = 1024 * 4 // nblocks
+    t = 2752 * 4 // nblocks
+    sets = [(ns_blocks, r, r), (max(1, ns_blocks // 2), t, r), (max(1, ns_blocks // 2), r, t)]
+    xs = [torch.empty(s, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=gen) for s in sets]
+    outs = [torch.empty_like(x) for x in xs]
+    flops = sum(s[0] * S.ns_flops(s[1], s[2]) for s in sets)
+
+    def fn():
+        for x, o in zip(xs, outs):
+            newton_schulz_batched(x, out=o, max_batch=256)
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    ms, tb, te = _timed(fn, steps, warmup)
+    ach = flops / (ms * 1e-3) / 1e12
+    return {"value": ach, "unit": "TFLOP/s", "ms": ms, "steps": steps,
+            "workload": "isolated batched Newton-Schulz, bf16, N(0,1) blocks: " + ", ".join(f"{s[0]}x{s[1]}x{s[2]}" for s in sets),
+            "roofline": {"bound": "tensor", "achieved": ach, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": ach / pk["bf16_tflops"], "peak_kind": f"{pk['source']}, burst bf16 GEMM", "traffic": None},
+            "clocks": sampler.stop(tb, te)}
+
+
+def measure_isolated_fp8(dev, n: int, state_format: str, div: str, steps: int, warmup: int) -> dict:
+    """The FP8 momentum kernel alone on a flat buffer of n elements (bf16 gradients N(0,1e-3), state
+    quantised once from N(0,1e-3)), writing codes, scales and the bf16 momentum."""
+    from monarch_muon_b200 import _lib, fp8_state
+    pk = peaks()
+    gen = torch.Generator(device=dev).manual_seed(99)
+    n = n // 128 * 128
+    expand_fmt = state_format == "fp8_expand"
+    mode = _lib.DIV_NAMES[div]
+    m0 = torch.empty(n, dtype=torch.float32, device=dev).normal_(0, 1e-3, generator=gen)
+    st = {}
+    fp8_state.quantize_(st, "momentum_buffer", m0, codec="expand" if expand_fmt else "absmax", div_mode=mode)
+    codes = st["momentum_buffer"].view(torch.uint8)
+    scales = st["scale_momentum_buffer"]
+    side = dict(expand=st["expand_momentum_buffer"], sqrt_minmax=st["sqrt_minmax_momentum_buffer"]) if expand_fmt else {}
+    del m0
+    g = torch.empty(n, dtype=torch.bfloat16, device=dev).normal_(0, 1e-3, generator=gen)
+    m16 = torch.empty(n, dtype=torch.bfloat16, device=dev)
+
+    def fn():
+        fp8_state.fp8_momentum_flat(codes, scales, g, 0.95, m_bf16=m16, div_mode=mode, **side)
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    ms, tb, te = _timed(fn, steps, warmup)
+    per_elem = S.FP8_ABSMAX_BYTES_PER_ELEM + (2 * 2 * 4 / 128 if expand_fmt else 0.0)   # two more fp32 per group, in and out
+    ach = n * per_elem / (ms * 1e-3) / 1e9
+    name = "range-expansion" if expand_fmt else "absmax"
+    out = {"value": ach, "unit": "GB/s", "ms": ms, "steps": steps, "elements": n, "division": div,
+           "workload": f"isolated FP8 {name} momentum kernel, flat buffer of {n} elements, bf16 gradients N(0,1e-3), "
+                       "groups of 128",
+           "roofline": {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                        "frac": ach / pk["hbm_gbs"], "peak_kind": f"{pk['source']}, copy bandwidth", "traffic": None},
+           "clocks": sampler.stop(tb, te)}
+    del codes, scales, g, m16, st, side
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_isolated(args, dev):
     """The two isolated kernels of the metric: batched Newton-Schulz (TFLOP/s
     against the bf16 tensor peak) and the FP8 momentum kernel (GB/s against HBM)."""
-    from monarch_muon_b200 import _lib, fp8_state, newton_schulz_batched
-    pk = peaks()
-    gen = torch.Generator(device=dev).manual_seed(99)
-    sampler = ClockSampler(dev.index)
-    sampler.start()
+    from monarch_muon_b200 import _lib
     l0 = _lib.launch_count()
     if args.case == "ns":
-        nb = args.ns_blocks
-        r = 1024 * 4 // args.nblocks
-        t = 2752 * 4 // args.nblocks
-        sets = [(nb, r, r), (max(1, nb // 2), t, r), (max(1, nb // 2), r, t)]
-        xs = [torch.empty(s, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=gen) for s in sets]
-        outs = [torch.empty_like(x) for x in xs]
-        flops = sum(s[0] * S.ns_flops(s[1], s[2]) for s in sets)
-
-        def fn():
-            for x, o in zip(xs, outs):
-                newton_schulz_batched(x, out=o, max_batch=256)
-        ms, tb, te = _timed(fn, args.steps, args.warmup)
-        ach = flops / (ms * 1e-3) / 1e12
-        line = {"metric": "newton_schulz_tflops", "value": ach, "unit": "TFLOP/s", "higher_is_better": True,
-                "ms_per_step": ms, "config": {"workload": "isolated batched Newton-Schulz, bf16, N(0,1) blocks: "
-                                              + ", ".join(f"{s[0]}x{s[1]}x{s[2]}" for s in sets),
-                                              "cache": "inputs_larger_than_l2"},
-                "roofline": {"bound": "tensor", "achieved": ach, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
-                             "frac": ach / pk["bf16_tflops"], "peak_kind": f"{pk['source']}, burst bf16 GEMM",
-                             "traffic": None}}
+        r = measure_isolated_ns(dev, args.nblocks, args.ns_blocks, args.steps, args.warmup)
+        line = {"metric": "newton_schulz_tflops"}
     else:
-        n = args.fp8_elems // 128 * 128
-        expand_fmt = args.state_format == "fp8_expand"
-        m0 = torch.empty(n, dtype=torch.float32, device=dev).normal_(0, 1e-3, generator=gen)
-        st = {}
-        fp8_state.quantize_(st, "momentum_buffer", m0, codec="expand" if expand_fmt else "absmax")
-        codes = st["momentum_buffer"].view(torch.uint8)
-        scales = st["scale_momentum_buffer"]
-        side = dict(expand=st["expand_momentum_buffer"], sqrt_minmax=st["sqrt_minmax_momentum_buffer"]) if expand_fmt else {}
-        del m0
-        g = torch.empty(n, dtype=torch.bfloat16, device=dev).normal_(0, 1e-3, generator=gen)
-        m16 = torch.empty(n, dtype=torch.bfloat16, device=dev)
-
-        def fn():
-            fp8_state.fp8_momentum_flat(codes, scales, g, 0.95, m_bf16=m16, **side)
-        ms, tb, te = _timed(fn, args.steps, args.warmup)
-        per_elem = S.FP8_ABSMAX_BYTES_PER_ELEM + (2 * 2 * 4 / 128 if expand_fmt else 0.0)   # two more fp32 per group, in and out
-        ach = n * per_elem / (ms * 1e-3) / 1e9
-        name = "range-expansion" if expand_fmt else "absmax"
-        line = {"metric": "fp8_momentum_gbs", "value": ach, "unit": "GB/s", "higher_is_better": True,
-                "ms_per_step": ms, "config": {"workload": f"isolated FP8 {name} momentum kernel, flat buffer of {n} "
-                                              "elements, bf16 gradients N(0,1e-3), groups of 128",
-                                              "cache": "inputs_larger_than_l2"},
-                "roofline": {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                             "frac": ach / pk["hbm_gbs"], "peak_kind": f"{pk['source']}, copy bandwidth",
-                             "traffic": None}}
-    line.update({"n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "dtype": "bf16",
+        r = measure_isolated_fp8(dev, args.fp8_elems, args.state_format, args.fp8_div, args.steps, args.warmup)
+        line = {"metric": "fp8_momentum_gbs"}
+    line.update({"value": r["value"], "unit": r["unit"], "higher_is_better": True, "ms_per_step": r["ms"],
+                 "config": {"workload": r["workload"], "cache": "inputs_larger_than_l2"}, "roofline": r["roofline"],
+                 "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "dtype": "bf16",
                  "data": "synthetic", "scaling": "strong", "vs_baseline": None,
-                 "gpu_launches": _lib.launch_count() - l0, "clocks": sampler.stop(tb, te),
+                 "gpu_launches": _lib.launch_count() - l0, "clocks": r["clocks"],
                  "device_status": _lib.read_status(dev)})
     print(json.dumps(line))
     return 0

@@ -63,11 +63,15 @@ extern "C" {
 
 int mmb_version(void);
 const char* mmb_last_error(void);
-/* Size every kernel's grid for at most n SMs (0 = all).  Leaving a few SMs
+/* Launch options.  The three setters below act on the CALLING HOST THREAD only (like mmb_last_error and
+ * mmb_set_device_grad_scale): they change how later calls of that thread size and schedule their kernels,
+ * never what is computed.  Nothing else in the library is mutable state.
+ *
+ * Size every kernel's grid for at most n SMs (0 = all).  Leaving a few SMs
  * free lets communication kernels (NCCL) run beside the persistent GEMMs. */
 int mmb_set_sm_limit(int n);
 /* Cap the grids of the bandwidth-bound kernels (momentum, update, AdamW) at n CTAs of 256 threads per SM
- * (0 = default, 32).  With n = 1 they fit beside the persistent GEMM CTAs, so work issued on a second stream
+ * (0 = default, 32; values outside 0..32 are refused with MMB_ERR_INVALID).  With n = 1 they fit beside the persistent GEMM CTAs, so work issued on a second stream
  * overlaps Newton-Schulz.  No counterpart in the reference. */
 int mmb_set_stream_ctas_per_sm(int n);
 /* Tile schedule of the Newton-Schulz GEMMs (no counterpart in the reference).  0 (default): every CTA pair
@@ -129,6 +133,9 @@ int mmb_momentum_step(const mmb_momentum_seg* segs, int nseg, int grad_dtype, in
  *     MMB_ERR_INVALID and a message; about 4.29e9 state elements fit.
  *   - The first call on each device looks up the array's device address, with
  *     that device current; make that first call outside any stream capture.
+ *     The address is remembered per device ordinal for the life of the process:
+ *     after cudaDeviceReset() on that device the entry point must not be used
+ *     again in the same process.
  *   - All calls on a device share the array.  It keeps whatever the last call
  *     left; nothing in it has to start at zero because every partial a call
  *     reads is written by that same call first.  Two calls whose kernels can

@@ -17,6 +17,11 @@ from . import build as _build
 BF16, F32 = 0, 1
 STATE_FP8_ABSMAX, STATE_FP8_EXPAND, STATE_BF16, STATE_F32 = 0, 1, 2, 3
 DIV_IEEE, DIV_FULL, DIV_IEEE_STRICT = 0, 1, 2
+# Default arithmetic of the FP8 quantisers: the GPU instructions the reference's Triton kernels compile to
+# (div.full.f32, sqrt.approx.ftz.f32, library powf).  With it the absmax codec reproduces the reference's
+# kernel bit for bit on the same GPU; DIV_IEEE reproduces the CPU oracle bit for bit instead.
+DIV_DEFAULT = DIV_FULL
+DIV_NAMES = {"full": DIV_FULL, "ieee": DIV_IEEE, "ieee_strict": DIV_IEEE_STRICT}
 NS_TCGEN05, NS_SIMT = 0, 1
 GEMM_K, GEMM_MN, GEMM_SYM = 0, 1, 2
 
@@ -183,3 +188,33 @@ def set_gemm_schedule(dynamic: bool) -> None:
 def set_sm_limit(n: int) -> None:
     """Size kernel grids for at most n SMs (0 = all)."""
     load().mmb_set_sm_limit(int(n))
+
+
+class launch_options:
+    """Context manager around the library's per-thread launch options: they are set on entry and always
+    put back to their defaults on exit, also when the body raises.
+
+        with _lib.launch_options(sm_limit=140, dynamic_schedule=True):
+            ...launch kernels...
+    """
+
+    def __init__(self, *, sm_limit: int = 0, dynamic_schedule: bool = False, stream_ctas_per_sm: int = 0):
+        self.sm_limit, self.dynamic, self.ctas = int(sm_limit), bool(dynamic_schedule), int(stream_ctas_per_sm)
+
+    def __enter__(self):
+        if self.sm_limit:
+            set_sm_limit(self.sm_limit)
+        if self.dynamic:
+            set_gemm_schedule(True)
+        if self.ctas:
+            set_stream_ctas_per_sm(self.ctas)
+        return self
+
+    def __exit__(self, *exc):
+        if self.sm_limit:
+            set_sm_limit(0)
+        if self.dynamic:
+            set_gemm_schedule(False)
+        if self.ctas:
+            set_stream_ctas_per_sm(0)
+        return False

@@ -27,18 +27,21 @@ static thread_local const float* t_grad_scale = nullptr;
 const float* device_grad_scale() { return t_grad_scale; }
 void set_device_grad_scale(const float* p) { t_grad_scale = p; }
 
-static std::atomic<int> g_sm_limit{0};
-void set_sm_limit(int n) { g_sm_limit.store(n < 0 ? 0 : n, std::memory_order_relaxed); }
+// Launch options are per host thread, like the error text and the gradient scale: two optimizers stepping on
+// two threads do not see each other's settings.
+static thread_local int t_sm_limit = 0;
+void set_sm_limit(int n) { t_sm_limit = n < 0 ? 0 : n; }
 
-static std::atomic<int> g_gemm_dynamic{0};
-void set_gemm_schedule_dynamic(bool on) { g_gemm_dynamic.store(on ? 1 : 0, std::memory_order_relaxed); }
-bool gemm_schedule_dynamic() { return g_gemm_dynamic.load(std::memory_order_relaxed) != 0; }
+static thread_local int t_gemm_dynamic = 0;
+void set_gemm_schedule_dynamic(bool on) { t_gemm_dynamic = on ? 1 : 0; }
+bool gemm_schedule_dynamic() { return t_gemm_dynamic != 0; }
 
-static std::atomic<int> g_stream_ctas_per_sm{0};
-void set_stream_ctas_per_sm(int n) { g_stream_ctas_per_sm.store(n < 0 ? 0 : n, std::memory_order_relaxed); }
-bool stream_kernels_share_sms() { return g_stream_ctas_per_sm.load(std::memory_order_relaxed) > 0; }
+static thread_local int t_stream_ctas_per_sm = 0;
+// at most 32: scratch arrays of the reductions are sized for 32 CTAs per SM
+void set_stream_ctas_per_sm(int n) { t_stream_ctas_per_sm = n < 0 ? 0 : (n > 32 ? 32 : n); }
+bool stream_kernels_share_sms() { return t_stream_ctas_per_sm > 0; }
 long long stream_grid_cap(int sms) {
-  const int n = g_stream_ctas_per_sm.load(std::memory_order_relaxed);
+  const int n = t_stream_ctas_per_sm;
   return static_cast<long long>(sms) * (n > 0 ? n : 32);
 }
 
@@ -53,7 +56,7 @@ int sm_count() {
     cached_dev = dev;
     cached_sms = sms;
   }
-  const int limit = g_sm_limit.load(std::memory_order_relaxed);
+  const int limit = t_sm_limit;
   if (limit > 0 && limit < cached_sms) return limit;
   return cached_sms;
 }
@@ -75,7 +78,9 @@ int mmb_set_sm_limit(int n) {
 }
 
 int mmb_set_stream_ctas_per_sm(int n) {
-  mmb::set_stream_ctas_per_sm(n);
+  using namespace mmb;
+  MMB_REQUIRE(n >= 0 && n <= 32, "mmb_set_stream_ctas_per_sm: n = %d is outside 0..32", n);
+  set_stream_ctas_per_sm(n);
   return MMB_OK;
 }
 

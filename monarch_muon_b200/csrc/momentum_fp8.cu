@@ -19,6 +19,8 @@
 // = 6.0625 bytes; the kernel is bandwidth bound.
 #include "fp8_codec.cuh"
 
+#include <atomic>
+
 namespace mmb {
 namespace {
 
@@ -637,23 +639,23 @@ void launch_momentum_format(int format, int div_mode, bool all_fast, const SegTa
 
 }  // namespace
 
-int momentum_step_impl(const mmb_momentum_seg* segs, int nseg, int grad_dtype, int state_format, int div_mode,
-                       float beta, float grad_scale, int expand_min, float* block_sumsq_dev, float* scratch_dev,
-                       int64_t scratch_floats, void* stream) {
-  MMB_REQUIRE(nseg >= 0 && (nseg == 0 || segs != nullptr), "mmb_momentum_step: bad segment table");
-  MMB_REQUIRE(grad_dtype == MMB_BF16 || grad_dtype == MMB_F32, "mmb_momentum_step: grad_dtype %d", grad_dtype);
+int momentum_step_impl(const char* who, const mmb_momentum_seg* segs, int nseg, int grad_dtype, int state_format,
+                       int div_mode, float beta, float grad_scale, int expand_min, float* block_sumsq_dev,
+                       float* scratch_dev, int64_t scratch_floats, void* stream) {
+  MMB_REQUIRE(nseg >= 0 && (nseg == 0 || segs != nullptr), "%s: bad segment table", who);
+  MMB_REQUIRE(grad_dtype == MMB_BF16 || grad_dtype == MMB_F32, "%s: grad_dtype %d", who, grad_dtype);
   MMB_REQUIRE(state_format >= MMB_STATE_FP8_ABSMAX && state_format <= MMB_STATE_F32,
-              "mmb_momentum_step: state_format %d", state_format);
-  MMB_REQUIRE(div_mode >= MMB_DIV_IEEE && div_mode <= MMB_DIV_IEEE_STRICT, "mmb_momentum_step: div_mode %d", div_mode);
+              "%s: state_format %d", who, state_format);
+  MMB_REQUIRE(div_mode >= MMB_DIV_IEEE && div_mode <= MMB_DIV_IEEE_STRICT, "%s: div_mode %d", who, div_mode);
   if (nseg == 0) return MMB_OK;
   const int64_t need = mmb_momentum_scratch_floats(segs, nseg);
   if (block_sumsq_dev != nullptr)
     MMB_REQUIRE(scratch_dev != nullptr && scratch_floats >= need,
-                "mmb_momentum_step: scratch of %lld floats needed, %lld given", (long long)need,
+                "%s: scratch of %lld floats needed, %lld given", who, (long long)need,
                 (long long)scratch_floats);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int sms = sm_count();
-  if (sms <= 0) return fail(MMB_ERR_CUDA, "mmb_momentum_step: no CUDA device");
+  if (sms <= 0) return fail(MMB_ERR_CUDA, "%s: no CUDA device", who);
   float* partials = block_sumsq_dev != nullptr ? scratch_dev : nullptr;
 
   long long partial_base = 0;
@@ -664,18 +666,18 @@ int momentum_step_impl(const mmb_momentum_seg* segs, int nseg, int grad_dtype, i
     bool all_fast = true;
     for (int i = 0; i < tab.nseg; ++i) {
       const mmb_momentum_seg& s = segs[base + i];
-      MMB_REQUIRE(s.numel > 0 && s.grad != nullptr && s.state != nullptr, "mmb_momentum_step: segment %d empty",
+      MMB_REQUIRE(s.numel > 0 && s.grad != nullptr && s.state != nullptr, "%s: segment %d empty", who,
                   base + i);
       if (state_format == MMB_STATE_FP8_ABSMAX || state_format == MMB_STATE_FP8_EXPAND)
-        MMB_REQUIRE(s.scale != nullptr, "mmb_momentum_step: segment %d has no scale array", base + i);
+        MMB_REQUIRE(s.scale != nullptr, "%s: segment %d has no scale array", who, base + i);
       if (state_format == MMB_STATE_FP8_EXPAND)
         MMB_REQUIRE(s.expand != nullptr && s.sqrt_minmax != nullptr,
-                    "mmb_momentum_step: segment %d lacks expand/sqrt_minmax", base + i);
+                    "%s: segment %d lacks expand/sqrt_minmax", who, base + i);
       const Plan p = plan_segment(s);
       if (block_sumsq_dev != nullptr)
         MMB_REQUIRE(p.block_elems == s.block_elems,
-                    "mmb_momentum_step: block_elems %lld of segment %d must be a multiple of 128 dividing numel "
-                    "when block sums are requested", (long long)s.block_elems, base + i);
+                    "%s: block_elems %lld of segment %d must be a multiple of 128 dividing numel "
+                    "when block sums are requested", who, (long long)s.block_elems, base + i);
       SegDev& d = tab.seg[i];
       d.grad = s.grad;
       d.state = s.state;
@@ -735,7 +737,9 @@ static __device__ __align__(256) float g_static_partials[STATIC_SCRATCH_FLOATS];
 namespace mmb {
 namespace {
 constexpr int MAX_DEVICES = 64;
-float* g_static_partials_addr[MAX_DEVICES] = {nullptr};
+// One slot per device ordinal, filled on the first call on that device.  Atomic because two host threads may
+// make that first call at once (both then store the same address).
+std::atomic<float*> g_static_partials_addr[MAX_DEVICES];
 
 // In host code `g_static_partials` is only a handle for the runtime, not a
 // device address; the address on the current device has to be asked for.
@@ -743,12 +747,14 @@ int static_partials_for_current_device(float** out) {
   int dev = -1;
   MMB_CUDA_CHECK(cudaGetDevice(&dev));
   MMB_REQUIRE(dev >= 0 && dev < MAX_DEVICES, "mmb_momentum_step_static: device index %d not supported", dev);
-  if (g_static_partials_addr[dev] == nullptr) {
+  float* cached = g_static_partials_addr[dev].load(std::memory_order_acquire);
+  if (cached == nullptr) {
     void* p = nullptr;
     MMB_CUDA_CHECK(cudaGetSymbolAddress(&p, g_static_partials));
-    g_static_partials_addr[dev] = static_cast<float*>(p);
+    cached = static_cast<float*>(p);
+    g_static_partials_addr[dev].store(cached, std::memory_order_release);
   }
-  *out = g_static_partials_addr[dev];
+  *out = cached;
   return MMB_OK;
 }
 }  // namespace
@@ -769,8 +775,8 @@ int64_t mmb_momentum_scratch_floats(const mmb_momentum_seg* segs, int nseg) {
 int mmb_momentum_step(const mmb_momentum_seg* segs, int nseg, int grad_dtype, int state_format, int div_mode,
                       float beta, float grad_scale, int expand_min, float* block_sumsq_dev, float* scratch_dev,
                       int64_t scratch_floats, void* stream) {
-  return mmb::momentum_step_impl(segs, nseg, grad_dtype, state_format, div_mode, beta, grad_scale, expand_min,
-                                 block_sumsq_dev, scratch_dev, scratch_floats, stream);
+  return mmb::momentum_step_impl("mmb_momentum_step", segs, nseg, grad_dtype, state_format, div_mode, beta, grad_scale,
+                                 expand_min, block_sumsq_dev, scratch_dev, scratch_floats, stream);
 }
 
 int64_t mmb_momentum_static_max_floats(void) { return STATIC_SCRATCH_FLOATS; }
@@ -787,8 +793,8 @@ int mmb_momentum_step_static(const mmb_momentum_seg* segs, int nseg, int grad_dt
   float* scratch = nullptr;
   int rc = static_partials_for_current_device(&scratch);
   if (rc != MMB_OK) return rc;
-  return momentum_step_impl(segs, nseg, grad_dtype, state_format, div_mode, beta, grad_scale, expand_min,
-                            block_sumsq_dev, scratch, STATIC_SCRATCH_FLOATS, stream);
+  return momentum_step_impl("mmb_momentum_step_static", segs, nseg, grad_dtype, state_format, div_mode, beta,
+                            grad_scale, expand_min, block_sumsq_dev, scratch, STATIC_SCRATCH_FLOATS, stream);
 }
 
 int mmb_fp8_quantize(const float* value_dev, uint8_t* codes_dev, float* scale_dev, float* expand_dev,

@@ -31,7 +31,7 @@ def groups_of(numel: int) -> int:
 
 
 def quantize_(state: dict, name: str, value: torch.Tensor, signed: bool = True, dtype=torch.float8_e4m3fn,
-              expand_min: int = 16, codec: str = "expand", div_mode: int = _lib.DIV_IEEE) -> None:
+              expand_min: int = 16, codec: str = "expand", div_mode: int = _lib.DIV_DEFAULT) -> None:
     """Store fp32 `value` as state[name] (E4M3 codes, value's shape) plus the
     per-group side arrays state['scale_'+name] (and 'expand_', 'sqrt_minmax_'
     for the expansion codec), allocating them on first use."""
@@ -110,7 +110,7 @@ class MomentumPlan:
 
 
 def momentum_step(segs, nseg: int, *, grad_dtype: torch.dtype, state_format: int, beta: float,
-                  grad_scale: float = 1.0, div_mode: int = _lib.DIV_IEEE, expand_min: int = 16,
+                  grad_scale: float = 1.0, div_mode: int = _lib.DIV_DEFAULT, expand_min: int = 16,
                   block_sumsq: torch.Tensor | None = None, scratch: torch.Tensor | None = None) -> None:
     """Launch the fused momentum kernel over a prepared segment table."""
     lib = _lib.load()
@@ -126,7 +126,7 @@ def scratch_floats(segs, nseg: int) -> int:
 def fp8_momentum_flat(codes: torch.Tensor, scales: torch.Tensor, grad: torch.Tensor, beta: float, *,
                       m_bf16: torch.Tensor | None = None, block_elems: int | None = None,
                       block_sumsq: torch.Tensor | None = None, grad_scale: float = 1.0,
-                      div_mode: int = _lib.DIV_IEEE, expand: torch.Tensor | None = None,
+                      div_mode: int = _lib.DIV_DEFAULT, expand: torch.Tensor | None = None,
                       sqrt_minmax: torch.Tensor | None = None, expand_min: int = 16) -> None:
     """One FP8-state heavy-ball step on a flat buffer, in place:
     codes (uint8/E4M3 [n]), scales (fp32 [ceil(n/128)]), grad (bf16/fp32 [n]).

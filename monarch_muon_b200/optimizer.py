@@ -58,7 +58,12 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
     state_format : "param" keeps `momentum_buffer` in the parameter dtype like
         the reference; "fp8_absmax" / "fp8_expand" store it as E4M3 codes with
         per-128-group side arrays (absmax scale, or COAT range expansion).
-    fp8_div : "ieee", "full" or "ieee_strict" - arithmetic of the FP8 quantiser (MMB_DIV_* in the header).
+    fp8_div : arithmetic of the FP8 quantiser (MMB_DIV_* in the header).  "full" (default) uses the GPU
+        instructions the reference's Triton kernels compile to, so FP8 absmax codes and scales equal the
+        reference kernel's bit for bit on the same GPU; "ieee" uses IEEE division and equals the CPU
+        oracle bit for bit (and, for the range-expansion format, forms powers on the special-function
+        unit: faster, about one code in 10^4 differs); "ieee_strict" is "ieee" through the compiler's
+        division and the library powf everywhere.
     ns_backend : "tcgen05" (tensor cores) or "simt" (cross-check kernel).
     ns_max_batch : slice Newton-Schulz into at most this many blocks per call
         to bound its workspace.
@@ -72,7 +77,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
 
     def __init__(self, muon_params, adamw_params, *, lr: float = 5e-3, momentum: float = 0.95,
                  adamw_betas: tuple[float, float] = (0.9, 0.95), adamw_weight_decay: float = 0.1,
-                 adamw_eps: float = 1e-8, state_format: str = "param", fp8_div: str = "ieee",
+                 adamw_eps: float = 1e-8, state_format: str = "param", fp8_div: str = "full",
                  ns_backend: str = "tcgen05", ns_max_batch: int | None = 256, expand_min: int = 16,
                  overlap: bool = False):
         if state_format not in _STATE_FORMATS:
@@ -87,7 +92,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         ]
         super().__init__(param_groups, defaults)
         self.state_format = state_format
-        self.fp8_div = {"ieee": _lib.DIV_IEEE, "full": _lib.DIV_FULL, "ieee_strict": _lib.DIV_IEEE_STRICT}[fp8_div]
+        self.fp8_div = _lib.DIV_NAMES[fp8_div]
         self.ns_backend = {"tcgen05": _lib.NS_TCGEN05, "simt": _lib.NS_SIMT}[ns_backend]
         self.ns_max_batch = ns_max_batch
         self.expand_min = expand_min
@@ -124,7 +129,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
             _lib.load().mmb_set_device_grad_scale(self._clip_out[1:].data_ptr())
         try:
             groups = list(self.param_groups)
-            overlapping = self.overlap and self._host is None and self._marks_allow_overlap()
+            overlapping = self.overlap and self._host is None
             if overlapping:
                 # AdamW groups are stepped on the side stream while the first slice is in Newton-Schulz
                 muon = [g for g in groups if g["update_type"] == "muon" and any(p.grad is not None for p in g["params"])]
@@ -169,9 +174,6 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
     def enable_phase_timing(self, on: bool = True) -> None:
         self._marks = [] if on else None
         self._open = {}
-
-    def _marks_allow_overlap(self) -> bool:
-        return True
 
     def _mark(self, phase: str) -> None:
         """"begin" opens a span on the current stream, any other name closes it under that name.  Spans
@@ -405,8 +407,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         side = self._side_streams.get(dev)
         if side is None:
             side = self._side_streams[dev] = torch.cuda.Stream(device=dev)
-        _lib.set_gemm_schedule(True)                    # pairs that find their SMs taken draw fewer tiles
-        try:
+        with _lib.launch_options(dynamic_schedule=True):   # pairs that find their SMs taken draw fewer tiles
             side.wait_stream(main)                      # gradients and last step's weights are ready
             n = len(slices)
             mom_done = [torch.cuda.Event() for _ in range(n)]
@@ -443,8 +444,6 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                 self._slice_update(lr, slices[n - 1])
                 self._mark("update")
             main.wait_stream(side)
-        finally:
-            _lib.set_gemm_schedule(False)
 
     def _slice_momentum(self, group, plan, sl) -> None:
         """Momentum (+codec, +bf16 copy, +block norms) of one slice; tables are cached, only gradient

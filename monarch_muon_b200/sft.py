@@ -99,10 +99,14 @@ class SFTOptimizer(torch.optim.Optimizer):
             segs = (_lib.MomentumSeg * len(ps))()
             upd = (_lib.MasterUpdateSeg * len(ps))()
             at = 0
+            keep = []        # contiguous copies of strided gradients must outlive the launch that reads them
             for k, (p, nb) in enumerate(zip(ps, counts)):
                 st = self._state_for(p, group)
                 st["step"] += 1
-                g = p.grad if p.grad.is_contiguous() else p.grad.contiguous()
+                g = p.grad
+                if not g.is_contiguous():
+                    g = g.contiguous()
+                    keep.append(g)
                 segs[k].grad = g.data_ptr()
                 segs[k].state = st["momentum"].data_ptr()
                 segs[k].m_bf16 = stack[at:].data_ptr()
@@ -174,17 +178,22 @@ class SFTOptimizer(torch.optim.Optimizer):
         self._adam_steps.clear()
 
 
+_NOT_MUON = ("embed_tokens", "lm_head")     # token embedding and output head stay with AdamW
+
+
 def parameter_groups(model, optimizer: str, lr: float, config: dict):
-    """The reference's split (finetune/sft_optimizer.py:62-71): matrices other than the embeddings and
-    the output head go to Muon, everything else to AdamW with `config["muon_adamw_lr"]`; with
-    optimizer == "adamw" one AdamW group holds everything."""
-    matrix, auxiliary = [], []
-    for name, p in model.named_parameters():
-        if p.ndim >= 2 and "embed_tokens" not in name and "lm_head" not in name:
-            matrix.append(p)
-        else:
-            auxiliary.append(p)
+    """Param groups for SFTOptimizer, with the reference's rule for who gets which algorithm
+    (finetune/sft_optimizer.py:62-71).
+
+    A parameter is stepped by Muon when it is a matrix or a stack of matrices (two or more dimensions) and
+    is neither the token embedding nor the output head; all others are stepped by AdamW at the learning
+    rate `config["muon_adamw_lr"]`.  Muon groups carry no weight decay.  Asking for "adamw" puts every
+    parameter, in the same order (Muon candidates first), into a single AdamW group at `lr`."""
+    named = list(model.named_parameters())
+    is_muon = {id(p): p.ndim >= 2 and not any(tag in name for tag in _NOT_MUON) for name, p in named}
+    muon_side = [p for _, p in named if is_muon[id(p)]]
+    adamw_side = [p for _, p in named if not is_muon[id(p)]]
     if optimizer == "adamw":
-        return [{"params": matrix + auxiliary, "algorithm": "adamw", "lr": lr}]
-    return [{"params": matrix, "algorithm": "muon", "lr": lr, "weight_decay": 0.0},
-            {"params": auxiliary, "algorithm": "adamw", "lr": config["muon_adamw_lr"]}]
+        return [dict(params=muon_side + adamw_side, algorithm="adamw", lr=lr)]
+    return [dict(params=muon_side, algorithm="muon", lr=lr, weight_decay=0.0),
+            dict(params=adamw_side, algorithm="adamw", lr=config["muon_adamw_lr"])]

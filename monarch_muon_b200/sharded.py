@@ -168,16 +168,42 @@ class ShardedMonarchMuon:
         return dist.all_reduce(whole, op=dist.ReduceOp.SUM, group=self.ag_group, async_op=True)
 
     # ------------------------------------------------------------------- step
+    def _check_gradients_in_arena(self) -> None:
+        """Every parameter's .grad must still be the arena view installed at construction: the
+        reduce-scatter sends the arena, not whatever tensor autograd may have put there instead.
+        `model.zero_grad()` (set_to_none=True by default) and `p.grad = None` break that; a fresh
+        gradient found here is copied into the arena and the view is put back."""
+        for params, places in ((self.muon_params, [(pl.offset,) for pl in self.plan.muon]),
+                               (self.adamw_params, [(off,) for _, off, _ in self.plan.adamw])):
+            for p, (offset,) in zip(params, places):
+                view = self.g_arena[offset:offset + p.numel()].view(p.shape)
+                g = p.grad
+                if g is None:
+                    view.zero_()                       # no gradient this step: contributes nothing to the sum
+                    p.grad = view
+                elif g.data_ptr() != view.data_ptr() or not g.is_contiguous():
+                    if g.shape != p.shape:
+                        raise ValueError("gradient shape differs from its parameter")
+                    view.copy_(g)
+                    p.grad = view
+
     @torch.no_grad()
     def step(self):
-        nchunks = len(self.plan.chunks)
-        if self.comm_sms > 0 and self.backend == "nccl":
+        self._check_gradients_in_arena()
+        nccl = self.backend == "nccl"
+        if nccl:
             from . import _lib
             total = torch.cuda.get_device_properties(self.device).multi_processor_count
-            _lib.set_sm_limit(max(2, total - self.comm_sms))
-        if self.dynamic_schedule and self.backend == "nccl":
-            from . import _lib
-            _lib.set_gemm_schedule(True)
+            options = _lib.launch_options(sm_limit=max(2, total - self.comm_sms) if self.comm_sms > 0 else 0,
+                                          dynamic_schedule=self.dynamic_schedule)
+        else:
+            import contextlib
+            options = contextlib.nullcontext()
+        with options:                                  # launch options are put back even if a local step raises
+            self._step_chunks()
+
+    def _step_chunks(self):
+        nchunks = len(self.plan.chunks)
         rs = []
         for k in range(nchunks):
             g_whole, g_mine, _, _ = self.chunk_views(k)
@@ -204,16 +230,19 @@ class ShardedMonarchMuon:
             ag.append(self._all_gather(w_whole, w_mine))
         for w in ag:
             w.wait()
-        if self.comm_sms > 0 and self.backend == "nccl":
-            from . import _lib
-            _lib.set_sm_limit(0)
-        if self.dynamic_schedule and self.backend == "nccl":
-            from . import _lib
-            _lib.set_gemm_schedule(False)
 
     def zero_grad(self, set_to_none: bool = False):
-        """Gradients are arena views and stay allocated; they are zeroed in place."""
+        """Gradients are arena views and stay allocated; they are zeroed in place (set_to_none is
+        accepted for signature compatibility and ignored).  Prefer this to model.zero_grad(): gradients
+        that were replaced or dropped are found by step() and copied back into the arena, at the cost
+        of that copy."""
         self.g_arena.zero_()
+        for p, pl in zip(self.muon_params, self.plan.muon):
+            if p.grad is None or p.grad.data_ptr() != self.g_arena[pl.offset:].data_ptr():
+                p.grad = self.g_arena[pl.offset:pl.offset + p.numel()].view(p.shape)
+        for p, (_, off, _) in zip(self.adamw_params, self.plan.adamw):
+            if p.grad is None or p.grad.data_ptr() != self.g_arena[off:].data_ptr():
+                p.grad = self.g_arena[off:off + p.numel()].view(p.shape)
 
     def state_dict(self):
         """Per-rank shard: the local optimizers' state, in chunk order."""

@@ -204,7 +204,7 @@ def test_fp8_absmax_momentum_bit_exact(mm, n, block, gdtype):
         codes, scales, m32, m16 = fp8_oracle.absmax_momentum_step(codes, scales, g, 0.95)
         d_ss = torch.zeros(nblk, device="cuda")
         mm["fp8"].fp8_momentum_flat(d_codes, d_scales, g.cuda(), 0.95, m_bf16=d_m, block_elems=block,
-                                    block_sumsq=d_ss)
+                                    block_sumsq=d_ss, div_mode=mm["lib"].DIV_IEEE)
         assert torch.equal(d_codes.cpu(), codes), f"codes differ at step {step}"
         assert np.array_equal(d_scales.cpu().numpy().view(np.uint32), scales.numpy().view(np.uint32))
         assert torch.equal(d_m.cpu(), m16)
@@ -220,7 +220,7 @@ def test_fp8_momentum_grad_scale_and_full_div(mm):
     g = (torch.randn(n, generator=gen) * 1e-3).bfloat16()
     want = fp8_oracle.absmax_momentum_step(codes, scales, g, 0.95, grad_scale=0.125)
     dc, ds = codes.cuda(), scales.cuda()
-    mm["fp8"].fp8_momentum_flat(dc, ds, g.cuda(), 0.95, grad_scale=0.125)
+    mm["fp8"].fp8_momentum_flat(dc, ds, g.cuda(), 0.95, grad_scale=0.125, div_mode=mm["lib"].DIV_IEEE)
     assert torch.equal(dc.cpu(), want[0]) and torch.equal(ds.cpu(), want[1])
     # approximate-division mode (what the reference's Triton build emits): scales within 2 ulp,
     # codes equal except where the quotient sits on a rounding boundary
@@ -292,7 +292,7 @@ def test_standalone_codecs(mm, codec, signed):
     g = gi.coat_input()
     v = g if signed else g * g
     st = {}
-    mm["fp8"].quantize_(st, "exp_avg", v.cuda(), signed=signed, codec=codec)
+    mm["fp8"].quantize_(st, "exp_avg", v.cuda(), signed=signed, codec=codec, div_mode=mm["lib"].DIV_IEEE)
     back = mm["fp8"].dequantize(st, "exp_avg", signed=signed)
     if codec == "absmax":
         codes, scales = fp8_oracle.absmax_quant(v)

@@ -114,7 +114,7 @@ def test_fp32_weights_close_to_fp32_newton_schulz_oracle():
 def test_fp8_absmax_state_is_bit_exact(case):
     from oracle import fp8_oracle, muon_oracle
     from monarch_muon_b200 import CoatStateMonarchMuon
-    opt, muon, adamw = _ours(case, cls=CoatStateMonarchMuon, codec="absmax")
+    opt, muon, adamw = _ours(case, cls=CoatStateMonarchMuon, codec="absmax", fp8_div="ieee")     # the CPU oracle divides IEEE
     _, _, _, hyper = gi.OPT_CASES[case]
     # oracle chain per tensor: codes/scales start at zero (state created as zeros)
     chain = [None] * len(muon)
@@ -401,7 +401,7 @@ def test_fused_fp8_adamw_against_oracle(codec, dtype):
     ref = [t.clone() for t in w]
     hyper = dict(lr=3e-3, betas=(0.9, 0.95), weight_decay=0.1, eps=1e-8)
     opt = CoatStateMonarchMuon([], ours, lr=hyper["lr"], adamw_betas=hyper["betas"],
-                               adamw_weight_decay=hyper["weight_decay"], adamw_eps=hyper["eps"], codec=codec)
+                               adamw_weight_decay=hyper["weight_decay"], adamw_eps=hyper["eps"], codec=codec, fp8_div="ieee")
     nside = 3 if codec == "expand" else 1
     zero_state = lambda n: (torch.zeros(n, dtype=torch.uint8),) + tuple(torch.ones(-(-n // 128)) for _ in range(nside))
     states = [(zero_state(t.numel()), zero_state(t.numel())) for t in w]
