@@ -325,6 +325,8 @@ def main():
     ap.add_argument("--fp8-div", default="full", choices=["full", "ieee", "ieee_strict"],
                     help="arithmetic of the FP8 quantiser: full (default; the reference kernels' GPU instructions, "
                          "bit-exact with them for the absmax codec), ieee (bit-exact with the CPU oracle)")
+    ap.add_argument("--fused-update", type=int, default=1, choices=[0, 1],
+                    help="weight update in the last Newton-Schulz GEMM's epilogue (1, default) or as its own kernel (0)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-subrecords", action="store_true",
                     help="leave out the extra measurements of the default line (isolated kernels, the reference's "
@@ -376,11 +378,12 @@ def main():
         from monarch_muon_b200 import CoatStateMonarchMuon
         opt = CoatStateMonarchMuon(muon, adamw, lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95),
                                    adamw_weight_decay=0.1, adamw_eps=1e-8, ns_max_batch=args.ns_max_batch,
-                                   overlap=bool(args.overlap), fp8_div=args.fp8_div)
+                                   overlap=bool(args.overlap), fp8_div=args.fp8_div, fuse_update=bool(args.fused_update))
     else:
         opt = MonarchMuonOptimizer(muon, adamw, lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95),
                                    adamw_weight_decay=0.1, adamw_eps=1e-8, state_format=args.state_format,
-                                   ns_max_batch=args.ns_max_batch, overlap=bool(args.overlap), fp8_div=args.fp8_div)
+                                   ns_max_batch=args.ns_max_batch, overlap=bool(args.overlap), fp8_div=args.fp8_div,
+                                   fuse_update=bool(args.fused_update))
     if args.state_format != "fp8_absmax":
         config["workload"] = config["workload"].replace("FP8 E4M3 absmax momentum state",
                                                         f"momentum state format {args.state_format}")

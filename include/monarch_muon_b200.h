@@ -177,6 +177,24 @@ int mmb_newton_schulz(const void* x_dev, void* out_dev, const float* block_sumsq
                       int rows, int cols, void* workspace_dev, int64_t workspace_bytes, int backend,
                       int32_t* status_dev, void* stream);
 
+/* Newton-Schulz and the Muon weight update in one call:
+ *   W[b] <- W[b] + alpha * NS(X)[b],   alpha = -lr * sqrt(rows / cols)
+ * Replaces _newton_schulz_batched followed by `param.data.add_(ortho, alpha=)`,
+ * monarch_muon.py:36-50 and :160-165 (membench twin :167-170).  With the
+ * tensor-core back end the update is the epilogue of the last GEMM: the
+ * orthogonalised block never reaches memory; each result tile is rounded to bf16
+ * (the value mmb_newton_schulz would store) and added to the weights with one
+ * fused multiply-add and one rounding to the weights' type, exactly what the
+ * stored result followed by mmb_muon_update gives.
+ *   x_dev            bf16 [batch, rows, cols], only read
+ *   weight_ptrs_dev  DEVICE array of `batch` pointers, entry b = block b's
+ *                    rows x cols weights (row-major, 16-byte aligned)
+ *   weight_dtype     MMB_BF16 or MMB_F32
+ * Other arguments as for mmb_newton_schulz. */
+int mmb_newton_schulz_update(const void* x_dev, const float* block_sumsq_dev, int batch, int rows, int cols,
+                             void* const* weight_ptrs_dev, int weight_dtype, float alpha, void* workspace_dev,
+                             int64_t workspace_bytes, int backend, int32_t* status_dev, void* stream);
+
 /* One batched GEMM of the family Newton-Schulz is built from (exposed for
  * tests and profiling):
  *   D[b] = sigma_b * alpha * opA[b] . opB[b]^T + diag * I
@@ -320,9 +338,22 @@ int mmb_set_device_grad_scale(const float* scale_dev);
  * failed self-check stores a non-zero code here and the kernel returns.
  * mmb_device_status_read synchronises `stream` and returns the word.
  * ---------------------------------------------------------------------- */
+/* Status codes a kernel may store (0 = nothing to report). */
+#define MMB_STATUS_WAIT_PRODUCER_EMPTY 0x101 /* a TMA producer waited too long for a free stage            */
+#define MMB_STATUS_WAIT_MMA_FULL 0x102       /* the MMA issuer waited too long for operands                 */
+#define MMB_STATUS_WAIT_MMA_TMEM_EMPTY 0x103 /* the MMA issuer waited too long for a drained accumulator     */
+#define MMB_STATUS_WAIT_EPI_TMEM_FULL 0x104  /* an epilogue warp waited too long for an accumulator          */
+#define MMB_STATUS_WAIT_SCHED_FULL 0x105     /* a role waited too long for its next tile number              */
+#define MMB_STATUS_WAIT_SCHED_EMPTY 0x106    /* the tile scheduler waited too long for a slot                */
+#define MMB_STATUS_WAIT_PROBE 0x1F0          /* mmb_wait_probe: the unanswered wait expired, as it must      */
 int mmb_device_status_create(int32_t** status_dev_out);
 int mmb_device_status_destroy(int32_t* status_dev);
 int mmb_device_status_read(int32_t* status_dev, int32_t* host_out, int reset, void* stream);
+/* Self-test of the bounded wait (no counterpart in the reference): launches one warp that waits, with the
+ * same wait routine the GEMM roles use and a limit of `limit_cycles` SM cycles (1 .. 2e9), on a barrier that
+ * nothing ever arrives at.  The wait expires, the kernel stores MMB_STATUS_WAIT_PROBE in the status word
+ * and returns; the device stays usable.  Nothing faults, traps or hangs. */
+int mmb_wait_probe(int64_t limit_cycles, int32_t* status_dev, void* stream);
 
 #ifdef __cplusplus
 }

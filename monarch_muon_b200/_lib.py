@@ -23,6 +23,11 @@ DIV_IEEE, DIV_FULL, DIV_IEEE_STRICT = 0, 1, 2
 DIV_DEFAULT = DIV_FULL
 DIV_NAMES = {"full": DIV_FULL, "ieee": DIV_IEEE, "ieee_strict": DIV_IEEE_STRICT}
 NS_TCGEN05, NS_SIMT = 0, 1
+STATUS_NAMES = {0x101: "TMA producer waited too long for a free stage", 0x102: "MMA issuer waited too long for operands",
+                0x103: "MMA issuer waited too long for a drained accumulator",
+                0x104: "epilogue waited too long for an accumulator", 0x105: "a role waited too long for its next tile",
+                0x106: "tile scheduler waited too long for a slot", 0x1F0: "wait probe expired (expected)"}
+STATUS_WAIT_PROBE = 0x1F0
 GEMM_K, GEMM_MN, GEMM_SYM = 0, 1, 2
 
 
@@ -80,6 +85,8 @@ SYMBOLS = {
     "mmb_fp8_dequantize": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _vp]),
     "mmb_ns_workspace_bytes": (_i64, [_i, _i, _i]),
     "mmb_newton_schulz": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _i64, _i, _vp, _vp]),
+    "mmb_newton_schulz_update": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _f, _vp, _i64, _i, _vp, _vp]),
+    "mmb_wait_probe": (_i, [_i64, _vp, _vp]),
     "mmb_gemm_occupancy": (_i, [_i, C.POINTER(C.c_int)]),
     "mmb_gemm_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _i, _i, _vp, _vp]),
     "mmb_muon_update": (_i, [C.POINTER(UpdateSeg), _i, _i, _f, _vp]),

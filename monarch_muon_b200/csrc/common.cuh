@@ -70,6 +70,7 @@ enum : int32_t {
   STATUS_WAIT_EPI_TMEM_FULL = 0x104,   // epilogue waited too long for an accumulator
   STATUS_WAIT_SCHED_FULL = 0x105,      // a role waited too long for its next tile number
   STATUS_WAIT_SCHED_EMPTY = 0x106,     // the tile scheduler waited too long for a slot to be returned
+  STATUS_WAIT_PROBE = 0x1F0,           // mmb_wait_probe(): the deliberately unanswered wait expired, as it must
 };
 
 #ifdef __CUDACC__

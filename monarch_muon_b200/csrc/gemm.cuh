@@ -20,10 +20,16 @@ struct GemmCall {
   const float* inv_norm;  // per batch, may be null
   int sigma_pow;          // sigma_b = inv_norm[b]^sigma_pow, 0..2
   int* sched = nullptr;   // two zeroed ints in device memory for the dynamic tile schedule (null: static schedule)
+  // Fused Muon update (tensor-core back end): when upd_w is set the result is not written to d; block b's
+  // weights upd_w[b] (M x N, row-major, 16-byte aligned) become W + upd_alpha * bf16(result) instead.
+  void* const* upd_w = nullptr;
+  float upd_alpha = 0.0f;
+  int upd_f32 = 0;
 };
 
 int gemm_tcgen05(const GemmCall& g, int32_t* status, cudaStream_t st);
 int gemm_simt(const GemmCall& g, cudaStream_t st);
 int gemm_occupancy(int pair, int* out);
+int wait_probe(long long limit_cycles, int32_t* status, cudaStream_t st);
 
 }  // namespace mmb

@@ -98,6 +98,11 @@ struct GemmArgs {
   int sigma_pow;
   int32_t* status;
   int* sched;  // dynamic schedule: [0] next tile number, [1] pairs that have seen the end; both 0 at launch
+  // fused weight update (UPD kernels): the result is not stored; instead W[b] <- W[b] + upd_alpha * bf16(result)
+  void* const* upd_w;   // per batch entry, pointer to that block's M x N weights (row-major, 16-byte aligned)
+  float upd_alpha;
+  int upd_f32;          // weights are fp32 (else bf16)
+  long long wait_limit; // SM cycles a role may wait on a barrier before it gives up
 };
 
 // ------------------------------------------------------------------ PTX glue
@@ -173,7 +178,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
 // cycles (clock64): 4e9 cycles is about two seconds at 2 GHz.
 template <bool CLUSTER_ACQUIRE = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                          int32_t code) {
+                                          int32_t code, long long limit = WAIT_LIMIT_CYCLES) {
   long long t0 = 0;
   for (uint32_t spin = 1;; ++spin) {
     if (CLUSTER_ACQUIRE ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
@@ -182,7 +187,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       const long long now = clock64();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > WAIT_LIMIT_CYCLES) {
+      } else if (now - t0 > limit) {
         *abort_flag = 1;
         if (status != nullptr) atomicCAS(status, 0, code);
         return false;
@@ -321,9 +326,10 @@ struct TileCursor {
   uint32_t n = 0;  // tiles drawn so far by this consumer
 };
 __device__ __forceinline__ long long draw_tile(TileCursor& c, uint32_t sched_full, uint32_t sched_empty,
-                                               const volatile int* slots, volatile int* abort_flag, int32_t* status) {
+                                               const volatile int* slots, volatile int* abort_flag, int32_t* status,
+                                               long long limit) {
   const uint32_t q = c.n % SCHED_DEPTH, ph = (c.n / SCHED_DEPTH) & 1u;
-  if (!mbar_wait<true>(sched_full + 8 * q, ph, abort_flag, status, STATUS_WAIT_SCHED_FULL)) return -1;
+  if (!mbar_wait<true>(sched_full + 8 * q, ph, abort_flag, status, STATUS_WAIT_SCHED_FULL, limit)) return -1;
   const int t = slots[q];
   mbar_arrive_cluster(mapa(sched_empty + 8 * q, 1));   // the ring's owner is the odd CTA (also when that is us)
   ++c.n;
@@ -334,7 +340,10 @@ __device__ __forceinline__ long long draw_tile(TileCursor& c, uint32_t sched_ful
 // 112 registers per thread (13 warps: 46,592 of the SM's 65,536) leave room for one 256-thread CTA of a
 // streaming kernel (64 registers) on the same SM, so momentum / update / AdamW launches on another
 // stream run beside the GEMMs instead of queueing behind them.
-template <int BN, bool PAIR, bool DYN = false>
+// UPD: the epilogue does not store the result; it rounds it to bf16 (the value the plain epilogue would
+// have stored) and applies the Muon weight update W <- W + alpha * result to the block's weights in place,
+// with one fused multiply-add and one rounding to the weights' type (what torch's add_(other, alpha=) does).
+template <int BN, bool PAIR, bool DYN = false, bool UPD = false>
 __global__ void __maxnreg__(112)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__ CUtensorMap map_a_mn,
             const __grid_constant__ CUtensorMap map_b_k, const __grid_constant__ CUtensorMap map_b_mn,
@@ -428,9 +437,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
       const CUtensorMap* map_k = is_a ? &map_a_k : &map_b_k;
       const CUtensorMap* map_mn = is_a ? &map_a_mn : &map_b_mn;
       TileCursor cursor;
-      for (long long t = DYN ? draw_tile(cursor, sched_full, sched_empty, sched_slots, abort_flag, args.status) : first_tile;
+      for (long long t = DYN ? draw_tile(cursor, sched_full, sched_empty, sched_slots, abort_flag, args.status, args.wait_limit) : first_tile;
            ok && t >= 0 && t < args.total_tiles;
-           t = DYN ? draw_tile(cursor, sched_full, sched_empty, sched_slots, abort_flag, args.status) : t + tile_step) {
+           t = DYN ? draw_tile(cursor, sched_full, sched_empty, sched_slots, abort_flag, args.status, args.wait_limit) : t + tile_step) {
         int b, m0, n0;
         tile_coords<BN, TILE_M>(t, args, b, m0, n0);
         const int r_tile = is_a ? m0 : n0;                       // decides K-major vs mirrored fetch
@@ -439,7 +448,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
           if (slice % PRODUCERS_PER_OPERAND != turn) continue;
           const uint32_t stage = slice % STAGES;
           const uint32_t phase = (slice / STAGES) & 1u;
-          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, args.status, STATUS_WAIT_PRODUCER_EMPTY)) {
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, args.status, STATUS_WAIT_PRODUCER_EMPTY, args.wait_limit)) {
             ok = false;
             break;
           }
@@ -482,14 +491,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
       uint32_t local = 0;
       bool ok = true;
       TileCursor cursor;
-      for (long long t = DYN ? draw_tile(cursor, sched_full, sched_empty, sched_slots, abort_flag, args.status) : first_tile;
+      for (long long t = DYN ? draw_tile(cursor, sched_full, sched_empty, sched_slots, abort_flag, args.status, args.wait_limit) : first_tile;
            ok && t >= 0 && t < args.total_tiles;
-           t = DYN ? draw_tile(cursor, sched_full, sched_empty, sched_slots, abort_flag, args.status) : t + tile_step, ++local) {
+           t = DYN ? draw_tile(cursor, sched_full, sched_empty, sched_slots, abort_flag, args.status, args.wait_limit) : t + tile_step, ++local) {
         int b, m0, n0;
         tile_coords<BN, TILE_M>(t, args, b, m0, n0);
         const uint32_t acc = local & 1u;
         const uint32_t acc_phase = (local >> 1) & 1u;
-        if (!mbar_wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, args.status, STATUS_WAIT_MMA_TMEM_EMPTY)) {
+        if (!mbar_wait(tmem_empty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, args.status, STATUS_WAIT_MMA_TMEM_EMPTY, args.wait_limit)) {
           ok = false;
           break;
         }
@@ -507,7 +516,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
           const uint32_t idesc = IDESC_BASE | ((ak ? 0u : 1u) << 15) | ((bk ? 0u : 1u) << 16);
           const uint32_t a_step = ak ? K_STEP : MN_STEP;
           const uint32_t b_step = bk ? K_STEP : MN_STEP;
-          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, args.status, STATUS_WAIT_MMA_FULL)) {
+          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, args.status, STATUS_WAIT_MMA_FULL, args.wait_limit)) {
             ok = false;
             break;
           }
@@ -530,7 +539,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
       for (uint32_t i = 0;; ++i) {
         const uint32_t q = i % SCHED_DEPTH, ph = (i / SCHED_DEPTH) & 1u;
         // every consumer of both CTAs has read the slot's previous tile (immediate on the first lap)
-        if (!mbar_wait<true>(sched_empty + 8 * q, ph ^ 1u, abort_flag, args.status, STATUS_WAIT_SCHED_EMPTY)) break;
+        if (!mbar_wait<true>(sched_empty + 8 * q, ph ^ 1u, abort_flag, args.status, STATUS_WAIT_SCHED_EMPTY, args.wait_limit)) break;
         const int drawn = atomicAdd(args.sched, 1);
         const int tile = drawn < total ? drawn : -1;
         sched_slots[q] = tile;
@@ -567,7 +576,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
     auto next_tile = [&](long long prev) -> long long {
       if (!DYN) return prev < 0 ? first_tile : prev + tile_step;
       long long t = 0;
-      if (lane == 0) t = draw_tile(cursor, sched_full, sched_empty, sched_slots, abort_flag, args.status);
+      if (lane == 0) t = draw_tile(cursor, sched_full, sched_empty, sched_slots, abort_flag, args.status, args.wait_limit);
       return __shfl_sync(0xffffffffu, t, 0);
     };
     for (long long t = next_tile(-1); ok && t >= 0 && t < args.total_tiles; t = next_tile(t), ++local) {
@@ -576,7 +585,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
       m0 += static_cast<int>(cta_rank) * BM;  // this CTA's half of a pair tile
       const uint32_t acc = local & 1u;
       const uint32_t acc_phase = (local >> 1) & 1u;
-      if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag, args.status, STATUS_WAIT_EPI_TMEM_FULL)) {
+      uint8_t* w_row = nullptr;  // UPD: this lane's row of the block's weights (null beyond the last row)
+      if (UPD) {
+        const int wrow = m0 + quarter * 32 + lane;
+        if (wrow < args.M) {
+          const int esz = args.upd_f32 ? 4 : 2;
+          w_row = static_cast<uint8_t*>(args.upd_w[b]) + static_cast<long long>(wrow) * args.N * esz;
+          // pull this warp's pieces of W towards L2 while the accumulator is still being computed
+          for (int c = half; c < BN / 64; c += 2) {
+            const int col0 = n0 + c * 64;
+            if (col0 >= args.N) break;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(w_row + static_cast<long long>(col0) * esz));
+            if (args.upd_f32 && col0 + 32 < args.N)
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(w_row + static_cast<long long>(col0 + 32) * esz));
+          }
+        }
+      }
+      if (!mbar_wait(tmem_full_bar + 8 * acc, acc_phase, abort_flag, args.status, STATUS_WAIT_EPI_TMEM_FULL, args.wait_limit)) {
         ok = false;
         break;
       }
@@ -591,7 +616,69 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
       const int row = row0 + lane;
       const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c = half; c < BN / 64; c += 2) {
+      for (int c = half; UPD && c < BN / 64; c += 2) {
+        const int col0 = n0 + c * 64;
+        if (col0 >= args.N || row0 >= args.M) break;  // uniform across the warp
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {                 // 32 columns at a time keeps the live registers low
+          const int colh = col0 + 32 * h;
+          if (colh >= args.N) break;                  // uniform
+          uint32_t v[32];
+          if (args.upd_f32) {
+            float4 wv[8];
+            float4* wp = reinterpret_cast<float4*>(w_row + static_cast<long long>(colh) * 4);
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (w_row != nullptr && colh + 4 * u < args.N) wv[u] = __ldcs(wp + u);
+            tcgen05_ld_32x32b_x32(t_base + c * 64 + 32 * h, v);
+            tcgen05_wait_ld();
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              float o[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int e = 32 * h + 4 * u + i;   // column inside the 64-wide chunk
+                float x = scale * __uint_as_float(v[4 * u + i]);
+                if (e == row - col0) x += args.diag;
+                o[i] = __bfloat162float(__float2bfloat16_rn(x));
+              }
+              if (w_row != nullptr && colh + 4 * u < args.N) {
+                wv[u].x = fmaf(args.upd_alpha, o[0], wv[u].x);
+                wv[u].y = fmaf(args.upd_alpha, o[1], wv[u].y);
+                wv[u].z = fmaf(args.upd_alpha, o[2], wv[u].z);
+                wv[u].w = fmaf(args.upd_alpha, o[3], wv[u].w);
+                __stcs(wp + u, wv[u]);
+              }
+            }
+          } else {
+            uint4 wv[4];
+            uint4* wp = reinterpret_cast<uint4*>(w_row + static_cast<long long>(colh) * 2);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (w_row != nullptr && colh + 8 * u < args.N) wv[u] = __ldcs(wp + u);
+            tcgen05_ld_32x32b_x32(t_base + c * 64 + 32 * h, v);
+            tcgen05_wait_ld();
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&wv[u]);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int e = 32 * h + 8 * u + 2 * i;
+                float x0 = scale * __uint_as_float(v[8 * u + 2 * i]);
+                float x1 = scale * __uint_as_float(v[8 * u + 2 * i + 1]);
+                if (e == row - col0) x0 += args.diag;
+                if (e + 1 == row - col0) x1 += args.diag;
+                const float2 o = __bfloat1622float2(__floats2bfloat162_rn(x0, x1));
+                const float2 w = __bfloat1622float2(wh[i]);
+                wh[i] = __floats2bfloat162_rn(fmaf(args.upd_alpha, o.x, w.x), fmaf(args.upd_alpha, o.y, w.y));
+              }
+              if (w_row != nullptr && colh + 8 * u < args.N) __stcs(wp + u, wv[u]);
+            }
+          }
+        }
+      }
+#pragma unroll 1
+      for (int c = half; !UPD && c < BN / 64; c += 2) {
         const int col0 = n0 + c * 64;
         if (col0 >= args.N || row0 >= args.M) break;  // uniform across the warp
         uint32_t v[64];
@@ -632,7 +719,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
         if (PAIR) mbar_arrive_cluster(mapa(tmem_empty_bar + 8 * acc, 0)); else mbar_arrive(tmem_empty_bar + 8 * acc);
       }
     }
-    if (lane == 0) bulk_wait_all();
+    if (!UPD && lane == 0) bulk_wait_all();
   }
 
   // ------------------------------------------------------------- teardown
@@ -713,9 +800,9 @@ int operand_maps(CUtensorMap* k_map, CUtensorMap* mn_map, const void* base, int 
   return MMB_OK;
 }
 
-template <int BN, bool PAIR, bool DYN = false>
+template <int BN, bool PAIR, bool DYN = false, bool UPD = false>
 int launch(const CUtensorMap* maps, const GemmArgs& args, int grid, cudaStream_t st) {
-  auto kern = gemm_kernel<BN, PAIR, DYN>;
+  auto kern = gemm_kernel<BN, PAIR, DYN, UPD>;
   constexpr int smem = Cfg<BN, PAIR>::SMEM_BYTES;
   MMB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   cudaLaunchConfig_t cfg = {};
@@ -736,10 +823,6 @@ int launch(const CUtensorMap* maps, const GemmArgs& args, int grid, cudaStream_t
 }
 
 }  // namespace tc
-
-int gemm_trace_read(long long* host) {  // DEV TRACE
-  return MMB_OK;
-}
 
 // How many CTAs (single) or clusters (pair) of the 256-wide kernel the device can hold at once.
 int gemm_occupancy(int pair, int* out) {
@@ -780,11 +863,7 @@ int gemm_tcgen05(const GemmCall& g, int32_t* status, cudaStream_t st) {
   if (g.sym_out) MMB_REQUIRE(g.M == g.N, "symmetric output must be square");
   const int bn = g.N > 128 ? 256 : (g.N > 64 ? 128 : 64);
   // two CTAs per 256 x 256 tile when the problem has at least two tile rows of 128
-  static const bool pair_allowed = [] {
-    const char* e = getenv("MMB_GEMM_PAIR");
-    return e == nullptr || e[0] != '0';
-  }();
-  const bool pair = pair_allowed && bn == 256 && g.M > BM;
+  const bool pair = bn == 256 && g.M > BM;
   const int tile_m = pair ? 2 * BM : BM;
   CUtensorMap maps[5];
   int rc;
@@ -811,6 +890,12 @@ int gemm_tcgen05(const GemmCall& g, int32_t* status, cudaStream_t st) {
   args.inv_norm = g.inv_norm; args.sigma_pow = g.inv_norm != nullptr ? g.sigma_pow : 0;
   args.status = status;
   args.sched = nullptr;
+  args.upd_w = g.upd_w;
+  args.upd_alpha = g.upd_alpha;
+  args.upd_f32 = g.upd_f32;
+  args.wait_limit = WAIT_LIMIT_CYCLES;
+  const bool upd = g.upd_w != nullptr;
+  if (upd) MMB_REQUIRE(!g.sym_out, "the fused weight update applies to a full (non-symmetric) result");
   const int sms = sm_count();
   if (sms <= 0) return fail(MMB_ERR_CUDA, "tcgen05 GEMM: no CUDA device");
   if (args.total_tiles == 0) return MMB_OK;
@@ -819,14 +904,42 @@ int gemm_tcgen05(const GemmCall& g, int32_t* status, cudaStream_t st) {
     const int grid = 2 * static_cast<int>(args.total_tiles < pairs ? args.total_tiles : pairs);
     if (g.sched != nullptr && gemm_schedule_dynamic() && args.total_tiles < (1ll << 30)) {
       args.sched = g.sched;
-      return launch<256, true, true>(maps, args, grid, st);
+      return upd ? launch<256, true, true, true>(maps, args, grid, st) : launch<256, true, true>(maps, args, grid, st);
     }
-    return launch<256, true>(maps, args, grid, st);
+    return upd ? launch<256, true, false, true>(maps, args, grid, st) : launch<256, true>(maps, args, grid, st);
   }
   const int grid = static_cast<int>(args.total_tiles < sms ? args.total_tiles : sms);
-  if (bn == 256) return launch<256, false>(maps, args, grid, st);
-  if (bn == 128) return launch<128, false>(maps, args, grid, st);
-  return launch<64, false>(maps, args, grid, st);
+  if (bn == 256) return upd ? launch<256, false, false, true>(maps, args, grid, st) : launch<256, false>(maps, args, grid, st);
+  if (bn == 128) return upd ? launch<128, false, false, true>(maps, args, grid, st) : launch<128, false>(maps, args, grid, st);
+  return upd ? launch<64, false, false, true>(maps, args, grid, st) : launch<64, false>(maps, args, grid, st);
+}
+
+// ------------------------------------------------------------ wait probe
+// One warp waits, with the GEMM's own bounded wait and a caller-chosen limit, on a barrier that nothing
+// ever arrives at.  The wait must expire, store its code in the status word and let the kernel return: the
+// behaviour every role of the GEMM relies on when a hand-off never comes.
+__global__ void wait_probe_kernel(long long limit_cycles, int32_t* status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    tc::mbar_init(tc::smem_u32(&bar), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0)
+    tc::mbar_wait(tc::smem_u32(&bar), 0, &abort_flag, status, STATUS_WAIT_PROBE, limit_cycles);
+  __syncthreads();
+}
+
+int wait_probe(long long limit_cycles, int32_t* status, cudaStream_t st) {
+  MMB_REQUIRE(status != nullptr, "mmb_wait_probe: null status word");
+  MMB_REQUIRE(limit_cycles > 0 && limit_cycles <= 2000000000ll, "mmb_wait_probe: limit of %lld cycles is outside 1..2e9",
+              limit_cycles);
+  wait_probe_kernel<<<1, 32, 0, st>>>(limit_cycles, status);
+  MMB_CUDA_CHECK(cudaGetLastError());
+  count_launch();
+  return MMB_OK;
 }
 
 }  // namespace mmb

@@ -352,6 +352,10 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
             const float r = __frcp_rn(s_new);
 #pragma unroll
             for (int i = 0; i < ELEMS_PER_LANE; ++i) q[i] = quotient_markstein(m[i], s_new, r);
+          } else if (DIV == MMB_DIV_FULL && finite_normal(s_new)) {  // uniform over the group
+            const float r = rcp_approx(s_new);                        // div.full.f32(m, s) == m * rcp.approx(s)
+#pragma unroll
+            for (int i = 0; i < ELEMS_PER_LANE; ++i) q[i] = __fmul_rn(m[i], r);
           } else {
 #pragma unroll
             for (int i = 0; i < ELEMS_PER_LANE; ++i) q[i] = fdiv<DIV>(m[i], s_new);

@@ -166,6 +166,21 @@ __global__ void inv_norm_kernel(const float* __restrict__ sumsq, float* __restri
   if (i < n) inv[i] = __fdiv_rn(1.0f, __fadd_rn(__fsqrt_rn(sumsq[i]), 1e-7f));
 }
 
+// W[b] <- W[b] + alpha * O[b] for blocks reached through a pointer table: the update that follows
+// Newton-Schulz when it is not fused into the last GEMM's epilogue (cross-check back end).
+template <typename WT>
+__global__ void __launch_bounds__(256)
+update_blocks_kernel(void* const* __restrict__ w_ptrs, const __nv_bfloat16* __restrict__ ortho, long long block_elems,
+                     float alpha) {
+  WT* w = static_cast<WT*>(w_ptrs[blockIdx.y]);
+  const __nv_bfloat16* o = ortho + static_cast<long long>(blockIdx.y) * block_elems;
+  for (long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; i < block_elems;
+       i += static_cast<long long>(gridDim.x) * 256) {
+    const float x = fmaf(alpha, __bfloat162float(o[i]), static_cast<float>(w[i]));
+    w[i] = static_cast<WT>(x);
+  }
+}
+
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct NsLayout {
@@ -212,17 +227,24 @@ int mmb_gemm_bf16(const void* a_dev, const void* b_dev, void* d_dev, int batch, 
   return gemm_dispatch(backend, g, status_dev, static_cast<cudaStream_t>(stream));
 }
 
-int mmb_newton_schulz(const void* x_dev, void* out_dev, const float* block_sumsq_dev, int batch, int rows, int cols,
-                      void* workspace_dev, int64_t workspace_bytes, int backend, int32_t* status_dev, void* stream) {
-  using namespace mmb;
-  MMB_REQUIRE(x_dev && out_dev && workspace_dev, "mmb_newton_schulz: null pointer");
-  MMB_REQUIRE(batch > 0 && rows > 0 && cols > 0, "mmb_newton_schulz: bad shape (%d,%d,%d)", batch, rows, cols);
-  MMB_REQUIRE((reinterpret_cast<uintptr_t>(workspace_dev) & 1023u) == 0, "mmb_newton_schulz: workspace not 1 KiB aligned");
+}  // extern "C"
+
+namespace mmb {
+namespace {
+
+// Newton-Schulz on `batch` blocks.  With w_ptrs == nullptr the result goes to out_dev; otherwise out_dev is
+// not used and the result updates the blocks' weights, W[b] <- W[b] + alpha * NS(X)[b].
+int newton_schulz_impl(const char* who, const void* x_dev, void* out_dev, const float* block_sumsq_dev, int batch,
+                       int rows, int cols, void* workspace_dev, int64_t workspace_bytes, int backend,
+                       int32_t* status_dev, void* stream, void* const* w_ptrs, int w_f32, float alpha) {
+  MMB_REQUIRE(x_dev && (out_dev || w_ptrs) && workspace_dev, "%s: null pointer", who);
+  MMB_REQUIRE(batch > 0 && rows > 0 && cols > 0, "%s: bad shape (%d,%d,%d)", who, batch, rows, cols);
+  MMB_REQUIRE((reinterpret_cast<uintptr_t>(workspace_dev) & 1023u) == 0, "%s: workspace not 1 KiB aligned", who);
   const NsLayout l = ns_layout(batch, rows, cols);
-  MMB_REQUIRE(workspace_bytes >= static_cast<int64_t>(l.total), "mmb_newton_schulz: workspace %lld < %lld bytes",
+  MMB_REQUIRE(workspace_bytes >= static_cast<int64_t>(l.total), "%s: workspace %lld < %lld bytes", who,
               (long long)workspace_bytes, (long long)l.total);
   if (backend == MMB_NS_TCGEN05)
-    MMB_REQUIRE(rows % 8 == 0 && cols % 8 == 0, "mmb_newton_schulz: tensor-core path needs rows, cols multiples of 8");
+    MMB_REQUIRE(rows % 8 == 0 && cols % 8 == 0, "%s: tensor-core path needs rows, cols multiples of 8", who);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t* ws = static_cast<uint8_t*>(workspace_dev);
   __nv_bfloat16* gram = reinterpret_cast<__nv_bfloat16*>(ws + l.gram);
@@ -256,8 +278,10 @@ int mmb_newton_schulz(const void* x_dev, void* out_dev, const float* block_sumsq
   const int m = tall ? cols : rows;
   const int n = tall ? rows : cols;
   const __nv_bfloat16* cur = static_cast<const __nv_bfloat16*>(x_dev);
+  const bool fuse_update = w_ptrs != nullptr && backend == MMB_NS_TCGEN05;
   for (int it = 0; it < NS_ITERS; ++it) {
-    __nv_bfloat16* nxt = (it == NS_ITERS - 1) ? static_cast<__nv_bfloat16*>(out_dev) : ((it & 1) ? xb : xa);
+    const bool last = it == NS_ITERS - 1;
+    __nv_bfloat16* nxt = (last && w_ptrs == nullptr) ? static_cast<__nv_bfloat16*>(out_dev) : ((it & 1) ? xb : xa);
     const int first = it == 0;
     int rc;
     // Gram: wide X X^T (K-major operands, contraction n); tall Y^T Y (MN-major operands, contraction rows)
@@ -268,17 +292,58 @@ int mmb_newton_schulz(const void* x_dev, void* out_dev, const float* block_sumsq
     GemmCall poly_call{gram, gram, poly, batch, m, m, m, GEMM_SYM, GEMM_SYM, 1, c, kappa, nullptr, 0, sched};
     if ((rc = gemm_dispatch(backend, poly_call, status_dev, st)) != MMB_OK) return rc;
     // Apply: wide X' = Pp X (B = X stored [K][N]); tall Y' = Y Pp (A = Y, B = Pp by symmetry)
-    if (!tall) {
-      GemmCall ap{poly, cur, nxt, batch, m, n, m, GEMM_SYM, GEMM_MN, 0, 1.0f, 0.0f, inv, first ? 1 : 0, sched};
-      rc = gemm_dispatch(backend, ap, status_dev, st);
-    } else {
-      GemmCall ap{cur, poly, nxt, batch, n, m, m, GEMM_K, GEMM_SYM, 0, 1.0f, 0.0f, inv, first ? 1 : 0, sched};
-      rc = gemm_dispatch(backend, ap, status_dev, st);
+    GemmCall ap = !tall ? GemmCall{poly, cur, nxt, batch, m, n, m, GEMM_SYM, GEMM_MN, 0, 1.0f, 0.0f, inv, first ? 1 : 0, sched}
+                        : GemmCall{cur, poly, nxt, batch, n, m, m, GEMM_K, GEMM_SYM, 0, 1.0f, 0.0f, inv, first ? 1 : 0, sched};
+    if (last && fuse_update) {  // the result (rows x cols, stored orientation) never reaches memory
+      ap.upd_w = w_ptrs;
+      ap.upd_alpha = alpha;
+      ap.upd_f32 = w_f32;
     }
-    if (rc != MMB_OK) return rc;
+    if ((rc = gemm_dispatch(backend, ap, status_dev, st)) != MMB_OK) return rc;
     cur = nxt;
   }
+  if (w_ptrs != nullptr && !fuse_update) {
+    const long long blk = static_cast<long long>(rows) * cols;
+    long long gx = (blk + 255) / 256;
+    if (gx > 64) gx = 64;
+    for (int b0 = 0; b0 < batch; b0 += 65535) {
+      const int nb = (batch - b0) < 65535 ? (batch - b0) : 65535;
+      dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(nb));
+      if (w_f32)
+        update_blocks_kernel<float><<<grid, 256, 0, st>>>(w_ptrs + b0, cur + b0 * blk, blk, alpha);
+      else
+        update_blocks_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(w_ptrs + b0, cur + b0 * blk, blk, alpha);
+      MMB_CUDA_CHECK(cudaGetLastError());
+      count_launch();
+    }
+  }
   return MMB_OK;
+}
+
+}  // namespace
+}  // namespace mmb
+
+extern "C" {
+
+int mmb_newton_schulz(const void* x_dev, void* out_dev, const float* block_sumsq_dev, int batch, int rows, int cols,
+                      void* workspace_dev, int64_t workspace_bytes, int backend, int32_t* status_dev, void* stream) {
+  return mmb::newton_schulz_impl("mmb_newton_schulz", x_dev, out_dev, block_sumsq_dev, batch, rows, cols, workspace_dev,
+                                 workspace_bytes, backend, status_dev, stream, nullptr, 0, 0.0f);
+}
+
+int mmb_newton_schulz_update(const void* x_dev, const float* block_sumsq_dev, int batch, int rows, int cols,
+                             void* const* weight_ptrs_dev, int weight_dtype, float alpha, void* workspace_dev,
+                             int64_t workspace_bytes, int backend, int32_t* status_dev, void* stream) {
+  using namespace mmb;
+  MMB_REQUIRE(weight_ptrs_dev != nullptr, "mmb_newton_schulz_update: null weight pointer table");
+  MMB_REQUIRE(weight_dtype == MMB_BF16 || weight_dtype == MMB_F32, "mmb_newton_schulz_update: weight_dtype %d",
+              weight_dtype);
+  return newton_schulz_impl("mmb_newton_schulz_update", x_dev, nullptr, block_sumsq_dev, batch, rows, cols, workspace_dev,
+                            workspace_bytes, backend, status_dev, stream, weight_ptrs_dev, weight_dtype == MMB_F32, alpha);
+}
+
+int mmb_wait_probe(int64_t limit_cycles, int32_t* status_dev, void* stream) {
+  return mmb::wait_probe(limit_cycles, status_dev, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

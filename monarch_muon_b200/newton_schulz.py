@@ -17,10 +17,12 @@ from . import _lib
 _workspaces: dict = {}
 
 
-def _workspace(nbytes: int, device: torch.device) -> torch.Tensor:
-    """Grow-only per-device scratch (A, P and two X buffers); 1 KiB aligned by
-    the caching allocator's 512-byte granularity plus an explicit offset."""
-    key = device.index if device.index is not None else torch.cuda.current_device()
+def _buffer(tag: str, nbytes: int, device: torch.device) -> torch.Tensor:
+    """Grow-only scratch, one buffer per (device, stream, tag), 1 KiB aligned (the caching allocator's
+    512-byte granularity plus an explicit offset).  Work that shares a buffer is ordered by its stream;
+    another stream gets a buffer of its own."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (index, torch.cuda.current_stream(device).cuda_stream, tag)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes + 1024:
         _workspaces.pop(key, None)
@@ -28,6 +30,17 @@ def _workspace(nbytes: int, device: torch.device) -> torch.Tensor:
         _workspaces[key] = buf
     off = (-buf.data_ptr()) % 1024
     return buf[off:off + nbytes]
+
+
+def _workspace(nbytes: int, device: torch.device) -> torch.Tensor:
+    """Newton-Schulz workspace (A, P and two X buffers)."""
+    return _buffer("ns", nbytes, device)
+
+
+def scratch_bf16(tag: str, numel: int, device: torch.device) -> torch.Tensor:
+    """A bf16 scratch array of `numel` elements from the same pool (the Newton-Schulz input of one slice
+    when the optimizer state is not itself a bf16 array)."""
+    return _buffer(tag, 2 * numel, device).view(torch.bfloat16)
 
 
 def release_workspaces() -> None:
@@ -99,3 +112,26 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, *, a_mode: int = _lib.GEMM_K, b_
                                      int(sym_out), alpha, diag, _lib.ptr(inv_norm), sigma_pow, backend,
                                      _lib.status_word(a.device), _lib.stream_ptr()), "gemm_bf16")
     return d
+
+
+def newton_schulz_update(stack: torch.Tensor, weight_ptrs: torch.Tensor, weight_dtype: torch.dtype, alpha: float, *,
+                         block_sumsq: torch.Tensor | None = None, backend: int = _lib.NS_TCGEN05) -> None:
+    """W[b] <- W[b] + alpha * NS(stack)[b] in one call (mmb_newton_schulz_update): the counterpart of
+    _newton_schulz_batched followed by `param.data.add_(ortho, alpha=)` (monarch_muon.py:36-50, 160-165).
+    `weight_ptrs` is an int64 CUDA tensor with one device address per block: that block's rows x cols
+    weights, row-major, 16-byte aligned.  `stack` is only read."""
+    _lib.require_cuda(stack, weight_ptrs)
+    if stack.dim() != 3 or stack.dtype != torch.bfloat16 or not stack.is_contiguous():
+        raise ValueError("newton_schulz_update expects a contiguous bfloat16 (batch, rows, cols) stack")
+    batch, rows, cols = stack.shape
+    if weight_ptrs.dtype != torch.int64 or weight_ptrs.numel() != batch or not weight_ptrs.is_contiguous():
+        raise ValueError("weight_ptrs must be a contiguous int64 tensor with one address per block")
+    if batch == 0:
+        return
+    lib = _lib.load()
+    with torch.cuda.device(stack.device):
+        ws = _workspace(lib.mmb_ns_workspace_bytes(batch, rows, cols), stack.device)
+        _lib.check(lib.mmb_newton_schulz_update(stack.data_ptr(), _lib.ptr(block_sumsq), batch, rows, cols,
+                                                weight_ptrs.data_ptr(), _lib.dtype_code(weight_dtype), float(alpha),
+                                                ws.data_ptr(), ws.numel(), backend, _lib.status_word(stack.device),
+                                                _lib.stream_ptr()), "newton_schulz_update")

@@ -8,15 +8,26 @@ everything else), `group["lr"]` read at call time so LR schedulers work,
 parameters without a gradient skipped, state created lazily on the first
 step, standard `state_dict` / `load_state_dict` / step hooks.
 
-What differs is where the arithmetic runs.  A step is a handful of launches:
+What differs is where the arithmetic runs.  Muon tensors of one block shape are
+worked through in slices (runs of consecutive tensors); per slice:
 
-  1. one fused momentum kernel over every Muon tensor (heavy ball + optional
-     FP8 state codec + bf16 copy for Newton-Schulz + per-block sums of
-     squares);
-  2. per block shape, 15 tcgen05 GEMM launches (5 x Gram / Poly / Apply) on
-     the momentum arena of that shape - the reference's torch.cat is gone
-     because momentum lives in one arena per shape;
-  3. one update launch per shape, one AdamW launch per <=128 tensors.
+  1. one fused momentum kernel (heavy ball + optional FP8 state codec + bf16
+     copy for Newton-Schulz + per-block sums of squares);
+  2. per <= `ns_max_batch` blocks, 15 tcgen05 GEMM launches (5 x Gram / Poly /
+     Apply) on that bf16 stack - the reference's torch.cat is gone because the
+     blocks of a slice already lie back to back - the last of which applies
+     W <- W - lr*sqrt(rows/cols)*O in its epilogue, so the orthogonalised blocks
+     are never written to memory and no separate update kernel runs.
+
+AdamW is one launch per <= 128 tensors.
+
+Memory.  The persistent Muon state is what the format says and nothing more:
+E4M3 codes (1 byte per element) plus per-group side arrays, or the
+parameter-dtype buffer like the reference.  The bf16 stack that feeds
+Newton-Schulz is scratch for one slice (at most `momentum_slice_elems`
+elements, 1.48 GB by default) drawn from a pool shared by all optimizers of a
+device and stream; with bf16 parameters in the reference's own format the
+state is itself that stack and no scratch is needed.
 
 There is no CPU path: tensors must live on a CUDA device.
 """
@@ -27,7 +38,7 @@ from collections import OrderedDict
 import torch
 
 from . import _lib, fp8_state
-from .newton_schulz import newton_schulz_batched
+from .newton_schulz import newton_schulz_batched, newton_schulz_update, scratch_bf16
 
 _STATE_FORMATS = ("param", "fp8_absmax", "fp8_expand")
 
@@ -38,10 +49,9 @@ class _ShapeGroup:
     def __init__(self, dtype, rows, cols):
         self.dtype, self.rows, self.cols = dtype, rows, cols
         self.params: list = []
-        self.block_start: list[int] = []      # first block of each tensor inside the group arena
+        self.block_start: list[int] = []      # first block of each tensor inside the group's state arrays
         self.nblocks = 0
-        self.m_arena = None                   # bf16 [nblocks, rows, cols]: Newton-Schulz input
-        self.ortho = None                     # bf16 [nblocks, rows, cols]: Newton-Schulz output
+        self.bf16_state = None                # bf16 [nblocks, rows, cols] when the state is itself the NS input
         self.first_block_global = 0           # index of the group's first block in block_sumsq
 
 
@@ -67,6 +77,13 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
     ns_backend : "tcgen05" (tensor cores) or "simt" (cross-check kernel).
     ns_max_batch : slice Newton-Schulz into at most this many blocks per call
         to bound its workspace.
+    fuse_update : (on by default) apply the weight update in the epilogue of the last Newton-Schulz GEMM.
+        Off: Newton-Schulz writes the orthogonalised slice to a second scratch stack and a separate kernel
+        updates the weights (same bits either way; kept for measurement).
+    momentum_slice_elems : elements of one momentum launch, i.e. of the bf16
+        scratch stack between the momentum kernel and Newton-Schulz (default
+        704 Mi elements = 1.48 GB; never fewer than `ns_max_batch` blocks).  Gradients fed from host memory are always
+        pipelined in slices of `ns_max_batch` blocks.
     overlap : (off by default) run the bandwidth-bound kernels (momentum of the next slice, weight
         update of the previous one, AdamW) on a second stream beside the
         tensor-bound Newton-Schulz of the current slice.  Same kernels on the
@@ -79,7 +96,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                  adamw_betas: tuple[float, float] = (0.9, 0.95), adamw_weight_decay: float = 0.1,
                  adamw_eps: float = 1e-8, state_format: str = "param", fp8_div: str = "full",
                  ns_backend: str = "tcgen05", ns_max_batch: int | None = 256, expand_min: int = 16,
-                 overlap: bool = False):
+                 overlap: bool = False, momentum_slice_elems: int = 704 << 20, fuse_update: bool = True):
         if state_format not in _STATE_FORMATS:
             raise ValueError(f"state_format must be one of {_STATE_FORMATS}")
         muon_params = list(muon_params)
@@ -95,6 +112,8 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         self.fp8_div = _lib.DIV_NAMES[fp8_div]
         self.ns_backend = {"tcgen05": _lib.NS_TCGEN05, "simt": _lib.NS_SIMT}[ns_backend]
         self.ns_max_batch = ns_max_batch
+        self.momentum_slice_elems = int(momentum_slice_elems)
+        self.fuse_update = bool(fuse_update)
         self.expand_min = expand_min
         self.grad_scale = 1.0            # multiplies Muon gradients inside the momentum kernel
         self._plans: dict = {}           # id(group) -> plan
@@ -190,9 +209,28 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                     self._marks.append((phase, e0, ev))
                 self._open[key] = ev                     # consecutive phases share a boundary
 
+    def check_device_status(self) -> None:
+        """Raise if a kernel of this library reported an expired bounded wait since the last check (the
+        Newton-Schulz GEMMs give up a hand-off that never comes, store a code and return; their output is
+        then incomplete).  Synchronises the current stream of every device that holds Muon parameters.
+        Called by state_dict() and phase_times_ms(), i.e. where the caller synchronises anyway."""
+        for plan in self._plans.values():
+            if plan is None:
+                continue
+            code = _lib.read_status(plan["device"])
+            if code != 0:
+                what = _lib.STATUS_NAMES.get(code, "unknown code")
+                raise RuntimeError(f"monarch_muon_b200: a kernel gave up a bounded wait (status {code:#x}: {what}); "
+                                   "the weights written by that step are incomplete")
+
+    def state_dict(self):
+        self.check_device_status()
+        return super().state_dict()
+
     def phase_times_ms(self) -> dict:
         """Milliseconds per phase accumulated since phase timing was enabled
         (call after a synchronise); clears the recorded events."""
+        self.check_device_status()
         out: dict = {}
         for name, e0, e1 in (self._marks or []):
             out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
@@ -268,20 +306,17 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
             sg.nblocks += nb
         plan = {"device": dev, "shapes": shapes, "params": list(params), "entry": {}}
         total_blocks = 0
-        mplan = fp8_state.MomentumPlan(dev)
         for sg in shapes.values():
             sg.first_block_global = total_blocks
             total_blocks += sg.nblocks
-            sg.m_arena = torch.zeros(sg.nblocks, sg.rows, sg.cols, dtype=torch.bfloat16, device=dev)
-            blk = sg.rows * sg.cols
-            in_place_state = self.state_format == "param" and sg.dtype == torch.bfloat16
-            # Newton-Schulz may overwrite its input unless that input is the state itself
-            sg.ortho = torch.empty_like(sg.m_arena) if in_place_state else sg.m_arena
             sg.fp32_state = None
             sg.codes = sg.scale = sg.expand = sg.sqrt_mm = None
-            if self.state_format == "param" and sg.dtype == torch.float32:
+            if self.state_format == "param" and sg.dtype == torch.bfloat16:
+                # the reference's own format with bf16 parameters: the state is the Newton-Schulz input
+                sg.bf16_state = torch.zeros(sg.nblocks, sg.rows, sg.cols, dtype=torch.bfloat16, device=dev)
+            elif self.state_format == "param":
                 sg.fp32_state = torch.zeros(sg.nblocks, sg.rows, sg.cols, dtype=torch.float32, device=dev)
-            if self._fp8():
+            else:
                 sg.codes = torch.zeros(sg.nblocks, sg.rows, sg.cols, dtype=torch.uint8, device=dev)
                 ngroups = sum(fp8_state.groups_of(p.numel()) for p in sg.params)
                 sg.scale = torch.zeros(ngroups, dtype=torch.float32, device=dev)
@@ -291,7 +326,6 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
             g_at = 0
             for p, b0 in zip(sg.params, sg.block_start):
                 nb = self._blocks_of(p)[0]
-                m_view = sg.m_arena[b0:b0 + nb].view(p.shape)
                 ng = fp8_state.groups_of(p.numel())
                 views = {}
                 if self._fp8():
@@ -305,17 +339,10 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                     state_t = sg.fp32_state[b0:b0 + nb].view(p.shape)
                     views["momentum_buffer"] = state_t
                 else:
-                    state_t = m_view
-                    views["momentum_buffer"] = m_view
-                idx = len(mplan.entries)
-                mplan.add(state=state_t, m_bf16=m_view, numel=p.numel(), block_elems=blk,
-                          scale=views.get("scale_momentum_buffer"), expand=views.get("expand_momentum_buffer"),
-                          sqrt_minmax=views.get("sqrt_minmax_momentum_buffer"))
-                # block sums are indexed globally over all shape groups
-                mplan.entries[idx]["first_block"] = sg.first_block_global + b0
-                plan["entry"][id(p)] = (idx, sg, b0, views)
+                    state_t = sg.bf16_state[b0:b0 + nb].view(p.shape)
+                    views["momentum_buffer"] = state_t
+                plan["entry"][id(p)] = (state_t, sg, b0, views)
                 g_at += ng
-        plan["momentum"] = mplan
         plan["block_sumsq"] = torch.zeros(total_blocks, dtype=torch.float32, device=dev)
         plan["scratch"] = None
         plan["slices"] = {}
@@ -343,18 +370,21 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         return _lib.STATE_BF16 if sg.dtype == torch.bfloat16 else _lib.STATE_F32
 
     # ------------------------------------------------------------ Muon: step
-    def _slices_for(self, plan, live):
-        """Cut the live tensors into slices: runs of consecutive tensors of one block shape holding at
-        most `ns_max_batch` blocks.  A slice is the unit of work (momentum -> Newton-Schulz -> update) and
-        of host-to-device pipelining.  Cached per set of live tensors."""
-        key = tuple(id(p) for p in live)
+    def _slices_for(self, plan, live, host_fed: bool):
+        """Cut the live tensors into slices: runs of consecutive tensors of one block shape.  A slice is
+        the unit of one momentum launch (and of host-to-device pipelining); its blocks go through
+        Newton-Schulz in sub-slices of at most `ns_max_batch` blocks.  Cached per set of live tensors."""
+        key = (tuple(id(p) for p in live), host_fed)
         cached = plan["slices"].get(key)
         if cached is not None:
             return cached
-        live_ids = set(key)
-        cap = self.ns_max_batch or (1 << 30)
+        live_ids = set(key[0])
+        ns_cap = self.ns_max_batch or (1 << 30)
         slices = []
         for sg in plan["shapes"].values():
+            blk = sg.rows * sg.cols
+            # host-fed gradients: small slices, so that the first copy is short and the last compute is too
+            cap = ns_cap if host_fed else max(ns_cap, self.momentum_slice_elems // blk)
             cur = None
             for p, b0 in zip(sg.params, sg.block_start):
                 if id(p) not in live_ids:
@@ -362,7 +392,8 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                     continue
                 nb = self._blocks_of(p)[0]
                 if cur is None or cur["b1"] - cur["b0"] + nb > cap:
-                    cur = {"sg": sg, "items": [], "b0": b0, "b1": b0, "tables": {}, "upd": None, "event": None}
+                    cur = {"sg": sg, "items": [], "b0": b0, "b1": b0, "tables": {}, "event": None, "sub": None,
+                           "index": len(slices)}
                     slices.append(cur)
                 cur["items"].append((p, b0))
                 cur["b1"] = b0 + nb
@@ -379,7 +410,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         plan = self._plan_for(group)
         dev = plan["device"]
         with torch.cuda.device(dev):
-            slices = self._slices_for(plan, live)
+            slices = self._slices_for(plan, live, host is not None)
             if overlapping and host is None:
                 self._muon_slices_overlapped(group, lr, plan, slices)
                 return
@@ -389,19 +420,18 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
             for sl in slices:
                 if sl["event"] is not None:
                     torch.cuda.current_stream().wait_event(sl["event"])
-                self._slice_momentum(group, plan, sl)
+                stack = self._slice_momentum(group, plan, sl, "m0")
                 self._mark("momentum")
-                self._slice_newton_schulz(plan, sl)
+                self._slice_newton_schulz_update(plan, sl, stack, lr)
                 self._mark("newton_schulz")
-                self._slice_update(lr, sl)
-                self._mark("update")
 
     def _muon_slices_overlapped(self, group, lr: float, plan, slices) -> None:
-        """Two streams: Newton-Schulz of slice k on the caller's stream; momentum of slice k+1, the
-        update of slice k-1 and (once) the AdamW groups on a side stream.  Newton-Schulz is tensor
-        bound and the others are bandwidth bound, so they can share the chip; the GEMMs draw their
-        tiles dynamically meanwhile.  On a B200 at its power cap the gain is small (the two kinds of
-        work share one power budget), which is why this is not the default."""
+        """Two streams: Newton-Schulz (with its fused update) of slice k on the caller's stream; momentum
+        of slice k+1 and (once) the AdamW groups on a side stream.  Newton-Schulz is tensor bound and the
+        others are bandwidth bound, so they can share the chip; the GEMMs draw their tiles dynamically
+        meanwhile.  On a B200 at its power cap the gain is small (the two kinds of work share one power
+        budget), which is why this is not the default.  The bf16 stacks of consecutive slices alternate
+        between two scratch buffers."""
         dev = plan["device"]
         main = torch.cuda.current_stream()
         side = self._side_streams.get(dev)
@@ -412,49 +442,60 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
             n = len(slices)
             mom_done = [torch.cuda.Event() for _ in range(n)]
             ns_done = [torch.cuda.Event() for _ in range(n)]
+            stacks = [None] * n
+            # the scratch pool is keyed by stream: draw both buffers on the caller's stream
+            tags = ("m0", "m1")
+            for k, sl in enumerate(slices):
+                stacks[k] = self._slice_stack(plan, sl, tags[k & 1])
             with torch.cuda.stream(side):
                 self._mark("begin")
-                self._slice_momentum(group, plan, slices[0])
+                self._slice_momentum(group, plan, slices[0], tags[0], stack=stacks[0])
                 self._mark("momentum")
                 mom_done[0].record(side)
             for k, sl in enumerate(slices):
                 with torch.cuda.stream(side):
                     if k + 1 < n:
+                        if k >= 1:
+                            side.wait_event(ns_done[k - 1])    # the buffer of slice k+1 was slice k-1's
                         self._mark("begin")
-                        self._slice_momentum(group, plan, slices[k + 1])
+                        self._slice_momentum(group, plan, slices[k + 1], tags[(k + 1) & 1], stack=stacks[k + 1])
                         self._mark("momentum")
                         mom_done[k + 1].record(side)
                     if k == 0:
                         deferred, self._deferred = self._deferred, []
                         for g in deferred:
                             self._adamw_step(g, g["lr"])
-                    if k >= 1:
-                        side.wait_event(ns_done[k - 1])
-                        self._mark("begin")
-                        self._slice_update(lr, slices[k - 1])
-                        self._mark("update")
                 main.wait_event(mom_done[k])
                 self._mark("begin")
-                self._slice_newton_schulz(plan, sl)
+                self._slice_newton_schulz_update(plan, sl, stacks[k], lr)
                 self._mark("newton_schulz")
                 ns_done[k].record(main)
-            with torch.cuda.stream(side):
-                side.wait_event(ns_done[n - 1])
-                self._mark("begin")
-                self._slice_update(lr, slices[n - 1])
-                self._mark("update")
             main.wait_stream(side)
 
-    def _slice_momentum(self, group, plan, sl) -> None:
-        """Momentum (+codec, +bf16 copy, +block norms) of one slice; tables are cached, only gradient
-        pointers change.  State is registered lazily, like _get_momentum_buffer (monarch_muon.py:133-137)."""
+    def _slice_stack(self, plan, sl, tag: str):
+        """The bf16 (blocks, rows, cols) stack Newton-Schulz reads for this slice: the state itself when
+        that is a bf16 array, else scratch that the momentum kernel fills."""
         sg = sl["sg"]
-        mplan = plan["momentum"]
+        if sg.bf16_state is not None:
+            return sg.bf16_state[sl["b0"]:sl["b1"]]
+        nb = sl["b1"] - sl["b0"]
+        flat = scratch_bf16(tag, nb * sg.rows * sg.cols, plan["device"])
+        return flat.view(nb, sg.rows, sg.cols)
+
+    def _slice_momentum(self, group, plan, sl, tag: str, stack=None):
+        """Momentum (+codec, +bf16 copy, +block norms) of one slice; tables are cached, only gradient
+        and scratch pointers change.  State is registered lazily, like _get_momentum_buffer
+        (monarch_muon.py:133-137).  Returns the slice's bf16 stack."""
+        sg = sl["sg"]
         dev = plan["device"]
+        if stack is None:
+            stack = self._slice_stack(plan, sl, tag)
+        blk = sg.rows * sg.cols
         buckets: "OrderedDict[tuple, list]" = OrderedDict()
-        for p, _ in sl["items"]:
+        keep = []
+        for p, pb0 in sl["items"]:
             st = self.state[p]
-            idx, _, _, views = plan["entry"][id(p)]
+            state_t, _, _, views = plan["entry"][id(p)]
             if "momentum_buffer" not in st:
                 st.update(views)
             g = p.grad
@@ -462,47 +503,91 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                 raise ValueError("gradient shape differs from its parameter")
             if not g.is_contiguous():
                 g = g.contiguous()
-            buckets.setdefault(g.dtype, []).append((idx, g))
+                keep.append(g)
+            buckets.setdefault(g.dtype, []).append((p, pb0, state_t, views, g))
         scode = self._state_code(sg)
         for gdtype, items in buckets.items():
             cached = sl["tables"].get(gdtype)
             if cached is None or cached[2] != len(items):
-                segs = mplan.table([g for _, g in items], [i for i, _ in items])
-                cached = sl["tables"][gdtype] = (segs, fp8_state.scratch_floats(segs, len(items)), len(items))
-            else:
-                segs = cached[0]
-                for k, (_, g) in enumerate(items):
-                    segs[k].grad = g.data_ptr()
-            if plan["scratch"] is None or plan["scratch"].numel() < cached[1]:
-                plan["scratch"] = torch.empty(cached[1], dtype=torch.float32, device=dev)
+                segs = (_lib.MomentumSeg * len(items))()
+                for k, (p, pb0, state_t, views, g) in enumerate(items):
+                    sgm = segs[k]
+                    sgm.state = state_t.data_ptr()
+                    sgm.scale = _lib.ptr(views.get("scale_momentum_buffer"))
+                    sgm.expand = _lib.ptr(views.get("expand_momentum_buffer"))
+                    sgm.sqrt_minmax = _lib.ptr(views.get("sqrt_minmax_momentum_buffer"))
+                    sgm.numel = p.numel()
+                    sgm.block_elems = blk
+                    sgm.first_block = sg.first_block_global + pb0
+                cached = sl["tables"][gdtype] = (segs, None, len(items))
+            segs = cached[0]
+            for k, (p, pb0, state_t, views, g) in enumerate(items):
+                segs[k].grad = g.data_ptr()
+                segs[k].m_bf16 = stack[pb0 - sl["b0"]:].data_ptr()       # scratch may move between steps
+            need = cached[1]
+            if need is None:
+                need = fp8_state.scratch_floats(segs, len(items))
+                sl["tables"][gdtype] = (segs, need, len(items))
+            if plan["scratch"] is None or plan["scratch"].numel() < need:
+                plan["scratch"] = torch.empty(need, dtype=torch.float32, device=dev)
             fp8_state.momentum_step(segs, len(items), grad_dtype=gdtype, state_format=scode,
                                     beta=group["momentum"], grad_scale=self.grad_scale,
                                     div_mode=self.fp8_div, expand_min=self.expand_min,
                                     block_sumsq=plan["block_sumsq"], scratch=plan["scratch"])
+        return stack
 
-    def _slice_newton_schulz(self, plan, sl) -> None:
+    def _slice_subslices(self, sl):
+        """Newton-Schulz sub-slices of a slice: (first block, last block) inside the slice and the device
+        table of weight addresses, one per block.  The table is rebuilt when a parameter's storage moved."""
         sg = sl["sg"]
-        b0, b1 = sl["b0"], sl["b1"]
-        ss = plan["block_sumsq"][sg.first_block_global + b0: sg.first_block_global + b1]
-        newton_schulz_batched(sg.m_arena[b0:b1], out=sg.ortho[b0:b1], block_sumsq=ss,
-                              backend=self.ns_backend, max_batch=None)
+        bases = tuple(p.data.data_ptr() for p, _ in sl["items"])
+        sub = sl["sub"]
+        if sub is not None and sub["bases"] == bases:
+            return sub["parts"]
+        esz = 2 if sg.dtype == torch.bfloat16 else 4
+        blk_bytes = sg.rows * sg.cols * esz
+        ptrs = []
+        for (p, _), base in zip(sl["items"], bases):
+            if not p.data.is_contiguous():
+                raise ValueError("Muon parameters must be contiguous")
+            if base % 16 or blk_bytes % 16:
+                raise ValueError("Muon parameters must be 16-byte aligned")
+            ptrs += [base + k * blk_bytes for k in range(self._blocks_of(p)[0])]
+        table = torch.tensor(ptrs, dtype=torch.int64).to(sg.params[0].device, non_blocking=False)
+        cap = self.ns_max_batch or len(ptrs)
+        parts = [(a, min(a + cap, len(ptrs)), table[a:min(a + cap, len(ptrs))]) for a in range(0, len(ptrs), cap)]
+        sl["sub"] = {"bases": bases, "parts": parts}
+        return parts
 
-    def _slice_update(self, lr: float, sl) -> None:
-        """W <- W - lr*sqrt(rows/cols)*O for the tensors of one slice."""
+    def _slice_newton_schulz_update(self, plan, sl, stack, lr: float) -> None:
+        """W <- W - lr*sqrt(rows/cols)*NS(momentum) for the tensors of one slice, the update fused into
+        the last GEMM's epilogue (monarch_muon.py:157-165)."""
         sg = sl["sg"]
         alpha = -lr * (sg.rows / sg.cols) ** 0.5
-        segs = sl["upd"]
-        if segs is None:
-            segs = sl["upd"] = (_lib.UpdateSeg * len(sl["items"]))()
-            for k, (p, pb0) in enumerate(sl["items"]):
-                segs[k].ortho = sg.ortho[pb0:].data_ptr()
-                segs[k].numel = p.numel()
-        for k, (p, _) in enumerate(sl["items"]):
+        first = sg.first_block_global + sl["b0"]
+        if self.fuse_update:
+            for a, b, table in self._slice_subslices(sl):
+                newton_schulz_update(stack[a:b], table, sg.dtype, alpha,
+                                     block_sumsq=plan["block_sumsq"][first + a:first + b], backend=self.ns_backend)
+            return
+        nb = sl["b1"] - sl["b0"]
+        ortho = scratch_bf16("ortho", nb * sg.rows * sg.cols, plan["device"]).view(nb, sg.rows, sg.cols)
+        cap = self.ns_max_batch or nb
+        for a in range(0, nb, cap):
+            b = min(a + cap, nb)
+            newton_schulz_batched(stack[a:b], out=ortho[a:b], block_sumsq=plan["block_sumsq"][first + a:first + b],
+                                  backend=self.ns_backend)
+        self._mark("newton_schulz")
+        segs = (_lib.UpdateSeg * len(sl["items"]))()
+        for k, (p, pb0) in enumerate(sl["items"]):
             if not p.data.is_contiguous():
                 raise ValueError("Muon parameters must be contiguous")
             segs[k].weight = p.data.data_ptr()
+            segs[k].ortho = ortho[pb0 - sl["b0"]:].data_ptr()
+            segs[k].numel = p.numel()
         _lib.check(_lib.load().mmb_muon_update(segs, len(sl["items"]), _lib.dtype_code(sg.dtype), alpha,
                                                _lib.stream_ptr()), "muon_update")
+        self._mark("update")
 
     # ------------------------------------------------- gradients from the host
     def _copy_stream(self, dev):
@@ -624,6 +709,14 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
         for pid, mine in managed.items():
             p = by_id[pid]
             _, _, _, views = plan["entry"][id(p)]
+            buf = mine.get("momentum_buffer")
+            if self._fp8() and buf is not None and buf.dtype != torch.float8_e4m3fn:
+                # a checkpoint written with plain (bf16/fp32) momentum, loaded into FP8 state: quantise it
+                tmp = {}
+                fp8_state.quantize_(tmp, "momentum_buffer", buf.to(p.device, torch.float32), True, torch.float8_e4m3fn,
+                                    self.expand_min, codec="expand" if self.state_format == "fp8_expand" else "absmax",
+                                    div_mode=self.fp8_div)
+                mine = tmp
             for k, v in mine.items():
                 if k not in views:
                     raise ValueError(f"state '{k}' does not fit state_format={self.state_format}")

@@ -22,28 +22,40 @@ def test_full_model_step_properties():
     assert {tuple(p.shape[1:]) for p in probe} == {(1024, 1024), (2752, 1024), (1024, 2752)}
     before = [p.data.clone() for p in probe]
     lr = 0.02
-    opt = MonarchMuonOptimizer(muon, adamw, lr=lr, state_format="fp8_absmax")
+    opt = MonarchMuonOptimizer(muon, adamw, lr=lr, state_format="fp8_absmax", fp8_div="ieee")   # the CPU oracle divides IEEE
+    torch.cuda.synchronize()
+    held_before = torch.cuda.memory_allocated(dev)
     opt.step()
     torch.cuda.synchronize()
     assert _lib.read_status(dev) == 0
+    # Memory.  Persistent optimizer state of the Muon tensors is one byte per element plus one fp32 scale per
+    # 128 (the reference's bf16 momentum is two bytes per element); everything else the step allocates -
+    # the bf16 stack of one slice, the Newton-Schulz workspace, the AdamW moments - stays under 7 GB.
+    n_muon = sum(p.numel() for p in muon)
+    muon_state = sum(v.numel() * v.element_size() for p in muon for v in opt.state[p].values() if torch.is_tensor(v))
+    assert muon_state == n_muon + 4 * (n_muon // 128)
+    adamw_state = sum(v.numel() * v.element_size() for p in adamw for v in opt.state[p].values() if torch.is_tensor(v))
+    scratch = torch.cuda.memory_allocated(dev) - held_before - muon_state - adamw_state
+    assert scratch < 5.6e9, scratch               # 1.5 GB stack + 3.9 GB workspace (256 tall blocks) + block sums
+    # Probe blocks against the CPU oracle: first block of one tensor per shape.  First step from zero state:
+    # m = g exactly, so the oracle needs only the gradient.
+    from oracle import fp8_oracle, muon_oracle
     for p, w0 in zip(probe, before):
-        nb, r, c = p.shape
-        delta = (p.data.float() - w0.float()) / (-lr * (r / c) ** 0.5)      # = Newton-Schulz output (+ bf16 weight rounding)
-        assert torch.isfinite(delta).all()
-        # the quintic maps every singular value of a full-rank block into about [0.68, 1.13]
-        # (bf16 storage of the weights adds some noise), so ||O||_F^2 / min(r, c) is about 1
-        energy = delta.pow(2).sum(dim=(1, 2)) / min(r, c)
-        assert float(energy.min()) > 0.45 and float(energy.max()) < 1.4, energy
-        # and the output is near-orthogonal: O O^T (or O^T O) close to a multiple of the identity
-        o = delta[0] if r <= c else delta[0].t()
-        gram = o @ o.t()
-        off = gram - torch.diag(torch.diag(gram))
-        assert float(off.norm() / gram.norm()) < 0.35
-        # FP8 state decodes to the gradient (first step: m = g) within E4M3's relative step of 2^-4
+        g0 = p.grad[0].cpu()
+        n = g0.numel()
+        codes, scales, _, m16 = fp8_oracle.absmax_momentum_step(torch.zeros(n, dtype=torch.uint8),
+                                                                torch.zeros(n // 128), g0.reshape(-1), 0.95)
         st = opt.state[p]
-        m = fp8_state.dequantize(st, "momentum_buffer", True, codec="absmax")
-        g = p.grad.float()
-        assert float((m - g).norm() / g.norm()) < 0.04
+        assert torch.equal(st["momentum_buffer"][0].view(torch.uint8).cpu().reshape(-1), codes)
+        o = muon_oracle.newton_schulz(m16.view(1, *g0.shape))[0]
+        base = w0[0].float().cpu()
+        want = (base - lr * (g0.shape[0] / g0.shape[1]) ** 0.5 * o.float()).bfloat16().float()    # stored as bf16, like ours
+        got = p.data[0].float().cpu()
+        # one step's increment, both sides rounded to bf16 weights: Newton-Schulz differences of 1-2 % flip the
+        # rounding of a few percent of the elements by one bf16 step of |W|
+        rel_step = float(((got - base) - (want - base)).norm() / (want - base).norm())
+        assert rel_step < 1.2e-1, rel_step
+        assert float((got - want).norm() / want.norm()) < 1e-2
     # a second step from the same gradients moves every probed block again by about the same amount
     mid = [p.data.clone() for p in probe]
     opt.step()

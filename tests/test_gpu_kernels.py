@@ -114,8 +114,10 @@ def test_gemm_symmetric_operands(mm, m, n, backend):
 
 
 # ------------------------------------------------------------------ Newton-Schulz
-NS_SHAPES = [(3, 128, 128), (2, 344, 128), (2, 128, 344), (2, 256, 512), (2, 1024, 1024), (1, 2752, 1024),
-             (1, 1024, 2752)]
+NS_SHAPES = [(3, 128, 128), (2, 344, 128), (2, 128, 344), (2, 256, 256), (2, 256, 512), (2, 1024, 1024), (1, 2752, 1024),
+             (1, 1024, 2752),
+             # the 2-block variant of the model: m = 2048 runs 8 x 8 pair tiles, 36 of 64 of them for symmetric products
+             (1, 2048, 2048), (1, 5504, 2048), (1, 2048, 5504)]
 
 # Tolerances, relative Frobenius norm per stack.  The reference's own bf16 path
 # differs from its fp32 path by e_ref (about 2.4e-2 on N(0,1) blocks, more on
@@ -151,6 +153,71 @@ def test_newton_schulz_against_oracle(mm, shape, backend):
     # scale invariance of the normalised iteration: NS(7x) == NS(x) up to bf16 noise
     got7 = mm["ns"].newton_schulz_batched((x * 7).cuda(), backend=be)
     assert relf(got7, got) < 3e-2
+
+
+@pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("backend", ["tcgen05", "simt"])
+@pytest.mark.parametrize("shape", [(3, 128, 128), (2, 344, 128), (2, 128, 344), (5, 256, 512), (2, 64, 64),
+                                   (3, 1024, 1024), (2, 2752, 1024), (2, 1024, 2752)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_newton_schulz_with_fused_update_equals_two_kernels(mm, shape, backend, wdtype):
+    """mmb_newton_schulz_update (the update applied in the epilogue of the last GEMM) must leave exactly
+    the weights that mmb_newton_schulz followed by mmb_muon_update leaves: same bf16 rounding of the
+    orthogonalised block, same fused multiply-add, same rounding to the weights' type - for bf16 and fp32
+    weights, wide, tall, ragged and small blocks, blocks scattered over separate tensors, and with the
+    dynamic tile schedule."""
+    L = mm["lib"]
+    if backend == "simt" and shape[1] * shape[2] > 256 * 512:
+        pytest.skip("cross-check kernel only on small shapes")
+    be = L.NS_TCGEN05 if backend == "tcgen05" else L.NS_SIMT
+    batch, rows, cols = shape
+    g = torch.Generator().manual_seed(sum(shape) + 1)
+    x = torch.randn(shape, generator=g).bfloat16().cuda()
+    # blocks of two "parameters" that are not adjacent in memory
+    n0 = batch // 2 + 1
+    wa = (0.02 * torch.randn(n0, rows, cols, generator=g)).to(wdtype).cuda()
+    wb = (0.02 * torch.randn(batch - n0, rows, cols, generator=g)).to(wdtype).cuda()
+    alpha = -0.02 * (rows / cols) ** 0.5
+    want = torch.cat([wa, wb]).clone()
+    ortho = mm["ns"].newton_schulz_batched(x, backend=be)
+    seg = (L.UpdateSeg * 1)()
+    seg[0].weight, seg[0].ortho, seg[0].numel = want.data_ptr(), ortho.data_ptr(), want.numel()
+    L.check(L.load().mmb_muon_update(seg, 1, L.dtype_code(wdtype), alpha, L.stream_ptr()))
+    esz = wa.element_size()
+    ptrs = [wa.data_ptr() + k * rows * cols * esz for k in range(n0)] + \
+           [wb.data_ptr() + k * rows * cols * esz for k in range(batch - n0)]
+    table = torch.tensor(ptrs, dtype=torch.int64).cuda()
+    x_before = x.clone()
+    for dynamic in ((False, True) if backend == "tcgen05" else (False,)):
+        a2, b2 = wa.clone(), wb.clone()
+        ptrs2 = [a2.data_ptr() + k * rows * cols * esz for k in range(n0)] + \
+                [b2.data_ptr() + k * rows * cols * esz for k in range(batch - n0)]
+        table2 = torch.tensor(ptrs2, dtype=torch.int64).cuda()
+        with L.launch_options(dynamic_schedule=dynamic):
+            mm["ns"].newton_schulz_update(x, table2, wdtype, alpha, backend=be)
+        assert L.read_status(x.device) == 0
+        got = torch.cat([a2, b2])
+        assert torch.equal(got, want), (dynamic, float((got.float() - want.float()).abs().max()))
+    assert torch.equal(x, x_before)                      # the input stack is only read
+    del table
+
+
+def test_bounded_wait_expires_and_reports(mm):
+    """A wait that nothing answers: one warp runs the GEMM's own bounded wait, with a limit of about a
+    millisecond, on a barrier no one arrives at.  The kernel must return, the status word must hold the
+    probe's code, and the device must go on working (a normal GEMM afterwards, status 0)."""
+    L = mm["lib"]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    assert L.read_status(dev) == 0
+    L.check(L.load().mmb_wait_probe(2_000_000, L.status_word(dev), L.stream_ptr()), "wait_probe")
+    assert L.read_status(dev, reset=False) == L.STATUS_WAIT_PROBE      # first writer wins, stays until reset
+    assert L.read_status(dev) == L.STATUS_WAIT_PROBE
+    assert L.read_status(dev) == 0
+    a = torch.randn(2, 256, 256, generator=torch.Generator().manual_seed(1)).bfloat16().cuda()
+    got = mm["ns"].gemm_bf16(a, a)
+    _check(got, a.float().cpu() @ a.float().cpu().transpose(1, 2))
+    assert L.read_status(dev) == 0
+    assert L.load().mmb_wait_probe(0, L.status_word(dev), L.stream_ptr()) != 0   # limits outside 1..2e9 are refused
 
 
 def test_newton_schulz_in_place_and_sliced(mm):
@@ -345,3 +412,28 @@ def test_fast_exact_quotient_equals_compiler_division_on_many_elements(mm):
         out.append((codes, scales))
     assert torch.equal(out[0][0], out[1][0])
     assert torch.equal(out[0][1].view(torch.int32), out[1][1].view(torch.int32))
+
+
+def test_reciprocal_quotient_equals_the_division_instruction_on_many_elements(mm):
+    """In its default arithmetic the fused kernel forms m / s as m * rcp.approx(s) with one reciprocal per
+    group; the stand-alone quantiser issues div.full.f32 per element, the instruction the reference's Triton
+    kernels compile `/` to.  Both must give the same codes and scales: 2^27 elements, group scales over
+    sixteen decades, zero groups, a group with an infinite element."""
+    n = 1 << 27
+    gen = torch.Generator(device="cuda").manual_seed(78)
+    g = torch.empty(n, device="cuda").normal_(0, 1, generator=gen)
+    g *= torch.pow(10.0, torch.empty(n // 128, device="cuda").uniform_(-12, 4, generator=gen)).repeat_interleave(128)
+    g[:128] = 0.0
+    g[256] = float("inf")
+    L = mm["lib"]
+    codes = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(n // 128, device="cuda")
+    state = torch.zeros(n, device="cuda")
+    for step in range(2):
+        mm["fp8"].fp8_momentum_flat(codes, scales, g, 0.95, div_mode=L.DIV_FULL)
+        state.mul_(0.95).add_(g)                     # heavy ball on the decoded state, two roundings
+        want = {}
+        mm["fp8"].quantize_(want, "m", state, True, codec="absmax", div_mode=L.DIV_FULL)
+        assert torch.equal(scales.view(torch.int32), want["scale_m"].view(torch.int32)), step
+        assert torch.equal(codes, want["m"].view(torch.uint8)), step
+        state = mm["fp8"].dequantize(want, "m", True, codec="absmax")

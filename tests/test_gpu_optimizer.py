@@ -461,3 +461,27 @@ def test_two_stream_overlap_gives_the_same_bits(fmt):
             if torch.is_tensor(v):
                 assert torch.equal(v.view(torch.uint8) if v.dtype == torch.float8_e4m3fn else v,
                                    b.state[q][k].view(torch.uint8) if v.dtype == torch.float8_e4m3fn else b.state[q][k]), k
+
+
+@pytest.mark.parametrize("case", ["bf16", "fp32"])
+@pytest.mark.parametrize("fmt", ["fp8_absmax", "param"])
+def test_fused_update_gives_the_same_bits_as_the_update_kernel(fmt, case):
+    """The weight update applied in the epilogue of the last Newton-Schulz GEMM (default) against Newton-Schulz
+    to memory followed by the update kernel: identical weights and state after three steps, bf16 and fp32
+    parameters, slices cut into several Newton-Schulz sub-slices."""
+    a, am, aa = _ours(case, state_format=fmt, ns_max_batch=2)
+    b, bm, ba = _ours(case, state_format=fmt, ns_max_batch=2, fuse_update=False)
+    for step in range(gi.OPT_STEPS):
+        mg, ag = gi.opt_grads(case, step)
+        _feed(am, aa, mg, ag)
+        _feed(bm, ba, mg, ag)
+        a.step()
+        b.step()
+    torch.cuda.synchronize()
+    for p, q in zip(am + aa, bm + ba):
+        assert torch.equal(p.data, q.data)
+        for k, v in a.state[p].items():
+            if torch.is_tensor(v):
+                w = b.state[q][k]
+                assert torch.equal(v.view(torch.uint8) if v.dtype == torch.float8_e4m3fn else v,
+                                   w.view(torch.uint8) if w.dtype == torch.float8_e4m3fn else w), k
