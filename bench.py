@@ -308,7 +308,11 @@ def main():
                          "tensor of --fp8-elems elements (FP8 moments with --state-format coat)")
     ap.add_argument("--ns-blocks", type=int, default=128, help="square blocks in --case ns (tall/wide get half each)")
     ap.add_argument("--fp8-elems", type=int, default=1_600_000_000)
-    ap.add_argument("--comm-sms", type=int, default=0, help="SMs left to NCCL during the sharded step")
+    ap.add_argument("--comm-sms", type=int, default=-1,
+                    help="SMs left to the communication kernels during the sharded step (-1: the transport's default)")
+    ap.add_argument("--comm", default="nccl", choices=["nccl", "multimem", "auto"],
+                    help="transport of the sharded step: NCCL collectives, this library's NVSwitch multicast kernels, "
+                         "or auto (multicast from four GPUs on where the fabric provides it)")
     ap.add_argument("--chunks", type=int, default=4, help="pipeline chunks of the sharded (multi-GPU) step")
     ap.add_argument("--dynamic-schedule", type=int, default=None, choices=[0, 1],
                     help="Newton-Schulz GEMM tiles drawn from a counter (1) or fixed round-robin (0); default: 1 in "

@@ -334,6 +334,30 @@ int mmb_grad_norm_clip(const mmb_grad_seg* segs, int nseg, float max_norm, float
 int mmb_set_device_grad_scale(const float* scale_dev);
 
 /* ------------------------------------------------------------------------
+ * Reduce-scatter / all-gather pieces of the data-parallel (owner-computes) step
+ * through NVSwitch multicast.  No counterpart in the reference, which all-reduces
+ * gradients with DDP and steps every parameter on every rank
+ * (pretrain/src/distributed/ddp.py:42-52).  Both calls take one address inside a
+ * MULTICAST mapping of a buffer that every GPU of the group holds at the same
+ * offset (torch.distributed's symmetric memory provides it) and one ordinary
+ * device address, `nbytes` a multiple of 16, all 16-byte aligned:
+ *   mmb_multimem_reduce_bf16  dst[i] = sum over the group's copies of src[i], bf16
+ *                             elements added with fp32 accumulation inside the
+ *                             switch (multimem.ld_reduce) - called on the range a
+ *                             rank owns, this is its share of a reduce-scatter;
+ *   mmb_multimem_broadcast    every copy of dst[i] = src[i] (multimem.st) - called
+ *                             on the range a rank owns, its share of an all-gather.
+ * `ctas` CTAs of 512 threads are launched (16 saturate the links; few on purpose,
+ * the kernels run beside the GEMMs).  The kernels wait on nothing and hold no
+ * flags: the caller orders them against the other ranks (all copies written before
+ * the first reduce; a group-wide collective after the last broadcast before any
+ * copy is read).  On a GPU or buffer without multicast support the calls must not
+ * be used.
+ * ---------------------------------------------------------------------- */
+int mmb_multimem_reduce_bf16(const void* multicast_src, void* dst_dev, int64_t nbytes, int ctas, void* stream);
+int mmb_multimem_broadcast(const void* src_dev, void* multicast_dst, int64_t nbytes, int ctas, void* stream);
+
+/* ------------------------------------------------------------------------
  * Device status word.  Kernels never trap: a bounded wait that expires or a
  * failed self-check stores a non-zero code here and the kernel returns.
  * mmb_device_status_read synchronises `stream` and returns the word.

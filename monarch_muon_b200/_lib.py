@@ -97,6 +97,8 @@ SYMBOLS = {
     "mmb_grad_norm_scratch_floats": (_i64, []),
     "mmb_grad_norm_clip": (_i, [C.POINTER(GradSeg), _i, _f, _vp, _vp, _i64, _vp]),
     "mmb_set_device_grad_scale": (_i, [_vp]),
+    "mmb_multimem_reduce_bf16": (_i, [_vp, _vp, _i64, _i, _vp]),
+    "mmb_multimem_broadcast": (_i, [_vp, _vp, _i64, _i, _vp]),
     "mmb_device_status_create": (_i, [C.POINTER(_vp)]),
     "mmb_device_status_destroy": (_i, [_vp]),
     "mmb_device_status_read": (_i, [_vp, C.POINTER(C.c_int32), _i, _vp]),

@@ -15,9 +15,12 @@ A chunk arena is `world` equal shards, shard r owned by rank r:
     arena = [chunk 0: shard(rank 0) | shard(rank 1) | ... ][chunk 1: ...] ... [AdamW chunk]
 
 Inside a Muon shard the owned tensors lie back to back, grouped by block shape.
-Whole tensors are owned (a parameter must stay one contiguous view), tensors of
-one shape are dealt to ranks in equal contiguous runs, and shards are padded to
-the longest one.  The AdamW chunk is cut element-wise into equal slices, so a
+Whole tensors are owned (a parameter must stay one contiguous view).  Tensors of
+one shape are dealt to ranks in contiguous runs of equal length - equal FLOPs and
+equal bytes at once when the counts divide, as they do for the LLaMA shapes here -
+and what does not divide goes, one tensor each, to the ranks with the least
+Newton-Schulz work so far (longest-processing-time rule), heavy shapes first.
+Shards are padded to the longest one.  The AdamW chunk is cut element-wise into equal slices, so a
 tensor may straddle ranks.
 """
 from __future__ import annotations
@@ -72,6 +75,13 @@ def _align(n: int, a: int) -> int:
     return -(-n // a) * a
 
 
+def _tensor_flops(shape) -> float:
+    """Newton-Schulz work of one (nblocks, rows, cols) tensor: 5 x (4 m^2 n + 2 m^3) per block."""
+    nb, r, c = shape
+    m, n = min(r, c), max(r, c)
+    return nb * 5.0 * (4.0 * m * m * n + 2.0 * m ** 3)
+
+
 def make_plan(muon_shapes, adamw_numels, world: int, n_chunks: int = 4, align: int = 128) -> Plan:
     """muon_shapes: (nblocks, rows, cols) per Muon tensor; adamw_numels: element
     counts of the AdamW tensors.  `align` keeps every tensor and shard on a
@@ -84,14 +94,26 @@ def make_plan(muon_shapes, adamw_numels, world: int, n_chunks: int = 4, align: i
         by_shape.setdefault((r, c), []).append(i)
     places = {}
     cursor = 0
+    load = [0.0] * world           # Newton-Schulz FLOPs dealt to each rank so far, over all chunks
+    # heaviest tensors first, so that the remainders of the light shapes can even out those of the heavy ones
+    order = sorted(by_shape.items(), key=lambda kv: -_tensor_flops(muon_shapes[kv[1][0]]))
     for ch in range(n_chunks):
         per_rank = [[] for _ in range(world)]
-        for (r, c), idxs in by_shape.items():
+        for (r, c), idxs in order:
             n = len(idxs)
             mine = idxs[ch * n // n_chunks:(ch + 1) * n // n_chunks]      # this chunk's share of the shape
             k = len(mine)
+            # every rank gets k // world tensors of the shape; the k % world left over go, one each, to the
+            # ranks that carry the least work so far (longest-processing-time rule on the remainders)
+            counts = [k // world] * world
+            for rank in sorted(range(world), key=lambda q: (load[q], q))[:k % world]:
+                counts[rank] += 1
+            at = 0
             for rank in range(world):
-                per_rank[rank] += mine[rank * k // world:(rank + 1) * k // world]
+                take = mine[at:at + counts[rank]]
+                at += counts[rank]
+                per_rank[rank] += take
+                load[rank] += sum(_tensor_flops(muon_shapes[i]) for i in take)
         sizes = [sum(_align(muon_shapes[i][0] * muon_shapes[i][1] * muon_shapes[i][2], align) for i in lst)
                  for lst in per_rank]
         shard = _align(max(sizes) if sizes else 0, align)

@@ -4,23 +4,44 @@ The reference trains with DDP: gradients are all-reduced and every rank then
 runs the whole optimizer step redundantly (pretrain/src/distributed/ddp.py:42-52).
 Here each rank steps only the tensors it owns:
 
-    reduce-scatter(gradients)  ->  local momentum / Newton-Schulz / update /
+    reduce-scatter(gradients)  ->  local momentum / Newton-Schulz + update /
     AdamW on the owned shard   ->  all-gather(updated weights)
 
-over NCCL (NVLink / NVSwitch).  The wire volume equals the all-reduce it
-replaces; optimizer state and optimizer compute shrink by the world size.
-Nothing in the step reads another GPU's memory from a kernel: remote data lands
-in local HBM through NCCL first.
+The wire volume equals the all-reduce it replaces; optimizer state and optimizer
+compute shrink by the world size.
 
 Weights and gradients live in two flat arenas laid out by `partition.make_plan`
 (chunk-major, then rank-major).  Parameters are re-pointed at views of the
 weight arena and given gradient views of the gradient arena, so backward
-accumulates straight into the buffer that is reduce-scattered.  Chunks are
-pipelined: all reduce-scatters are queued up front on one communicator, each
-chunk's local step waits only for its own reduce-scatter, and its all-gather is
-queued on a second communicator as soon as its kernels are enqueued.
+accumulates straight into the buffer that is reduced.  Chunks are pipelined.
+
+Two transports (`comm=`):
+
+  "nccl"      NCCL reduce-scatter / all-gather through torch.distributed: all
+              reduce-scatters are queued up front on one communicator, each
+              chunk's local step waits only for its own, and its all-gather is
+              queued on a second communicator as soon as its kernels are
+              enqueued.  Remote data lands in local HBM through NCCL; no kernel
+              of this library touches another GPU's memory.
+  "multimem"  this library's own kernels over NVSwitch multicast
+              (csrc/multimem.cu): the arenas are symmetric memory, a rank reduces
+              its shard of a chunk with multimem.ld_reduce (the sum is formed
+              inside the switch) on one side stream and broadcasts its updated
+              shard with multimem.st on another, while the GEMMs of the chunk in
+              between run on the caller's stream.  The reduce loads the links
+              outbound and the broadcast inbound, so the two overlap at full
+              rate, which two ring collectives cannot.  Ranks are ordered against
+              each other by one tiny NCCL all-reduce before the first reduce of a
+              step and one after the last broadcast; the kernels themselves never
+              wait on a peer.  Pays from four GPUs on (with two, a ring moves
+              fewer bytes per link).
+  "auto"      "multimem" where the group has four or more ranks on one node and
+              the arenas could be mapped for multicast, else "nccl".
 """
 from __future__ import annotations
+
+import contextlib
+import hashlib
 
 import torch
 import torch.distributed as dist
@@ -46,25 +67,27 @@ class ShardedMonarchMuon:
     average : divide the reduced gradient by the world size (DDP semantics).
     local_factory(muon_params, adamw_params, **hyper) : builds the optimizer
         that steps the owned views; defaults to MonarchMuonOptimizer (CUDA).
-    comm_sms : SMs kept free of this library's kernels during the step, for the
-        collectives' kernels.
+    comm : "nccl", "multimem" or "auto" (see the module text).
+    comm_sms : SMs kept free of this library's compute kernels during the step,
+        for the communication kernels (default: 0 with NCCL, 16 with multimem).
     dynamic_schedule : let the Newton-Schulz GEMMs draw their tiles from a counter
-        during the step, so that SMs taken by a collective's kernels cost those
+        during the step, so that SMs taken by a communication kernel cost those
         SMs' share of the work instead of stalling a whole launch.
     """
 
     def __init__(self, muon_params, adamw_params, *, process_group=None, lr: float = 5e-3, momentum: float = 0.95,
                  adamw_betas=(0.9, 0.95), adamw_weight_decay: float = 0.1, adamw_eps: float = 1e-8,
                  n_chunks: int = 4, average: bool = True, local_factory=None, second_group: bool = True,
-                 comm_sms: int = 0, dynamic_schedule: bool = True, **local_kwargs):
+                 comm: str = "nccl", comm_sms: int | None = None, comm_ctas: int = 16,
+                 dynamic_schedule: bool = True, **local_kwargs):
         if not dist.is_initialized():
             raise RuntimeError("ShardedMonarchMuon needs an initialised torch.distributed process group")
+        if comm not in ("nccl", "multimem", "auto"):
+            raise ValueError("comm must be 'nccl', 'multimem' or 'auto'")
         self.group = process_group
         self.world = dist.get_world_size(process_group)
         self.rank = dist.get_rank(process_group)
         self.backend = dist.get_backend(process_group)
-        self.ag_group = dist.new_group(ranks=list(range(dist.get_world_size())), backend=self.backend) \
-            if (second_group and process_group is None) else process_group
         self.muon_params = list(muon_params)
         self.adamw_params = list(adamw_params)
         allp = self.muon_params + self.adamw_params
@@ -79,16 +102,32 @@ class ShardedMonarchMuon:
                 raise ValueError("Muon parameters must be 3-D (nblocks, rows, cols)")
         self.plan = partition.make_plan([tuple(p.shape) for p in self.muon_params],
                                         [p.numel() for p in self.adamw_params], self.world, n_chunks)
+        self._check_same_plan_everywhere()
+        self.ag_group = dist.new_group(ranks=list(range(dist.get_world_size())), backend=self.backend) \
+            if (second_group and process_group is None) else process_group
         self.average = average
-        # SMs left free during the step so that NCCL's kernels can run beside the persistent GEMMs
-        # (which otherwise occupy every SM and serialise with them)
-        self.comm_sms = comm_sms
         self.dynamic_schedule = dynamic_schedule
+        self.comm_ctas = int(comm_ctas)
         n = self.plan.total_elems
-        self.w_arena = torch.zeros(n, dtype=self.dtype, device=self.device)
-        self.g_arena = torch.zeros(n, dtype=self.dtype, device=self.device)
+        # ---- arenas: symmetric memory when this library's multicast kernels move the data
+        self.comm = "nccl"
+        self._mc_g = self._mc_w = 0
+        want_mc = comm == "multimem" or (comm == "auto" and self.world >= 4)
+        if want_mc and self.backend == "nccl" and self.dtype == torch.bfloat16:
+            arenas = self._symmetric_arenas(n)
+            if arenas is not None:
+                self.w_arena, self.g_arena, self._mc_w, self._mc_g = arenas
+                self.comm = "multimem"
+            elif comm == "multimem":
+                raise RuntimeError("comm='multimem': the arenas could not be mapped for NVSwitch multicast on this group")
+        if self.comm == "nccl":
+            self.w_arena = torch.zeros(n, dtype=self.dtype, device=self.device)
+            self.g_arena = torch.zeros(n, dtype=self.dtype, device=self.device)
+        # SMs left free during the step so that communication kernels can run beside the persistent GEMMs
+        # (which otherwise occupy every SM and serialise with them)
+        self.comm_sms = (16 if self.comm == "multimem" else 0) if comm_sms is None else int(comm_sms)
         # reduced gradients of the owned shards, chunk after chunk (the gradient arena itself is left
-        # untouched by the reduce-scatter, so it can keep accumulating or be reused)
+        # untouched by the reduction, so it can keep accumulating or be reused)
         self.own_offset = []
         at = 0
         for ch in self.plan.chunks:
@@ -113,17 +152,64 @@ class ShardedMonarchMuon:
              "eps": adamw_eps, "params": self.adamw_params},
         ]
         self.local = []
+        self._owned = []            # per chunk: [(kind, index in the caller's list, start inside the tensor, proxy)]
         for k, ch in enumerate(self.plan.chunks):
             if ch.kind == "muon":
                 owned = []
                 for t in self.plan.owned_muon(self.rank, k):
                     shape = self.muon_params[t.index].shape
-                    owned.append(self._proxy(k, t.offset, t.numel, shape))
-                self.local.append(local_factory(owned, [], **hyper) if owned else None)
+                    owned.append(("muon", t.index, 0, self._proxy(k, t.offset, t.numel, shape)))
+                self.local.append(local_factory([q for *_, q in owned], [], **hyper) if owned else None)
             else:
-                owned = [self._proxy(k, off, length, (length,))
-                         for _, _, length, off in self.plan.adamw_slices(self.rank)]
-                self.local.append(local_factory([], owned, **hyper) if owned else None)
+                owned = [("adamw", idx, start, self._proxy(k, off, length, (length,)))
+                         for idx, start, length, off in self.plan.adamw_slices(self.rank)]
+                self.local.append(local_factory([], [q for *_, q in owned], **hyper) if owned else None)
+            self._owned.append(owned)
+        self._streams = None
+        self._flag = None
+
+    # ----------------------------------------------------------------- checks
+    def _check_same_plan_everywhere(self) -> None:
+        """Every rank must have built the same ownership plan (same parameter lists, chunking and world
+        size): a rank with another table would reduce and gather other byte ranges.  Compared through one
+        all-gather of a digest; a mismatch raises on every rank instead of corrupting or hanging later."""
+        text = repr((self.world, [(c.offset, c.shard_elems, c.kind) for c in self.plan.chunks],
+                     [(t.index, t.chunk, t.rank, t.offset, t.numel) for t in self.plan.muon], self.plan.adamw,
+                     str(self.dtype)))
+        digest = hashlib.sha256(text.encode()).digest()[:8]
+        mine = torch.tensor(list(digest), dtype=torch.uint8)
+        if self.backend == "nccl":
+            mine = mine.to(self.device)
+        gathered = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(gathered, mine, group=self.group)
+        if any(not torch.equal(g, mine) for g in gathered):
+            raise ValueError("ShardedMonarchMuon: the ranks built different ownership plans (different parameter "
+                             "lists, chunk counts or dtypes); every rank must pass the same parameters in the same order")
+
+    def _symmetric_arenas(self, n: int):
+        """Weight and gradient arenas in symmetric memory with their multicast addresses, or None when the
+        group cannot provide them (no NVSwitch multicast, allocation refused).  All ranks decide together."""
+        ok, out = 1, None
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            group = self.group if self.group is not None else dist.group.WORLD
+            w = symm_mem.empty(n, dtype=self.dtype, device=self.device)
+            g = symm_mem.empty(n, dtype=self.dtype, device=self.device)
+            hw = symm_mem.rendezvous(w, group)
+            hg = symm_mem.rendezvous(g, group)
+            mw, mg = int(hw.multicast_ptr), int(hg.multicast_ptr)
+            if not mw or not mg:
+                ok = 0
+            else:
+                w.zero_()
+                g.zero_()
+                out = (w, g, mw, mg)
+                self._symm_handles = (hw, hg)        # keep the mappings alive
+        except Exception:                            # no symmetric memory in this build / on this fabric
+            ok = 0
+        flag = torch.tensor([ok], device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        return out if int(flag.item()) == 1 else None
 
     # ----------------------------------------------------------------- layout
     def _rebind(self, p, offset: int) -> None:
@@ -167,15 +253,22 @@ class ShardedMonarchMuon:
         mine.copy_(keep)
         return dist.all_reduce(whole, op=dist.ReduceOp.SUM, group=self.ag_group, async_op=True)
 
+    def _fence(self):
+        """Order this rank's stream against every other rank's: a one-element NCCL all-reduce.  Work queued
+        before it on any rank has finished before work queued after it on any rank starts."""
+        if self._flag is None:
+            self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
+        dist.all_reduce(self._flag, group=self.group)
+
     # ------------------------------------------------------------------- step
     def _check_gradients_in_arena(self) -> None:
         """Every parameter's .grad must still be the arena view installed at construction: the
-        reduce-scatter sends the arena, not whatever tensor autograd may have put there instead.
+        reduction reads the arena, not whatever tensor autograd may have put there instead.
         `model.zero_grad()` (set_to_none=True by default) and `p.grad = None` break that; a fresh
         gradient found here is copied into the arena and the view is put back."""
-        for params, places in ((self.muon_params, [(pl.offset,) for pl in self.plan.muon]),
-                               (self.adamw_params, [(off,) for _, off, _ in self.plan.adamw])):
-            for p, (offset,) in zip(params, places):
+        for params, offsets in ((self.muon_params, [pl.offset for pl in self.plan.muon]),
+                                (self.adamw_params, [off for _, off, _ in self.plan.adamw])):
+            for p, offset in zip(params, offsets):
                 view = self.g_arena[offset:offset + p.numel()].view(p.shape)
                 g = p.grad
                 if g is None:
@@ -188,48 +281,132 @@ class ShardedMonarchMuon:
                     p.grad = view
 
     @torch.no_grad()
-    def step(self):
-        self._check_gradients_in_arena()
-        nccl = self.backend == "nccl"
-        if nccl:
+    def step(self, host_grad_arena: torch.Tensor | None = None):
+        """One sharded step.  `host_grad_arena` (extension): this rank's gradients as one pinned host tensor
+        with the arena's layout and dtype; it is copied into the gradient arena chunk by chunk on a copy
+        stream, each chunk's reduction starting as soon as its own copy has landed, so the host-to-device
+        transfer of later chunks runs under the reduction and compute of earlier ones."""
+        self._copied = None
+        if host_grad_arena is not None:
+            if host_grad_arena.shape != self.g_arena.shape or host_grad_arena.dtype != self.g_arena.dtype:
+                raise ValueError("host_grad_arena must have the gradient arena's shape and dtype")
+            self._enqueue_host_copies(host_grad_arena)
+        else:
+            self._check_gradients_in_arena()
+        if self.backend == "nccl":
             from . import _lib
             total = torch.cuda.get_device_properties(self.device).multi_processor_count
             options = _lib.launch_options(sm_limit=max(2, total - self.comm_sms) if self.comm_sms > 0 else 0,
                                           dynamic_schedule=self.dynamic_schedule)
         else:
-            import contextlib
             options = contextlib.nullcontext()
         with options:                                  # launch options are put back even if a local step raises
-            self._step_chunks()
+            if self.comm == "multimem":
+                self._step_chunks_multimem()
+            else:
+                self._step_chunks()
+
+    def _enqueue_host_copies(self, host) -> None:
+        main = torch.cuda.current_stream(self.device)
+        if getattr(self, "_copy_stream", None) is None:
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+            self._issue_stream = torch.cuda.Stream(device=self.device)
+        cs = self._copy_stream
+        cs.wait_stream(main)                           # last step's readers of the arena are done
+        self._copied = []
+        with torch.cuda.stream(cs):
+            for ch in self.plan.chunks:
+                lo, hi = ch.offset, ch.offset + self.world * ch.shard_elems
+                self.g_arena[lo:hi].copy_(host[lo:hi], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(cs)
+                self._copied.append(ev)
+
+    def _local_step(self, k: int) -> None:
+        opt = self.local[k]
+        if opt is None:
+            return
+        ch = self.plan.chunks[k]
+        scale = 1.0 / self.world if self.average else 1.0
+        group = self.param_groups[0 if ch.kind == "muon" else 1]
+        for g in opt.param_groups:
+            if g["update_type"] == group["update_type"]:
+                for key, val in group.items():
+                    if key not in ("params", "update_type"):
+                        g[key] = val
+        if ch.kind == "muon":
+            opt.grad_scale = scale
+        elif scale != 1.0:
+            self.chunk_views(k)[1].mul_(scale)      # AdamW has no fused gradient scale
+        opt.step()
 
     def _step_chunks(self):
         nchunks = len(self.plan.chunks)
         rs = []
         for k in range(nchunks):
             g_whole, g_mine, _, _ = self.chunk_views(k)
-            rs.append(self._reduce_scatter(g_whole, g_mine))
+            if self._copied is not None:
+                # the collective is issued from a stream that waits for this chunk's copy only, so the
+                # caller's stream (and the local steps queued on it) does not wait for later copies
+                with torch.cuda.stream(self._issue_stream):
+                    self._issue_stream.wait_event(self._copied[k])
+                    rs.append(self._reduce_scatter(g_whole, g_mine))
+            else:
+                rs.append(self._reduce_scatter(g_whole, g_mine))
         ag = []
-        scale = 1.0 / self.world if self.average else 1.0
         for k in range(nchunks):
             rs[k].wait()
-            opt = self.local[k]
-            ch = self.plan.chunks[k]
-            if opt is not None:
-                group = self.param_groups[0 if ch.kind == "muon" else 1]
-                for g in opt.param_groups:
-                    if g["update_type"] == group["update_type"]:
-                        for key, val in group.items():
-                            if key not in ("params", "update_type"):
-                                g[key] = val
-                if ch.kind == "muon":
-                    opt.grad_scale = scale
-                elif scale != 1.0:
-                    self.chunk_views(k)[1].mul_(scale)      # AdamW has no fused gradient scale
-                opt.step()
+            self._local_step(k)
             _, _, w_whole, w_mine = self.chunk_views(k)
             ag.append(self._all_gather(w_whole, w_mine))
         for w in ag:
             w.wait()
+
+    def _step_chunks_multimem(self):
+        """The chunk pipeline over this library's multicast kernels: all reductions are queued on one side
+        stream, each chunk's local step waits for its own reduction on the caller's stream, and its
+        broadcast goes to a second side stream; reductions (outbound on the links) and broadcasts (inbound)
+        overlap each other and the GEMMs."""
+        from . import _lib
+        lib = _lib.load()
+        main = torch.cuda.current_stream(self.device)
+        if self._streams is None:
+            self._streams = (torch.cuda.Stream(device=self.device), torch.cuda.Stream(device=self.device))
+        s_red, s_bc = self._streams
+        esz = self.g_arena.element_size()
+        nchunks = len(self.plan.chunks)
+        if self._copied is not None:
+            main.wait_event(self._copied[-1])          # peers read this rank's arena: all of it must have landed
+        self._fence()                                  # every rank's gradients are in its arena
+        s_red.wait_stream(main)
+        s_bc.wait_stream(main)
+        reduced = []
+        with torch.cuda.stream(s_red):
+            for k in range(nchunks):
+                ch = self.plan.chunks[k]
+                lo = ch.offset + self.rank * ch.shard_elems
+                _lib.check(lib.mmb_multimem_reduce_bf16(self._mc_g + lo * esz,
+                                                        self.g_own[self.own_offset[k]:].data_ptr(),
+                                                        ch.shard_elems * esz, self.comm_ctas, s_red.cuda_stream),
+                           "multimem_reduce_bf16")
+                ev = torch.cuda.Event()
+                ev.record(s_red)
+                reduced.append(ev)
+        for k in range(nchunks):
+            ch = self.plan.chunks[k]
+            main.wait_event(reduced[k])
+            self._local_step(k)
+            done = torch.cuda.Event()
+            done.record(main)
+            lo = ch.offset + self.rank * ch.shard_elems
+            with torch.cuda.stream(s_bc):
+                s_bc.wait_event(done)
+                _lib.check(lib.mmb_multimem_broadcast(self.w_arena[lo:].data_ptr(), self._mc_w + lo * esz,
+                                                      ch.shard_elems * esz, self.comm_ctas, s_bc.cuda_stream),
+                           "multimem_broadcast")
+        main.wait_stream(s_bc)
+        main.wait_stream(s_red)
+        self._fence()                                  # every rank's broadcasts have landed everywhere
 
     def zero_grad(self, set_to_none: bool = False):
         """Gradients are arena views and stay allocated; they are zeroed in place (set_to_none is
@@ -244,14 +421,88 @@ class ShardedMonarchMuon:
             if p.grad is None or p.grad.data_ptr() != self.g_arena[off:].data_ptr():
                 p.grad = self.g_arena[off:off + p.numel()].view(p.shape)
 
+    # ----------------------------------------------------------- checkpoints
+    def _local_entries(self):
+        """This rank's optimizer state, keyed like the reference's state_dict: for a Muon tensor
+        ("muon", index) -> its state; for the slice of an AdamW tensor ("adamw", index, start) -> the
+        slice's state.  Tensors are moved to the CPU."""
+        out = {}
+        for owned, opt in zip(self._owned, self.local):
+            if opt is None:
+                continue
+            for kind, idx, start, proxy in owned:
+                st = opt.state.get(proxy)
+                if not st:
+                    continue
+                entry = {k: (v.detach().cpu() if torch.is_tensor(v) else v) for k, v in st.items()}
+                out[(kind, idx) if kind == "muon" else (kind, idx, start)] = entry
+        return out
+
     def state_dict(self):
-        """Per-rank shard: the local optimizers' state, in chunk order."""
-        return {"rank": self.rank, "world": self.world,
-                "chunks": [None if o is None else o.state_dict() for o in self.local]}
+        """The optimizer state in the reference's shape: {"state": {parameter index: {...}}, "param_groups":
+        [...]} with Muon parameters first (indices as in MonarchMuonOptimizer(muon_params, adamw_params)),
+        identical on every rank and independent of the world size it was saved on, so that the reference's
+        save_checkpoint / load_checkpoint (pretrain/src/optim/utils.py:103-132) round-trip it and a run can
+        resume on another number of GPUs.  Collective: every rank must call it.  Moments of an AdamW tensor
+        that is cut across ranks are reassembled (element-wise state; `step` is taken from its first slice)."""
+        for opt in self.local:
+            if opt is not None and hasattr(opt, "check_device_status"):
+                opt.check_device_status()
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, self._local_entries(), group=self.group)
+        nm = len(self.muon_params)
+        state = {}
+        pieces = {}
+        for entries in gathered:
+            for key, entry in entries.items():
+                if key[0] == "muon":
+                    state[key[1]] = entry
+                else:
+                    pieces.setdefault(key[1], []).append((key[2], entry))
+        for idx, parts in pieces.items():
+            parts.sort(key=lambda t: t[0])
+            p = self.adamw_params[idx]
+            merged = {}
+            for name, v in parts[0][1].items():
+                if torch.is_tensor(v) and v.dim() > 0:
+                    if any(v2[name].dtype == torch.float8_e4m3fn for _, v2 in parts):
+                        raise NotImplementedError("FP8 AdamW moments of a tensor cut across ranks are not merged")
+                    merged[name] = torch.cat([e[name].reshape(-1) for _, e in parts]).view(p.shape)
+                else:
+                    merged[name] = v
+            state[nm + idx] = merged
+        groups = []
+        at = 0
+        for g in self.param_groups:
+            d = {k: v for k, v in g.items() if k != "params"}
+            d["params"] = list(range(at, at + len(g["params"])))
+            at += len(g["params"])
+            groups.append(d)
+        return {"state": state, "param_groups": groups}
 
     def load_state_dict(self, sd):
-        if sd["world"] != self.world or sd["rank"] != self.rank:
-            raise ValueError("sharded state was saved for another rank/world size")
-        for o, s in zip(self.local, sd["chunks"]):
-            if o is not None and s is not None:
-                o.load_state_dict(s)
+        """Restore a state dict written by state_dict() - on any world size - or by the reference's
+        optimizer: every rank takes the entries of the tensors (and AdamW slices) it owns."""
+        nm = len(self.muon_params)
+        for g, saved in zip(self.param_groups, sd["param_groups"]):
+            for k, v in saved.items():
+                if k != "params":
+                    g[k] = v
+        for owned, opt in zip(self._owned, self.local):
+            if opt is None:
+                continue
+            local_state = {}
+            params = [q for *_, q in owned]
+            for i, (kind, idx, start, proxy) in enumerate(owned):
+                entry = sd["state"].get(idx if kind == "muon" else nm + idx)
+                if entry is None:
+                    continue
+                if kind == "muon":
+                    local_state[i] = dict(entry)
+                else:
+                    n = proxy.numel()
+                    local_state[i] = {k: (v.reshape(-1)[start:start + n].clone() if torch.is_tensor(v) and v.dim() > 0 else v)
+                                      for k, v in entry.items()}
+            base = opt.state_dict()["param_groups"]
+            # the local optimizer numbers its parameters 0.. in the order of `owned`
+            opt.load_state_dict({"state": local_state, "param_groups": base})

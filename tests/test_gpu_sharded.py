@@ -28,14 +28,23 @@ def grads(r, step):
     # multiples of 2^-12 keep the bf16 sums over ranks exact, so the reduction order cannot matter
     return [(torch.randint(-8, 9, s, generator=g).float() * 2.0 ** -12).bfloat16() for s in ms + asz]
 muon = [torch.nn.Parameter(w.to(dev)) for w in w_m]; adamw = [torch.nn.Parameter(w.to(dev)) for w in w_a]
-opt = ShardedMonarchMuon(muon, adamw, lr=0.02, n_chunks=2, average=False, state_format="fp8_absmax")
+comm = os.environ.get("MMB_TEST_COMM", "nccl")
+opt = ShardedMonarchMuon(muon, adamw, lr=0.02, n_chunks=2, average=False, state_format="fp8_absmax", comm=comm)
+assert opt.comm == comm, (opt.comm, comm)
+host = torch.empty(opt.g_arena.shape, dtype=opt.g_arena.dtype, pin_memory=True)
 # serial twin on the summed gradient, same kernels
 smuon = [torch.nn.Parameter(w.to(dev)) for w in w_m]; sadamw = [torch.nn.Parameter(w.to(dev)) for w in w_a]
 ser = MonarchMuonOptimizer(smuon, sadamw, lr=0.02, state_format="fp8_absmax")
-for step in range(2):
+for step in range(3):
     for p, g in zip(muon + adamw, grads(rank, step)):
         p.grad.copy_(g.to(dev))
-    opt.step()
+    if step == 2:                       # third step: gradients fed from pinned host memory, chunk by chunk
+        host.copy_(opt.g_arena)
+        torch.cuda.synchronize()
+        opt.g_arena.zero_()
+        opt.step(host_grad_arena=host)
+    else:
+        opt.step()
     tot = [sum(gs) for gs in zip(*[[t.float() for t in grads(r, step)] for r in range(world)])]
     for p, g in zip(smuon + sadamw, tot):
         p.grad = g.bfloat16().to(dev)
@@ -49,14 +58,19 @@ dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_sharded_step_is_bitwise_the_serial_step(tmp_path):
+@pytest.mark.parametrize("comm", ["nccl", "multimem"])
+def test_sharded_step_is_bitwise_the_serial_step(tmp_path, comm):
+    """Two GPUs, three steps (the last one fed from pinned host memory), gradients whose sums over the ranks
+    are exact in bf16: the sharded weights must equal, bit for bit, those of the serial step on the summed
+    gradient - with NCCL collectives and with this library's NVSwitch multicast kernels.  Ranks live in
+    child processes and leave only after their last step; NCCL's own in-switch algorithms are off here."""
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     env = dict(os.environ, MMB_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
-               NCCL_NVLS_ENABLE="0")
+               NCCL_NVLS_ENABLE="0", MMB_TEST_COMM=comm)
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                           "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
                          env=env, capture_output=True, text=True, timeout=600)
