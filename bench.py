@@ -307,6 +307,8 @@ def main():
                          "back for seconds so that the power cap is in force; adamw: the AdamW kernel alone on a flat bf16 "
                          "tensor of --fp8-elems elements (FP8 moments with --state-format coat)")
     ap.add_argument("--ns-blocks", type=int, default=128, help="square blocks in --case ns (tall/wide get half each)")
+    ap.add_argument("--ns-update", type=int, default=0, choices=[0, 1],
+                    help="--case ns: apply the weight update in the last GEMM's epilogue (as the optimizer step does)")
     ap.add_argument("--fp8-elems", type=int, default=1_600_000_000)
     ap.add_argument("--comm-sms", type=int, default=-1,
                     help="SMs left to the communication kernels during the sharded step (-1: the transport's default)")
@@ -624,10 +626,12 @@ def run_gemm_comparison(args, dev):
     return 0
 
 
-def measure_isolated_ns(dev, nblocks: int, ns_blocks: int, steps: int, warmup: int) -> dict:
+def measure_isolated_ns(dev, nblocks: int, ns_blocks: int, steps: int, warmup: int, with_update: bool = False) -> dict:
     """Batched Newton-Schulz alone on N(0,1) bf16 blocks: `ns_blocks` square blocks and half as many of the
-    tall and of the wide shape (128 + 64 + 64 at the 4-block shapes is the metric's isolated case)."""
+    tall and of the wide shape (128 + 64 + 64 at the 4-block shapes is the metric's isolated case).  With
+    `with_update` the weight update rides in the last GEMM's epilogue, as in the optimizer step."""
     from monarch_muon_b200 import newton_schulz_batched
+    from monarch_muon_b200.newton_schulz import newton_schulz_update
     pk = peaks()
     gen = torch.Generator(device=dev).manual_seed(99)
     r = 1024 * 4 // nblocks
@@ -637,9 +641,16 @@ def measure_isolated_ns(dev, nblocks: int, ns_blocks: int, steps: int, warmup: i
     outs = [torch.empty_like(x) for x in xs]
     flops = sum(s[0] * S.ns_flops(s[1], s[2]) for s in sets)
 
+    tables = [torch.tensor([o.data_ptr() + k * s[1] * s[2] * 2 for k in range(s[0])], dtype=torch.int64).to(dev)
+              for o, s in zip(outs, sets)]
+
     def fn():
-        for x, o in zip(xs, outs):
-            newton_schulz_batched(x, out=o, max_batch=256)
+        for x, o, t in zip(xs, outs, tables):
+            if with_update:                       # `outs` play the weights
+                for a in range(0, x.shape[0], 256):
+                    newton_schulz_update(x[a:a + 256], t[a:a + 256], torch.bfloat16, -0.02)
+            else:
+                newton_schulz_batched(x, out=o, max_batch=256)
     sampler = ClockSampler(dev.index or 0)
     sampler.start()
     ms, tb, te = _timed(fn, steps, warmup)
@@ -695,7 +706,7 @@ def run_isolated(args, dev):
     from monarch_muon_b200 import _lib
     l0 = _lib.launch_count()
     if args.case == "ns":
-        r = measure_isolated_ns(dev, args.nblocks, args.ns_blocks, args.steps, args.warmup)
+        r = measure_isolated_ns(dev, args.nblocks, args.ns_blocks, args.steps, args.warmup, bool(args.ns_update))
         line = {"metric": "newton_schulz_tflops"}
     else:
         r = measure_isolated_fp8(dev, args.fp8_elems, args.state_format, args.fp8_div, args.steps, args.warmup)

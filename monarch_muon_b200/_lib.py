@@ -22,7 +22,7 @@ DIV_IEEE, DIV_FULL, DIV_IEEE_STRICT = 0, 1, 2
 # kernel bit for bit on the same GPU; DIV_IEEE reproduces the CPU oracle bit for bit instead.
 DIV_DEFAULT = DIV_FULL
 DIV_NAMES = {"full": DIV_FULL, "ieee": DIV_IEEE, "ieee_strict": DIV_IEEE_STRICT}
-NS_TCGEN05, NS_SIMT = 0, 1
+NS_TCGEN05, NS_SIMT, NS_TCGEN05_MULTI = 0, 1, 2
 STATUS_NAMES = {0x101: "TMA producer waited too long for a free stage", 0x102: "MMA issuer waited too long for operands",
                 0x103: "MMA issuer waited too long for a drained accumulator",
                 0x104: "epilogue waited too long for an accumulator", 0x105: "a role waited too long for its next tile",

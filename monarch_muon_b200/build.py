@@ -18,7 +18,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libmonarch_muon_b200.so")
 SOURCES = ("common.cu", "momentum_fp8.cu", "elementwise.cu", "master_weights.cu", "adamw_fp8.cu", "gemm_tcgen05.cu",
-           "newton_schulz.cu", "multimem.cu")
+           "newton_schulz.cu", "ns_onchip.cu", "multimem.cu")
 
 
 def _nvcc() -> str:

@@ -1,6 +1,8 @@
 // Interface between the Newton-Schulz driver and its GEMM back ends.
 #pragma once
 
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace mmb {
@@ -28,8 +30,17 @@ struct GemmCall {
 };
 
 int gemm_tcgen05(const GemmCall& g, int32_t* status, cudaStream_t st);
+namespace tc {
+// Tensor map over a bf16 array [batch][outer][inner] with a box of {64, box_outer, 1} and 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* base, int batch, int outer, int inner, int box_outer);
+}  // namespace tc
 int gemm_simt(const GemmCall& g, cudaStream_t st);
 int gemm_occupancy(int pair, int* out);
+
+// Newton-Schulz of small blocks in one launch, operands resident in shared / tensor memory (ns_onchip.cu).
+bool ns_onchip_fits(int rows, int cols);
+int ns_onchip(const void* x, void* out, const float* inv_norm, int batch, int rows, int cols, float beta, float kappa,
+              float c, void* const* upd_w, int upd_f32, float upd_alpha, int32_t* status, cudaStream_t st);
 int wait_probe(long long limit_cycles, int32_t* status, cudaStream_t st);
 
 }  // namespace mmb

@@ -56,6 +56,7 @@
 
 #include "common.cuh"
 #include "gemm.cuh"
+#include "tcgen05_ptx.cuh"
 
 namespace mmb {
 namespace tc {
@@ -73,7 +74,6 @@ constexpr int CHUNK_BYTES = 64 * BK * 2;      // one 64-wide MN-major chunk (8 K
 constexpr int EPI_WARP_BYTES = 32 * 64 * 2;   // one epilogue warp's staging buffer: 32 rows x 64 columns of bf16
 constexpr int EPI_BYTES = NUM_EPI_WARPS * EPI_WARP_BYTES;
 constexpr int SYM_SHIFT = 8;                  // symmetric storage granularity: 256
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;
 constexpr int SCHED_DEPTH = 4;                // tile numbers a pair may hold ahead of its consumers (dynamic schedule)
 constexpr int SCHED_CONSUMERS_PER_CTA = 2 * PRODUCERS_PER_OPERAND + NUM_EPI_WARPS;  // plus the MMA thread in the even CTA
 
@@ -104,170 +104,6 @@ struct GemmArgs {
   int upd_f32;          // weights are fp32 (else bf16)
   long long wait_limit; // SM cycles a role may wait on a barrier before it gives up
 };
-
-// ------------------------------------------------------------------ PTX glue
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done;
-}
-// Same test with acquire semantics at cluster scope: for barriers whose arrival publishes data written
-// into this CTA's shared memory by the peer CTA.
-__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done;
-}
-__device__ __forceinline__ void st_shared_cluster_s32(uint32_t cluster_addr, int v) {
-  asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// shared::cluster address of `addr` (a shared::cta address) in the CTA of rank `rank`
-__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
-}
-// Relaxed on purpose: the arrival only announces bytes; the data itself is ordered by the bulk copy's
-// complete_tx.  A release here would make the producer wait for its own loads in flight and collapse
-// the pipeline to one stage.
-__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.relaxed.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
-}
-// Bounded wait.  Returns false when the CTA is aborting (this wait expired or
-// another role's did).  The fast path is a bare try_wait loop: the clock is
-// only consulted every 256 unsuccessful polls (each poll already suspends the
-// thread for a while), because reading a timer on every miss sits on the
-// critical path of each producer/consumer hand-off.  The limit is counted in SM
-// cycles (clock64): 4e9 cycles is about two seconds at 2 GHz.
-template <bool CLUSTER_ACQUIRE = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                          int32_t code, long long limit = WAIT_LIMIT_CYCLES) {
-  long long t0 = 0;
-  for (uint32_t spin = 1;; ++spin) {
-    if (CLUSTER_ACQUIRE ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
-    if ((spin & 255u) == 0u) {
-      if (*abort_flag) return false;
-      const long long now = clock64();
-      if (t0 == 0) {
-        t0 = now;
-      } else if (now - t0 > limit) {
-        *abort_flag = 1;
-        if (status != nullptr) atomicCAS(status, 0, code);
-        return false;
-      }
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-// Same load issued by a CTA of a pair: the data lands in this CTA's shared memory, the byte count is
-// signalled to `cluster_bar`, which may live in the peer CTA.
-__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c0, int c1,
-                                                 int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
-               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read_0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {  // arrives on `bar` in both CTAs of the pair
-  const uint16_t mask = 3;
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-               ::"r"(bar), "h"(mask)
-               : "memory");
-}
-// tcgen05.mma kind::f16 with the 64-bit shared-memory descriptors passed as (low, high) halves: only the
-// low half (start address) changes inside the K loop, so the issuing thread does 32-bit adds only.
-template <bool PAIR>
-__device__ __forceinline__ void tcgen05_mma_f16_split(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
-                                                      uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
-  if (PAIR) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-        "setp.ne.b32 p, %6, 0;\n\t"
-        "mov.b64 da, {%1, %2};\n\t"
-        "mov.b64 db, {%3, %4};\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-        "setp.ne.b32 p, %6, 0;\n\t"
-        "mov.b64 da, {%1, %2};\n\t"
-        "mov.b64 db, {%3, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-        : "memory");
-  }
-}
-__device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t* v) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle (built in the MMA issue loop):
 //   bits  0-13  start address >> 4
@@ -585,13 +421,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
       m0 += static_cast<int>(cta_rank) * BM;  // this CTA's half of a pair tile
       const uint32_t acc = local & 1u;
       const uint32_t acc_phase = (local >> 1) & 1u;
-      uint8_t* w_row = nullptr;  // UPD: this lane's row of the block's weights (null beyond the last row)
+      uint8_t* w_base = nullptr;  // UPD: this block's weights
       if (UPD) {
+        w_base = static_cast<uint8_t*>(args.upd_w[b]);
+        // pull this warp's pieces of W towards L2 while the accumulator is still being computed: lane = row
         const int wrow = m0 + quarter * 32 + lane;
         if (wrow < args.M) {
           const int esz = args.upd_f32 ? 4 : 2;
-          w_row = static_cast<uint8_t*>(args.upd_w[b]) + static_cast<long long>(wrow) * args.N * esz;
-          // pull this warp's pieces of W towards L2 while the accumulator is still being computed
+          const uint8_t* w_row = w_base + static_cast<long long>(wrow) * args.N * esz;
           for (int c = half; c < BN / 64; c += 2) {
             const int col0 = n0 + c * 64;
             if (col0 >= args.N) break;
@@ -616,69 +453,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
       const int row = row0 + lane;
       const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c = half; UPD && c < BN / 64; c += 2) {
-        const int col0 = n0 + c * 64;
-        if (col0 >= args.N || row0 >= args.M) break;  // uniform across the warp
-#pragma unroll 1
-        for (int h = 0; h < 2; ++h) {                 // 32 columns at a time keeps the live registers low
-          const int colh = col0 + 32 * h;
-          if (colh >= args.N) break;                  // uniform
-          uint32_t v[32];
-          if (args.upd_f32) {
-            float4 wv[8];
-            float4* wp = reinterpret_cast<float4*>(w_row + static_cast<long long>(colh) * 4);
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-              if (w_row != nullptr && colh + 4 * u < args.N) wv[u] = __ldcs(wp + u);
-            tcgen05_ld_32x32b_x32(t_base + c * 64 + 32 * h, v);
-            tcgen05_wait_ld();
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              float o[4];
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int e = 32 * h + 4 * u + i;   // column inside the 64-wide chunk
-                float x = scale * __uint_as_float(v[4 * u + i]);
-                if (e == row - col0) x += args.diag;
-                o[i] = __bfloat162float(__float2bfloat16_rn(x));
-              }
-              if (w_row != nullptr && colh + 4 * u < args.N) {
-                wv[u].x = fmaf(args.upd_alpha, o[0], wv[u].x);
-                wv[u].y = fmaf(args.upd_alpha, o[1], wv[u].y);
-                wv[u].z = fmaf(args.upd_alpha, o[2], wv[u].z);
-                wv[u].w = fmaf(args.upd_alpha, o[3], wv[u].w);
-                __stcs(wp + u, wv[u]);
-              }
-            }
-          } else {
-            uint4 wv[4];
-            uint4* wp = reinterpret_cast<uint4*>(w_row + static_cast<long long>(colh) * 2);
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-              if (w_row != nullptr && colh + 8 * u < args.N) wv[u] = __ldcs(wp + u);
-            tcgen05_ld_32x32b_x32(t_base + c * 64 + 32 * h, v);
-            tcgen05_wait_ld();
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&wv[u]);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int e = 32 * h + 8 * u + 2 * i;
-                float x0 = scale * __uint_as_float(v[8 * u + 2 * i]);
-                float x1 = scale * __uint_as_float(v[8 * u + 2 * i + 1]);
-                if (e == row - col0) x0 += args.diag;
-                if (e + 1 == row - col0) x1 += args.diag;
-                const float2 o = __bfloat1622float2(__floats2bfloat162_rn(x0, x1));
-                const float2 w = __bfloat1622float2(wh[i]);
-                wh[i] = __floats2bfloat162_rn(fmaf(args.upd_alpha, o.x, w.x), fmaf(args.upd_alpha, o.y, w.y));
-              }
-              if (w_row != nullptr && colh + 8 * u < args.N) __stcs(wp + u, wv[u]);
-            }
-          }
-        }
-      }
-#pragma unroll 1
-      for (int c = half; !UPD && c < BN / 64; c += 2) {
+      for (int c = half; c < BN / 64; c += 2) {
         const int col0 = n0 + c * 64;
         if (col0 >= args.N || row0 >= args.M) break;  // uniform across the warp
         uint32_t v[64];
@@ -700,17 +475,75 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
             oh[i] = __floats2bfloat162_rn(x0, x1);
           }
         }
-        if (lane == 0) bulk_wait_read_0();  // this warp's previous store has left the buffer
+        if (!UPD && lane == 0) bulk_wait_read_0();  // this warp's previous store has left the buffer
         __syncwarp();
         // 128-byte swizzle: 16-byte unit q of row r lives at unit q ^ (r & 7)
         uint8_t* rowp = my_buf + lane * 128;
 #pragma unroll
         for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) << 4)) = ov[q];
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_3d(&map_d, my_buf_addr, col0, row0, b);
-          bulk_commit();
+        if (!UPD) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&map_d, my_buf_addr, col0, row0, b);
+            bulk_commit();
+          }
+        } else {
+          // The piece (32 rows x 64 columns of bf16, the value the plain epilogue stores) is read back row
+          // by row so that the weights are touched in whole 128-byte lines: eight lanes per row, four rows
+          // per pass.  W <- fma(alpha, piece, W), one rounding to the weights' type.
+          __syncwarp();
+          const int q = lane & 7;
+          const int col = col0 + 8 * q;
+          uint4 pv[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + (lane >> 3);
+            pv[i] = *reinterpret_cast<const uint4*>(my_buf + r * 128 + ((q ^ (r & 7)) << 4));
+          }
+          __syncwarp();                                  // the buffer may be overwritten by the next chunk
+          if (col < args.N) {
+            if (args.upd_f32) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int grow = row0 + 4 * i + (lane >> 3);
+                if (grow >= args.M) break;
+                float4* wp = reinterpret_cast<float4*>(w_base + (static_cast<long long>(grow) * args.N + col) * 4);
+                float4 w0 = __ldcs(wp), w1 = __ldcs(wp + 1);
+                const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&pv[i]);
+                const float2 o0 = __bfloat1622float2(oh[0]), o1 = __bfloat1622float2(oh[1]);
+                const float2 o2 = __bfloat1622float2(oh[2]), o3 = __bfloat1622float2(oh[3]);
+                w0.x = fmaf(args.upd_alpha, o0.x, w0.x); w0.y = fmaf(args.upd_alpha, o0.y, w0.y);
+                w0.z = fmaf(args.upd_alpha, o1.x, w0.z); w0.w = fmaf(args.upd_alpha, o1.y, w0.w);
+                w1.x = fmaf(args.upd_alpha, o2.x, w1.x); w1.y = fmaf(args.upd_alpha, o2.y, w1.y);
+                w1.z = fmaf(args.upd_alpha, o3.x, w1.z); w1.w = fmaf(args.upd_alpha, o3.y, w1.w);
+                __stcs(wp, w0);
+                __stcs(wp + 1, w1);
+              }
+            } else {
+              uint4 wv[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {              // all eight loads in flight before the first use
+                const int grow = row0 + 4 * i + (lane >> 3);
+                if (grow < args.M)
+                  wv[i] = __ldcs(reinterpret_cast<const uint4*>(w_base + (static_cast<long long>(grow) * args.N + col) * 2));
+              }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int grow = row0 + 4 * i + (lane >> 3);
+                if (grow >= args.M) break;
+                const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&pv[i]);
+                __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&wv[i]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 o = __bfloat1622float2(oh[j]);
+                  const float2 w = __bfloat1622float2(wh[j]);
+                  wh[j] = __floats2bfloat162_rn(fmaf(args.upd_alpha, o.x, w.x), fmaf(args.upd_alpha, o.y, w.y));
+                }
+                __stcs(reinterpret_cast<uint4*>(w_base + (static_cast<long long>(grow) * args.N + col) * 2), wv[i]);
+              }
+            }
+          }
         }
       }
       tcgen05_fence_before();

@@ -117,7 +117,7 @@ int gemm_simt(const GemmCall& g, cudaStream_t st) {
 namespace {
 
 int gemm_dispatch(int backend, const GemmCall& g, int32_t* status, cudaStream_t st) {
-  if (backend == MMB_NS_TCGEN05) return gemm_tcgen05(g, status, st);
+  if (backend == MMB_NS_TCGEN05 || backend == MMB_NS_TCGEN05_MULTI) return gemm_tcgen05(g, status, st);
   if (backend == MMB_NS_SIMT) return gemm_simt(g, st);
   return fail(MMB_ERR_INVALID, "unknown Newton-Schulz backend %d", backend);
 }
@@ -243,7 +243,7 @@ int newton_schulz_impl(const char* who, const void* x_dev, void* out_dev, const 
   const NsLayout l = ns_layout(batch, rows, cols);
   MMB_REQUIRE(workspace_bytes >= static_cast<int64_t>(l.total), "%s: workspace %lld < %lld bytes", who,
               (long long)workspace_bytes, (long long)l.total);
-  if (backend == MMB_NS_TCGEN05)
+  if (backend == MMB_NS_TCGEN05 || backend == MMB_NS_TCGEN05_MULTI)
     MMB_REQUIRE(rows % 8 == 0 && cols % 8 == 0, "%s: tensor-core path needs rows, cols multiples of 8", who);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t* ws = static_cast<uint8_t*>(workspace_dev);
@@ -254,7 +254,7 @@ int newton_schulz_impl(const char* who, const void* x_dev, void* out_dev, const 
   float* inv = reinterpret_cast<float*>(ws + l.inv);
   float* sumsq = reinterpret_cast<float*>(ws + l.sumsq);
   int* sched = nullptr;
-  if (backend == MMB_NS_TCGEN05 && gemm_schedule_dynamic()) {
+  if ((backend == MMB_NS_TCGEN05 || backend == MMB_NS_TCGEN05_MULTI) && gemm_schedule_dynamic()) {
     sched = reinterpret_cast<int*>(ws + l.sched);
     MMB_CUDA_CHECK(cudaMemsetAsync(sched, 0, 2 * sizeof(int), st));  // each launch leaves them at zero again
   }
@@ -277,6 +277,9 @@ int newton_schulz_impl(const char* who, const void* x_dev, void* out_dev, const 
   const bool tall = rows > cols;
   const int m = tall ? cols : rows;
   const int n = tall ? rows : cols;
+  if (backend == MMB_NS_TCGEN05 && ns_onchip_fits(rows, cols))   // the whole iteration in one launch, on chip
+    return ns_onchip(x_dev, out_dev, inv, batch, rows, cols, beta, kappa, c, w_ptrs, w_f32, alpha, status_dev, st);
+  if (backend == MMB_NS_TCGEN05_MULTI) backend = MMB_NS_TCGEN05;
   const __nv_bfloat16* cur = static_cast<const __nv_bfloat16*>(x_dev);
   const bool fuse_update = w_ptrs != nullptr && backend == MMB_NS_TCGEN05;
   for (int it = 0; it < NS_ITERS; ++it) {

@@ -375,8 +375,6 @@ class ShardedMonarchMuon:
         s_red, s_bc = self._streams
         esz = self.g_arena.element_size()
         nchunks = len(self.plan.chunks)
-        if self._copied is not None:
-            main.wait_event(self._copied[-1])          # peers read this rank's arena: all of it must have landed
         self._fence()                                  # every rank's gradients are in its arena
         s_red.wait_stream(main)
         s_bc.wait_stream(main)
@@ -384,6 +382,11 @@ class ShardedMonarchMuon:
         with torch.cuda.stream(s_red):
             for k in range(nchunks):
                 ch = self.plan.chunks[k]
+                if self._copied is not None:
+                    # gradients arriving from the host: a chunk may be reduced once every rank's copy of that
+                    # chunk has landed - one more fence per chunk, on the reduction stream
+                    s_red.wait_event(self._copied[k])
+                    self._fence()
                 lo = ch.offset + self.rank * ch.shard_elems
                 _lib.check(lib.mmb_multimem_reduce_bf16(self._mc_g + lo * esz,
                                                         self.g_own[self.own_offset[k]:].data_ptr(),

@@ -437,3 +437,52 @@ def test_reciprocal_quotient_equals_the_division_instruction_on_many_elements(mm
         assert torch.equal(scales.view(torch.int32), want["scale_m"].view(torch.int32)), step
         assert torch.equal(codes, want["m"].view(torch.uint8)), step
         state = mm["fp8"].dequantize(want, "m", True, codec="absmax")
+
+
+ONCHIP_SHAPES = [(3, 128, 128), (2, 344, 128), (2, 128, 344), (300, 128, 128), (5, 96, 200), (4, 128, 384),
+                 (3, 384, 128), (7, 200, 72)]
+
+
+@pytest.mark.parametrize("shape", ONCHIP_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_onchip_newton_schulz_matches_the_multi_launch_path_and_the_oracle(mm, shape):
+    """Blocks whose short side is at most 128 (and long side at most 384) run all five iterations in one
+    launch with X, Ah and Pp resident in shared and tensor memory.  Same operands, same roundings as the
+    fifteen-launch path: the results must agree to bf16 rounding noise (the order of the K = 16 partial
+    products inside an accumulator may differ) and meet the same bounds against the CPU oracle; one launch
+    instead of seventeen; repeated calls and more blocks than SMs give identical bits; the fused weight
+    update equals the two-kernel form bit for bit."""
+    from oracle import muon_oracle
+    L = mm["lib"]
+    g = torch.Generator().manual_seed(sum(shape) + 3)
+    x = torch.randn(shape, generator=g).bfloat16()
+    xd = x.cuda()
+    n0 = L.launch_count()
+    got = mm["ns"].newton_schulz_batched(xd, backend=L.NS_TCGEN05)
+    launches = L.launch_count() - n0
+    assert L.read_status(xd.device) == 0
+    assert launches == 3, launches                       # block norms, their reciprocals, the on-chip kernel
+    multi = mm["ns"].newton_schulz_batched(xd, backend=L.NS_TCGEN05_MULTI)
+    assert L.read_status(xd.device) == 0
+    assert torch.isfinite(got).all()
+    assert relf(got, multi) < 4e-3, relf(got, multi)
+    if shape[0] <= 8:
+        ref32 = muon_oracle.newton_schulz(x.float())
+        ref16 = muon_oracle.newton_schulz(x)
+        e_ref = relf(ref16, ref32)
+        assert relf(got, ref32) <= max(NS_SLACK_VS_FP32 * e_ref, 1e-2)
+        assert relf(got, ref16) <= max(NS_SLACK_VS_BF16_ORACLE * e_ref, 1.5e-2)
+    again = mm["ns"].newton_schulz_batched(xd, backend=L.NS_TCGEN05)
+    assert torch.equal(got, again)
+    # fused update on scattered blocks == result stored, then the update kernel
+    batch, rows, cols = shape
+    for wdtype in (torch.bfloat16, torch.float32):
+        w = (0.02 * torch.randn(shape, generator=g)).to(wdtype).cuda()
+        want = w.clone()
+        alpha = -0.02 * (rows / cols) ** 0.5
+        seg = (L.UpdateSeg * 1)()
+        seg[0].weight, seg[0].ortho, seg[0].numel = want.data_ptr(), got.data_ptr(), want.numel()
+        L.check(L.load().mmb_muon_update(seg, 1, L.dtype_code(wdtype), alpha, L.stream_ptr()))
+        ptrs = torch.tensor([w.data_ptr() + k * rows * cols * w.element_size() for k in range(batch)], dtype=torch.int64).cuda()
+        mm["ns"].newton_schulz_update(xd, ptrs, wdtype, alpha, backend=L.NS_TCGEN05)
+        assert L.read_status(xd.device) == 0
+        assert torch.equal(w, want), wdtype

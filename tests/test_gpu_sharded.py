@@ -53,6 +53,8 @@ torch.cuda.synchronize()
 ok = all(torch.equal(a.data, b.data) for a, b in zip(muon + adamw, smuon + sadamw))
 flag = torch.tensor([1 if ok else 0], device=dev); dist.all_reduce(flag, op=dist.ReduceOp.MIN)
 if rank == 0: print("SHARDED_EQUALS_SERIAL" if int(flag) == 1 else "SHARDED_DIFFERS")
+del opt, host                       # no rank leaves while another may still use the shared mappings
+torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
 dist.destroy_process_group()
 '''
 
