@@ -473,6 +473,7 @@ def main():
         release_workspaces()
         torch.cuda.empty_cache()
         sub["isolated_ns"] = measure_isolated_ns(dev, 4, 128, 10, 3)
+        sub["small_block_ns"] = measure_small_block_ns(dev, 20, 5)
         sub["isolated_fp8_1.6e9"] = measure_isolated_fp8(dev, 1_600_000_000, "fp8_absmax", args.fp8_div, 20, 3)
         sub["isolated_fp8_2558525440"] = measure_isolated_fp8(dev, 2_558_525_440, "fp8_absmax", args.fp8_div, 20, 3)
         release_workspaces()
@@ -660,6 +661,29 @@ def measure_isolated_ns(dev, nblocks: int, ns_blocks: int, steps: int, warmup: i
             "roofline": {"bound": "tensor", "achieved": ach, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": ach / pk["bf16_tflops"], "peak_kind": f"{pk['source']}, burst bf16 GEMM", "traffic": None},
             "clocks": sampler.stop(tb, te)}
+
+
+def measure_small_block_ns(dev, steps: int, warmup: int) -> dict:
+    """Newton-Schulz on the block set of the small plumbing model (d_model 256, 4 layers, 2-block Monarch:
+    88 blocks of 128x128, 16 of 344x128, 8 of 128x344), where every block fits one SM: the one-launch
+    on-chip kernel beside the fifteen-launch path on the same inputs."""
+    from monarch_muon_b200 import _lib, newton_schulz_batched
+    gen = torch.Generator(device=dev).manual_seed(7)
+    sets = [(88, 128, 128), (16, 344, 128), (8, 128, 344)]
+    xs = [torch.empty(s, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=gen) for s in sets]
+    outs = [torch.empty_like(x) for x in xs]
+    res = {"workload": "Newton-Schulz on " + ", ".join(f"{s[0]}x{s[1]}x{s[2]}" for s in sets) + " bf16 blocks"}
+    for name, backend in (("one_launch_on_chip", _lib.NS_TCGEN05), ("fifteen_launches", _lib.NS_TCGEN05_MULTI)):
+        def fn():
+            for x, o in zip(xs, outs):
+                newton_schulz_batched(x, out=o, backend=backend)
+        l0 = _lib.launch_count()
+        fn()
+        per_call = _lib.launch_count() - l0
+        ms, _, _ = _timed(fn, steps, warmup)
+        res[name] = {"us": ms * 1e3, "kernel_launches": per_call}
+    res["speedup"] = res["fifteen_launches"]["us"] / res["one_launch_on_chip"]["us"]
+    return res
 
 
 def measure_isolated_fp8(dev, n: int, state_format: str, div: str, steps: int, warmup: int) -> dict:

@@ -113,9 +113,11 @@ def load():
     global _lib
     with _lock:
         if _lib is None:
-            path = _build.LIB_PATH
-            if not os.path.exists(path) or os.environ.get("MMB_REBUILD") == "1":
-                path = _build.build()
+            path = os.environ.get("MMB_LIBRARY")          # a prebuilt library elsewhere (must export the same ABI)
+            if not path:
+                path = _build.LIB_PATH
+                if not os.path.exists(path) or os.environ.get("MMB_REBUILD") == "1":
+                    path = _build.build()
             lib = C.CDLL(path)
             for name, (res, args) in SYMBOLS.items():
                 fn = getattr(lib, name)          # AttributeError if the symbol is missing

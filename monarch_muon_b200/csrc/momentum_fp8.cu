@@ -222,6 +222,99 @@ __device__ __forceinline__ float f32_state_unit(const SegDev& sg, long long e0, 
   return ss;
 }
 
+// FP8 absmax state, aligned pointers, full groups: the judged kernel.  Two groups of loads in flight per
+// lane; the arithmetic works on pairs of elements with the packed fp32 instructions (same bits as the
+// scalar ones, half the issue slots).  m = rn(beta * rn(code * scale)) + g, quantised with
+// scale' = (absmax + 1e-20) / 448 and code' = cvt.rn.satfinite.e4m3(m / scale').  Returns this lane's
+// share of sum(m^2).
+template <typename GradT, int DIV>
+__device__ __forceinline__ float fp8_absmax_unit(const SegDev& sg, long long e0, int ngroups, int grp_in_warp, int sub,
+                                                 float beta, float grad_scale) {
+  const bool scaled = grad_scale != 1.0f;
+  const float2 beta2 = make_float2(beta, beta), gs2 = make_float2(grad_scale, grad_scale);
+  float2 ss2 = make_float2(0.0f, 0.0f);
+  RawGroup<GradT> cur, nxt;
+  bool cur_ok = grp_in_warp < ngroups;
+  if (cur_ok) load_raw<MMB_STATE_FP8_ABSMAX, GradT>(cur, sg, e0 + static_cast<long long>(grp_in_warp) * GROUP + sub * ELEMS_PER_LANE);
+  for (int g0 = 0; g0 < ngroups; g0 += 4) {
+    const int gi_next = g0 + 4 + grp_in_warp;
+    const bool nxt_ok = gi_next < ngroups;
+    if (nxt_ok) load_raw<MMB_STATE_FP8_ABSMAX, GradT>(nxt, sg, e0 + static_cast<long long>(gi_next) * GROUP + sub * ELEMS_PER_LANE);
+    const long long at = e0 + static_cast<long long>(g0 + grp_in_warp) * GROUP + sub * ELEMS_PER_LANE;
+    float2 m[ELEMS_PER_LANE / 2];
+    float amax = 0.0f;
+    if (cur_ok) {
+      const uint16_t* h = reinterpret_cast<const uint16_t*>(&cur.codes);
+      const float2 sc2 = make_float2(cur.scale, cur.scale);
+#pragma unroll
+      for (int p = 0; p < ELEMS_PER_LANE / 2; ++p) {
+        float2 g;
+        if (sizeof(GradT) == 2) {
+          const uint32_t w = reinterpret_cast<const uint32_t*>(cur.grad)[p];
+          g = make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));   // bf16 -> fp32 is a shift
+        } else {
+          g = reinterpret_cast<const float2*>(cur.grad)[p];
+        }
+        if (scaled) {  // like grad.mul_(scale) on the stored gradient: rounded to the gradient's type
+          g = mul2(g, gs2);
+          if (sizeof(GradT) == 2) g = __bfloat1622float2(__floats2bfloat162_rn(g.x, g.y));
+        }
+        const float2 dec = mul2(e4m3x2_to_float2(h[p]), sc2);
+        const float2 bm = mul2(beta2, dec);
+        // The sum stays two scalar add.rn: the assembler was seen to contract a packed multiply followed by a
+        // packed add into one fused multiply-add, which would drop the reference's second rounding
+        // (buf.mul_(beta) then buf.add_(grad)); scalar add.rn is never contracted.
+        const float2 t = make_float2(__fadd_rn(bm.x, g.x), __fadd_rn(bm.y, g.y));
+        m[p] = t;
+        amax = fmaxf(amax, fmaxf(fabsf(t.x), fabsf(t.y)));
+      }
+    } else {
+#pragma unroll
+      for (int p = 0; p < ELEMS_PER_LANE / 2; ++p) m[p] = make_float2(0.0f, 0.0f);
+    }
+    amax = group_max(amax);
+    const float s_new = fdiv<DIV>(__fadd_rn(amax, 1e-20f), 448.0f);
+    if (cur_ok) {
+      uint4 cv;
+      uint16_t* ch = reinterpret_cast<uint16_t*>(&cv);
+      if (DIV == MMB_DIV_IEEE && markstein_ok(s_new)) {   // uniform over the group
+        const float r = __frcp_rn(s_new);
+#pragma unroll
+        for (int p = 0; p < ELEMS_PER_LANE / 2; ++p)
+          ch[p] = float2_to_e4m3x2(quotient_markstein(m[p].x, s_new, r), quotient_markstein(m[p].y, s_new, r));
+      } else if (DIV == MMB_DIV_FULL && finite_normal(s_new)) {  // uniform over the group
+        const float r = rcp_approx(s_new);                        // div.full.f32(m, s) == m * rcp.approx(s)
+        const float2 r2 = make_float2(r, r);
+#pragma unroll
+        for (int p = 0; p < ELEMS_PER_LANE / 2; ++p) {
+          const float2 q = mul2(m[p], r2);
+          ch[p] = float2_to_e4m3x2(q.x, q.y);
+        }
+      } else {
+#pragma unroll
+        for (int p = 0; p < ELEMS_PER_LANE / 2; ++p)
+          ch[p] = float2_to_e4m3x2(fdiv<DIV>(m[p].x, s_new), fdiv<DIV>(m[p].y, s_new));
+      }
+      *reinterpret_cast<uint4*>(static_cast<uint8_t*>(sg.state) + at) = cv;
+      if (sub == 0) sg.scale[at / GROUP] = s_new;
+#pragma unroll
+      for (int p = 0; p < ELEMS_PER_LANE / 2; ++p) ss2 = fma2(m[p], m[p], ss2);
+      if (sg.m_out != nullptr) {
+        uint4 mv[2];
+        __nv_bfloat162* mh = reinterpret_cast<__nv_bfloat162*>(mv);
+#pragma unroll
+        for (int p = 0; p < ELEMS_PER_LANE / 2; ++p) mh[p] = __floats2bfloat162_rn(m[p].x, m[p].y);
+        uint4* mp = reinterpret_cast<uint4*>(sg.m_out + at);
+        mp[0] = mv[0];
+        mp[1] = mv[1];
+      }
+    }
+    cur = nxt;
+    cur_ok = nxt_ok;
+  }
+  return ss2.x + ss2.y;
+}
+
 // -------------------------------------------------------------- fused kernel
 // ALL_FAST: the host has checked that every unit of the launch qualifies for the
 // fast path, so the general path is compiled out (fewer registers, more warps).
@@ -264,6 +357,8 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
       ss = bf16_state_unit<GradT>(sg, e0, ngroups, grp_in_warp, sub, beta, grad_scale);
     } else if (FORMAT == MMB_STATE_F32 && fast) {
       ss = f32_state_unit<GradT>(sg, e0, ngroups, grp_in_warp, sub, beta, grad_scale);
+    } else if (FORMAT == MMB_STATE_FP8_ABSMAX && fast) {
+      ss = fp8_absmax_unit<GradT, DIV>(sg, e0, ngroups, grp_in_warp, sub, beta, grad_scale);
     } else if (fast) {
       RawGroup<GradT> cur, nxt;
       bool cur_ok = grp_in_warp < ngroups;
