@@ -44,18 +44,22 @@ extern "C" {
 #define MMB_STATE_BF16 2       /* plain buffer, two roundings per step         */
 #define MMB_STATE_F32 3
 
-/* division used by the FP8 quantiser: IEEE round-to-nearest (matches a CPU
- * restatement bit for bit) or the GPU's approximate full-range division that
- * the reference's Triton build emits for `/`. */
+/* Arithmetic of the FP8 quantisers.
+ *   MMB_DIV_FULL  (what the Python layer passes by default) the GPU instructions the reference's Triton
+ *                 kernels compile to: div.full.f32 for `/`, sqrt.approx.ftz.f32, library powf / log2f.  The
+ *                 absmax codec then equals the reference's kernel bit for bit on the same GPU; the
+ *                 range-expansion codec equals it in expand_ and sqrt_minmax_ and to a few ulp in scale_
+ *                 (the two toolchains compile powf differently).
+ *   MMB_DIV_IEEE  IEEE round-to-nearest division (formed exactly from a reciprocal and one correction step):
+ *                 equals a CPU restatement bit for bit.  For the range-expansion format it also forms pow()
+ *                 as 2^(y*log2 x) on the special-function unit when the exponent is at most 4 (within
+ *                 ~1e-6 of the library powf: about 80 codes per million differ from the reference's).
+ *   MMB_DIV_IEEE_STRICT  IEEE results through the compiler's division and the library powf everywhere:
+ *                 slower, same bits as MMB_DIV_IEEE for the absmax format; exists to verify the fast exact
+ *                 quotient against. */
 #define MMB_DIV_IEEE 0
 #define MMB_DIV_FULL 1
-#define MMB_DIV_IEEE_STRICT 2 /* IEEE results through the compiler's division everywhere: slower, same bits
-                                 as MMB_DIV_IEEE for the absmax format; exists to verify the fast exact
-                                 quotient against.  For the range-expansion format MMB_DIV_IEEE also forms
-                                 pow() as 2^(y*log2 x) on the special-function unit when the exponent is at
-                                 most 4 (result within ~1e-6 of the library powf: about one E4M3 code in
-                                 10^5 moves by one step), while STRICT and FULL call the library powf, as
-                                 the reference's kernels do */
+#define MMB_DIV_IEEE_STRICT 2
 
 /* Newton-Schulz GEMM back ends */
 #define MMB_NS_TCGEN05 0 /* tcgen05.mma + TMEM + TMA (the product).  Blocks with 64 < min(rows, cols) <= 128

@@ -11,29 +11,8 @@ constexpr int THREADS = 256;
 constexpr int MAX_SEG = 128;
 constexpr int VEC = 8;  // elements per thread per step
 
-template <typename T>
-__device__ __forceinline__ float ld(const T* p);
-template <>
-__device__ __forceinline__ float ld<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
-template <>
-__device__ __forceinline__ float ld<float>(const float* p) { return *p; }
-template <typename T>
-__device__ __forceinline__ void st(T* p, float v);
-template <>
-__device__ __forceinline__ void st<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
-template <>
-__device__ __forceinline__ void st<float>(float* p, float v) { *p = v; }
-
-// Round to the tensor's storage type and come back: models one torch op.
-template <typename T>
-__device__ __forceinline__ float rd(float v);
-template <>
-__device__ __forceinline__ float rd<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-template <>
-__device__ __forceinline__ float rd<float>(float v) { return v; }
-
-// The same rounding for two values at once: one packed conversion instead of two (the conversion unit is
-// the busiest pipe of the AdamW kernel).
+// Round two values to the tensor's storage type and come back (models one torch op on each): one packed
+// conversion instead of two (the conversion unit is the busiest pipe of the AdamW kernel).
 template <typename T>
 __device__ __forceinline__ void rd2(float& a, float& b);
 template <>

@@ -20,10 +20,18 @@ sft_oracle    the fine-tuning optimizer on fp32 master weights
               (finetune/sft_optimizer.py), pinned bit-exactly to the
               reference's own run.
 
-Parity pin: the restatement is checked in tests/test_oracle_golden.py against
-vectors produced by importing and running the reference's own Python on CPU
-(tests/golden/make_golden.py).  The expansion codec could not be executed on
-CPU (its Triton kernel needs libdevice.pow), so that codec is
-"parity unpinned": it follows the reference source line by line but no
-reference output exists to compare with.
+make_ref      stages the reference project's own files, unmodified, under the
+              git-ignored oracle/_ref/ (with a manifest of hashes).
+ref_loader    imports those staged modules (the reference's Triton FP8 kernels,
+              its optimizer classes, its training program) for the GPU parity
+              tests and the benchmark's reference arms.
+
+Parity pins.  (1) The restatement is checked in tests/test_oracle_golden.py
+against vectors produced by importing and running the reference's own Python on
+CPU (tests/golden/make_golden.py).  The expansion codec could not be executed on
+CPU (its Triton kernel needs libdevice.pow), so fp8_oracle's restatement of that
+codec has no CPU pin.  (2) On a GPU the reference itself is the arbiter:
+tests/test_gpu_reference.py compares the CUDA kernels with the reference's
+kernels and classes run from oracle/_ref/ - absmax codec bit for bit, expansion
+codec to its measured residual.
 """

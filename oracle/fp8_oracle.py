@@ -10,14 +10,19 @@ absmax      one fp32 scale per group.
                         (triton_kernels.py:51-63)
 expansion   COAT dynamic-range expansion, three fp32 side values per group
             (pretrain/src/models/monarch/coat_state_muon.py:22-43 dequantise,
-            :46-91 quantise).  PARITY UNPINNED: the reference kernel cannot be
-            executed without a GPU, so no reference output pins this part.
+            :46-91 quantise).  PARITY UNPINNED ON THE CPU: the reference kernel
+            cannot be executed without a GPU (the Triton interpreter has no
+            libdevice.pow), so no reference output pins this restatement.  It is
+            not the arbiter of the CUDA expansion codec: that is the reference's
+            own kernel, JIT-compiled and run on the GPU from the staged copy
+            under oracle/_ref/ (tests/test_gpu_reference.py).
 
 Divisions are IEEE round-to-nearest here.  The reference's Triton build
 lowers `/` to the GPU's approximate full-range division, whose last-bit
 behaviour is hardware defined and cannot be restated on a CPU; the CUDA
-kernels therefore offer both divisions and are bit-compared with this file
-in the IEEE mode.
+kernels offer both: their default issues the GPU instruction and is
+bit-compared with the reference's kernels on the GPU, their IEEE mode is
+bit-compared with this file.
 """
 from __future__ import annotations
 

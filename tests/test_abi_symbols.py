@@ -71,3 +71,49 @@ def test_calls_validate_arguments_without_a_gpu():
     assert rc == -1
     assert lib.mmb_ns_workspace_bytes(4, 1024, 1024) > 4 * 1024 * 1024 * 2 * 4
     assert lib.mmb_momentum_static_max_floats() == 1 << 20
+
+
+def test_launch_options_are_validated_and_per_thread():
+    """mmb_set_stream_ctas_per_sm sizes grids whose reductions have scratch for 32 CTAs per SM: larger
+    values are refused (they would index past that scratch), 0..32 accepted.  The options act on the
+    calling thread only."""
+    import threading
+    from monarch_muon_b200 import _lib
+    lib = _lib.load()
+    assert lib.mmb_set_stream_ctas_per_sm(33) == -1 and b"outside 0..32" in lib.mmb_last_error()
+    assert lib.mmb_set_stream_ctas_per_sm(-1) == -1
+    assert lib.mmb_set_stream_ctas_per_sm(32) == 0 and lib.mmb_set_stream_ctas_per_sm(0) == 0
+    with pytest.raises(RuntimeError):
+        _lib.set_stream_ctas_per_sm(64)
+    seen = {}
+
+    def other():
+        # a fresh thread starts from the defaults whatever this thread has set
+        with _lib.launch_options(stream_ctas_per_sm=1, dynamic_schedule=True):
+            seen["inside"] = True
+        seen["done"] = True
+    with _lib.launch_options(stream_ctas_per_sm=2):
+        t = threading.Thread(target=other)
+        t.start()
+        t.join()
+    assert seen == {"inside": True, "done": True}
+    # the context manager restores the defaults even when the body raises
+    with pytest.raises(ZeroDivisionError):
+        with _lib.launch_options(sm_limit=100, dynamic_schedule=True, stream_ctas_per_sm=1):
+            1 / 0
+    assert lib.mmb_wait_probe(0, None, None) == -1               # argument check comes before any launch
+
+
+def test_staged_reference_is_unmodified():
+    """oracle/_ref/ (when present) holds the reference's files byte for byte: every file still has the hash
+    recorded when it was staged, and the files the GPU tests and the benchmark import are there."""
+    from oracle import make_ref, ref_loader
+    if not ref_loader.available():
+        pytest.skip("oracle/_ref/ not staged (python oracle/make_ref.py <reference checkout>)")
+    assert make_ref.verify()
+    for rel in ("pretrain/src/models/monarch/coat_state_muon.py", "pretrain/src/models/monarch/monarch_muon.py",
+                "membench/src/models/monarch/monarch_muon.py", "pretrain/third_party/coat/optimizer/triton_kernels.py",
+                "pretrain/src/main.py", "pretrain/src/optim/base.py", "pretrain/tests/test_coat_state_muon.py"):
+        assert os.path.exists(os.path.join(ref_loader.ROOT, rel)), rel
+    twin = ref_loader.membench_twin()
+    assert hasattr(twin, "MonarchMuonOptimizer") and hasattr(twin, "_newton_schulz_batched")

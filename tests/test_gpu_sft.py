@@ -182,3 +182,31 @@ def test_parameter_groups_split():
     assert groups[1]["lr"] == 3e-5 and len(groups[1]["params"]) == 5
     only = parameter_groups(m, "adamw", 1e-3, {})
     assert len(only) == 1 and len(only[0]["params"]) == 6
+
+
+def test_strided_gradients_are_read_through_a_copy_that_outlives_the_launch():
+    """A gradient that is not contiguous (here: the transpose of a contiguous tensor) is stepped through a
+    contiguous copy; the copy must stay alive until the kernels that read it have been launched.  Several
+    such parameters in one group, so that a freed copy would be handed to the next one: the result must
+    equal the step on contiguous gradients bit for bit."""
+    from monarch_muon_b200.sft import SFTOptimizer
+    gen = torch.Generator().manual_seed(31)
+    shapes = [(128, 256), (256, 128), (128, 256), (2, 128, 256)]
+    ws = [torch.randn(s, generator=gen).bfloat16() for s in shapes]
+    gs = [torch.randn(s, generator=gen).bfloat16() for s in shapes]
+    results = []
+    for strided in (False, True):
+        params = [torch.nn.Parameter(w.clone().cuda()) for w in ws]
+        opt = SFTOptimizer([{"params": params, "algorithm": "muon"}], lr=1e-2)
+        for step in range(2):
+            for p, g in zip(params, gs):
+                g = g.cuda()
+                if strided:
+                    g = g.transpose(-1, -2).contiguous().transpose(-1, -2)      # same values, strided layout
+                    assert not g.is_contiguous()
+                p.grad = g
+            opt.step()
+        torch.cuda.synchronize()
+        results.append([p.data.clone() for p in params])
+    for a, b in zip(*results):
+        assert torch.equal(a, b)

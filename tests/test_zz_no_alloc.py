@@ -6,7 +6,8 @@ loop where an allocation may stall or fail).  For them the momentum step exists
 in a second form whose scratch is a fixed array inside the library.  This test
 drives both forms through the C ABI on identical inputs, twice in a row, and
 requires identical bits in every output: E4M3 codes, fp32 scales, the bf16
-momentum and the per-block sums of squares.  It also checks the size limit.
+momentum and the per-block sums of squares; the same outputs are also held
+against the CPU oracle.  It also checks the size limit.
 
 The file name sorts last on purpose: a run that stops at the first failure has
 then already executed every other test.
@@ -54,6 +55,7 @@ def test_static_scratch_entry_matches_allocating_entry():
     ss_a = torch.zeros(nblocks, device=dev)
     ss_b = torch.zeros(nblocks, device=dev)
     stream = _lib.stream_ptr()
+    oracle_state = [(torch.zeros(n, dtype=torch.uint8), torch.zeros(n // 128)) for n in sizes]
     for call in range(2):                                   # two calls in a row share the built-in array
         grads = [(1e-3 * torch.randn(n, generator=gen)).bfloat16().to(dev) for n in sizes]
         segs_a, _ = _segments(_lib, grads, codes_a, scales_a, m_a, block)
@@ -74,6 +76,14 @@ def test_static_scratch_entry_matches_allocating_entry():
             bv = b.view(torch.int16) if b.dtype == torch.bfloat16 else b
             assert torch.equal(av, bv), f"outputs differ on call {call}"
         assert float(ss_b.min()) > 0.0
+        # and against the CPU oracle directly (IEEE division on both sides): codes, scales, bf16 momentum
+        from oracle import fp8_oracle
+        for k, g in enumerate(grads):
+            want = fp8_oracle.absmax_momentum_step(oracle_state[k][0], oracle_state[k][1], g.cpu(), 0.95)
+            oracle_state[k] = (want[0], want[1])
+            assert torch.equal(codes_b[k].cpu(), want[0]), f"codes differ from the oracle on call {call}"
+            assert torch.equal(scales_b[k].cpu().view(torch.int32), want[1].view(torch.int32))
+            assert torch.equal(m_b[k].cpu().view(torch.int16), want[3].view(torch.int16))
 
 
 def test_static_scratch_entry_refuses_oversized_tables():
