@@ -312,6 +312,8 @@ def main():
     ap.add_argument("--fp8-elems", type=int, default=1_600_000_000)
     ap.add_argument("--comm-sms", type=int, default=-1,
                     help="SMs left to the communication kernels during the sharded step (-1: the transport's default)")
+    ap.add_argument("--comm-ctas", type=int, default=-1,
+                    help="CTAs of each multicast kernel in the sharded step (-1: one per SM)")
     ap.add_argument("--comm", default="nccl", choices=["nccl", "multimem", "auto"],
                     help="transport of the sharded step: NCCL collectives, this library's NVSwitch multicast kernels, "
                          "or auto (multicast from four GPUs on where the fabric provides it)")
@@ -333,6 +335,8 @@ def main():
                          "bit-exact with them for the absmax codec), ieee (bit-exact with the CPU oracle)")
     ap.add_argument("--fused-update", type=int, default=1, choices=[0, 1],
                     help="weight update in the last Newton-Schulz GEMM's epilogue (1, default) or as its own kernel (0)")
+    ap.add_argument("--dependent-launch", type=int, default=1, choices=[0, 1],
+                    help="Newton-Schulz GEMMs launched with programmatic stream serialisation (1, the default) or plainly")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-subrecords", action="store_true",
                     help="leave out the extra measurements of the default line (isolated kernels, the reference's "
@@ -372,6 +376,8 @@ def main():
     from monarch_muon_b200 import MonarchMuonOptimizer, _lib
     if args.dynamic_schedule:
         _lib.set_gemm_schedule(True)
+    if not args.dependent_launch:
+        _lib.set_gemm_dependent_launch(False)
     if args.case == "gemm":
         return run_gemm_comparison(args, dev)
     if args.case == "adamw":

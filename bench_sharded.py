@@ -93,6 +93,7 @@ def run_sharded(args, rank, world, local_rank, config, metric):
     opt = ShardedMonarchMuon(muon, adamw, lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95),
                              adamw_weight_decay=0.1, adamw_eps=1e-8, n_chunks=args.chunks,
                              comm_sms=None if args.comm_sms < 0 else args.comm_sms,
+                             comm_ctas=None if args.comm_ctas < 0 else args.comm_ctas,
                              dynamic_schedule=args.dynamic_schedule != 0,
                              state_format="fp8_absmax", comm=args.comm, fp8_div=args.fp8_div)
     if parity.startswith("differs") and opt.comm == "multimem":

@@ -71,7 +71,7 @@ extern "C" {
 
 int mmb_version(void);
 const char* mmb_last_error(void);
-/* Launch options.  The three setters below act on the CALLING HOST THREAD only (like mmb_last_error and
+/* Launch options.  The four setters below act on the CALLING HOST THREAD only (like mmb_last_error and
  * mmb_set_device_grad_scale): they change how later calls of that thread size and schedule their kernels,
  * never what is computed.  Nothing else in the library is mutable state.
  *
@@ -87,6 +87,12 @@ int mmb_set_stream_ctas_per_sm(int n);
  * a pair whose SMs are shared with another kernel (a collective running beside the step) takes fewer tiles
  * instead of delaying the launch.  Results do not depend on the schedule. */
 int mmb_set_gemm_schedule(int dynamic);
+/* How the Newton-Schulz GEMMs follow one another on their stream (no counterpart in the reference).
+ * 1 (default): each GEMM is launched with programmatic stream serialisation; its CTAs may become resident
+ * and set up their barriers and tensor memory while the previous kernel of the stream is finishing, and
+ * wait (griddepcontrol.wait) for that kernel to complete before they touch global memory.  0: plain
+ * launches.  Results do not depend on it. */
+int mmb_set_gemm_dependent_launch(int on);
 /* Kernels launched by this library in this process so far. */
 int64_t mmb_launch_count(void);
 

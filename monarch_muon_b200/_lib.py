@@ -76,6 +76,7 @@ SYMBOLS = {
     "mmb_launch_count": (_i64, []),
     "mmb_set_sm_limit": (_i, [_i]),
     "mmb_set_gemm_schedule": (_i, [_i]),
+    "mmb_set_gemm_dependent_launch": (_i, [_i]),
     "mmb_set_stream_ctas_per_sm": (_i, [_i]),
     "mmb_momentum_scratch_floats": (_i64, [C.POINTER(MomentumSeg), _i]),
     "mmb_momentum_step": (_i, [C.POINTER(MomentumSeg), _i, _i, _i, _i, _f, _f, _i, _vp, _vp, _i64, _vp]),
@@ -196,6 +197,11 @@ def set_gemm_schedule(dynamic: bool) -> None:
     check(load().mmb_set_gemm_schedule(1 if dynamic else 0), "set_gemm_schedule")
 
 
+def set_gemm_dependent_launch(on: bool) -> None:
+    """Newton-Schulz GEMMs launched with programmatic stream serialisation (True, default) or plainly."""
+    check(load().mmb_set_gemm_dependent_launch(1 if on else 0), "set_gemm_dependent_launch")
+
+
 def set_sm_limit(n: int) -> None:
     """Size kernel grids for at most n SMs (0 = all)."""
     load().mmb_set_sm_limit(int(n))
@@ -209,8 +215,10 @@ class launch_options:
             ...launch kernels...
     """
 
-    def __init__(self, *, sm_limit: int = 0, dynamic_schedule: bool = False, stream_ctas_per_sm: int = 0):
+    def __init__(self, *, sm_limit: int = 0, dynamic_schedule: bool = False, stream_ctas_per_sm: int = 0,
+                 dependent_launch: bool = True):
         self.sm_limit, self.dynamic, self.ctas = int(sm_limit), bool(dynamic_schedule), int(stream_ctas_per_sm)
+        self.dependent = bool(dependent_launch)
 
     def __enter__(self):
         if self.sm_limit:
@@ -219,6 +227,8 @@ class launch_options:
             set_gemm_schedule(True)
         if self.ctas:
             set_stream_ctas_per_sm(self.ctas)
+        if not self.dependent:
+            set_gemm_dependent_launch(False)
         return self
 
     def __exit__(self, *exc):
@@ -228,4 +238,6 @@ class launch_options:
             set_gemm_schedule(False)
         if self.ctas:
             set_stream_ctas_per_sm(0)
+        if not self.dependent:
+            set_gemm_dependent_launch(True)
         return False

@@ -36,6 +36,10 @@ static thread_local int t_gemm_dynamic = 0;
 void set_gemm_schedule_dynamic(bool on) { t_gemm_dynamic = on ? 1 : 0; }
 bool gemm_schedule_dynamic() { return t_gemm_dynamic != 0; }
 
+static thread_local int t_gemm_dependent_launch = 1;
+void set_gemm_dependent_launch(bool on) { t_gemm_dependent_launch = on ? 1 : 0; }
+bool gemm_dependent_launch() { return t_gemm_dependent_launch != 0; }
+
 static thread_local int t_stream_ctas_per_sm = 0;
 // at most 32: scratch arrays of the reductions are sized for 32 CTAs per SM
 void set_stream_ctas_per_sm(int n) { t_stream_ctas_per_sm = n < 0 ? 0 : (n > 32 ? 32 : n); }
@@ -86,6 +90,11 @@ int mmb_set_stream_ctas_per_sm(int n) {
 
 int mmb_set_gemm_schedule(int dynamic) {
   mmb::set_gemm_schedule_dynamic(dynamic != 0);
+  return MMB_OK;
+}
+
+int mmb_set_gemm_dependent_launch(int on) {
+  mmb::set_gemm_dependent_launch(on != 0);
   return MMB_OK;
 }
 

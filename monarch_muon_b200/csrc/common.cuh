@@ -53,6 +53,11 @@ bool stream_kernels_share_sms();
 void set_gemm_schedule_dynamic(bool on);
 bool gemm_schedule_dynamic();
 
+// Newton-Schulz GEMMs are launched with programmatic stream serialisation (default) or plainly
+// (mmb_set_gemm_dependent_launch).
+void set_gemm_dependent_launch(bool on);
+bool gemm_dependent_launch();
+
 // Device scalar that the momentum and AdamW kernels multiply gradients by (mmb_set_device_grad_scale),
 // or null.  Thread local, like the error message.
 const float* device_grad_scale();

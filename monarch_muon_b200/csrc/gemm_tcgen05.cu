@@ -103,6 +103,7 @@ struct GemmArgs {
   float upd_alpha;
   int upd_f32;          // weights are fp32 (else bf16)
   long long wait_limit; // SM cycles a role may wait on a barrier before it gives up
+  int pdl;              // launched with programmatic stream serialisation: wait for the previous kernel here
 };
 
 // Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle (built in the MMA issue loop):
@@ -254,6 +255,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
   if (PAIR) cluster_sync();  // the peer's barriers exist before anything is signalled across
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (args.pdl) {
+    // Everything above touched only this CTA's shared and tensor memory, so it may run while the previous
+    // kernel of the stream is still finishing.  From here on global memory is read and written.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  }
 
   if (warp == 0 || warp >= FIRST_EXTRA_PRODUCER) {
     // ------------------------------------------------------ TMA producers
@@ -643,13 +650,15 @@ int launch(const CUtensorMap* maps, const GemmArgs& args, int grid, cudaStream_t
   cfg.blockDim = dim3(NUM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = PAIR ? 2 : 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = args.pdl ? 2 : 1;
   MMB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[2], maps[3], maps[4], args));
   count_launch();
   return MMB_OK;
@@ -727,6 +736,7 @@ int gemm_tcgen05(const GemmCall& g, int32_t* status, cudaStream_t st) {
   args.upd_alpha = g.upd_alpha;
   args.upd_f32 = g.upd_f32;
   args.wait_limit = WAIT_LIMIT_CYCLES;
+  args.pdl = gemm_dependent_launch() ? 1 : 0;
   const bool upd = g.upd_w != nullptr;
   if (upd) MMB_REQUIRE(!g.sym_out, "the fused weight update applies to a full (non-symmetric) result");
   const int sms = sm_count();

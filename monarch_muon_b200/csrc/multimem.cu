@@ -14,15 +14,20 @@
 // The two load opposite link directions, so a reduce of one chunk and a broadcast of another run side by
 // side at full rate, which ring collectives (both directions busy in each) cannot do.  The kernels hold no
 // flags and wait on nothing: ordering between ranks is the caller's (a collective on the stream before the
-// first reduce of a step and after its last broadcast).  Small grids on purpose: they are bound by the
-// links, not by the SMs, and run beside the Newton-Schulz GEMMs.
+// first reduce of a step and after its last broadcast).
+//
+// Small CTAs on purpose.  The kernels run beside the Newton-Schulz GEMMs, whose CTAs take an SM's shared
+// memory and 13 warps of 112 registers but leave 18,944 registers, 51 warp slots and a sliver of shared
+// memory unused.  A CTA of 256 threads at no more than 48 registers with no shared memory fits into that
+// remainder, so one communication CTA per SM shares the SM with a GEMM CTA instead of taking the SM (and,
+// for a two-CTA GEMM tile, its neighbour) away from the GEMM for as long as the transfer lasts.
 #include "common.cuh"
 
 namespace mmb {
 namespace {
 
-constexpr int MC_THREADS = 512;
-constexpr int MC_UNROLL = 8;  // 16-byte requests in flight per thread
+constexpr int MC_THREADS = 256;
+constexpr int MC_UNROLL = 4;  // 16-byte requests in flight per thread
 
 __device__ __forceinline__ uint4 mc_ld_reduce_bf16x8(const uint4* mc) {
   uint4 v;

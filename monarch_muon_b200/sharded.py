@@ -69,7 +69,10 @@ class ShardedMonarchMuon:
         that steps the owned views; defaults to MonarchMuonOptimizer (CUDA).
     comm : "nccl", "multimem" or "auto" (see the module text).
     comm_sms : SMs kept free of this library's compute kernels during the step,
-        for the communication kernels (default: 0 with NCCL, 16 with multimem).
+        for the communication kernels (default 0: NCCL's kernels take SMs from the
+        GEMMs as they come, the multicast kernels are small enough to share an SM
+        with a GEMM CTA).
+    comm_ctas : CTAs of each multicast kernel (default: one per SM).
     dynamic_schedule : let the Newton-Schulz GEMMs draw their tiles from a counter
         during the step, so that SMs taken by a communication kernel cost those
         SMs' share of the work instead of stalling a whole launch.
@@ -78,7 +81,7 @@ class ShardedMonarchMuon:
     def __init__(self, muon_params, adamw_params, *, process_group=None, lr: float = 5e-3, momentum: float = 0.95,
                  adamw_betas=(0.9, 0.95), adamw_weight_decay: float = 0.1, adamw_eps: float = 1e-8,
                  n_chunks: int = 4, average: bool = True, local_factory=None, second_group: bool = True,
-                 comm: str = "nccl", comm_sms: int | None = None, comm_ctas: int = 16,
+                 comm: str = "nccl", comm_sms: int | None = None, comm_ctas: int | None = None,
                  dynamic_schedule: bool = True, **local_kwargs):
         if not dist.is_initialized():
             raise RuntimeError("ShardedMonarchMuon needs an initialised torch.distributed process group")
@@ -107,7 +110,8 @@ class ShardedMonarchMuon:
             if (second_group and process_group is None) else process_group
         self.average = average
         self.dynamic_schedule = dynamic_schedule
-        self.comm_ctas = int(comm_ctas)
+        self.comm_ctas = int(comm_ctas) if comm_ctas is not None else (
+            torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 1)
         n = self.plan.total_elems
         # ---- arenas: symmetric memory when this library's multicast kernels move the data
         self.comm = "nccl"
@@ -125,7 +129,7 @@ class ShardedMonarchMuon:
             self.g_arena = torch.zeros(n, dtype=self.dtype, device=self.device)
         # SMs left free during the step so that communication kernels can run beside the persistent GEMMs
         # (which otherwise occupy every SM and serialise with them)
-        self.comm_sms = (16 if self.comm == "multimem" else 0) if comm_sms is None else int(comm_sms)
+        self.comm_sms = 0 if comm_sms is None else int(comm_sms)
         # reduced gradients of the owned shards, chunk after chunk (the gradient arena itself is left
         # untouched by the reduction, so it can keep accumulating or be reused)
         self.own_offset = []

@@ -202,6 +202,25 @@ def test_newton_schulz_with_fused_update_equals_two_kernels(mm, shape, backend, 
     del table
 
 
+def test_dependent_launch_does_not_change_the_result(mm):
+    """The GEMMs of one Newton-Schulz call follow one another with programmatic stream serialisation by
+    default (a kernel's CTAs set up while the previous kernel drains, then wait for it); launched plainly
+    they must give the same bits."""
+    L = mm["lib"]
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(6, 512, 1376, generator=g).to(torch.bfloat16).cuda()
+    be = L.NS_TCGEN05_MULTI
+    a = mm["ns"].newton_schulz_batched(x, backend=be).clone()
+    with L.launch_options(dependent_launch=False):
+        b = mm["ns"].newton_schulz_batched(x, backend=be).clone()
+    with L.launch_options(dependent_launch=False, dynamic_schedule=True):
+        c = mm["ns"].newton_schulz_batched(x, backend=be).clone()
+    with L.launch_options(dynamic_schedule=True):
+        d = mm["ns"].newton_schulz_batched(x, backend=be).clone()
+    assert L.read_status(x.device) == 0
+    assert torch.equal(a, b) and torch.equal(a, c) and torch.equal(a, d)
+
+
 def test_bounded_wait_expires_and_reports(mm):
     """A wait that nothing answers: one warp runs the GEMM's own bounded wait, with a limit of about a
     millisecond, on a barrier no one arrives at.  The kernel must return, the status word must hold the
