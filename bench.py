@@ -314,10 +314,13 @@ def main():
                     help="SMs left to the communication kernels during the sharded step (-1: the transport's default)")
     ap.add_argument("--comm-ctas", type=int, default=-1,
                     help="CTAs of each multicast kernel in the sharded step (-1: one per SM)")
-    ap.add_argument("--comm", default="nccl", choices=["nccl", "multimem", "auto"],
+    ap.add_argument("--comm", default="auto", choices=["nccl", "multimem", "p2p", "auto"],
                     help="transport of the sharded step: NCCL collectives, this library's NVSwitch multicast kernels, "
-                         "or auto (multicast from four GPUs on where the fabric provides it)")
+                         "its peer load/store kernels, or auto (peer kernels on two GPUs, NCCL on more: what measured "
+                         "fastest)")
     ap.add_argument("--chunks", type=int, default=4, help="pipeline chunks of the sharded (multi-GPU) step")
+    ap.add_argument("--chunk-edge", type=float, default=0.5,
+                    help="size of the first and last Muon chunk of the sharded step relative to the inner ones")
     ap.add_argument("--dynamic-schedule", type=int, default=None, choices=[0, 1],
                     help="Newton-Schulz GEMM tiles drawn from a counter (1) or fixed round-robin (0); default: 1 in "
                          "the sharded (multi-GPU) step, 0 on one GPU")

@@ -85,6 +85,8 @@ def run_sharded(args, rank, world, local_rank, config, metric):
     dev = torch.device("cuda", local_rank)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     dist.init_process_group("nccl", device_id=dev)
+    if not args.dependent_launch:
+        _lib.set_gemm_dependent_launch(False)
     parity = parity_check(dev, rank, world, args.comm)
     muon, adamw = bench.build_workload(dev, args.nblocks, seed=1234)      # same weights on every rank
     grads = [p.grad for p in muon + adamw]
@@ -93,10 +95,10 @@ def run_sharded(args, rank, world, local_rank, config, metric):
     opt = ShardedMonarchMuon(muon, adamw, lr=0.02, momentum=0.95, adamw_betas=(0.9, 0.95),
                              adamw_weight_decay=0.1, adamw_eps=1e-8, n_chunks=args.chunks,
                              comm_sms=None if args.comm_sms < 0 else args.comm_sms,
-                             comm_ctas=None if args.comm_ctas < 0 else args.comm_ctas,
+                             comm_ctas=None if args.comm_ctas < 0 else args.comm_ctas, chunk_edge=args.chunk_edge,
                              dynamic_schedule=args.dynamic_schedule != 0,
                              state_format="fp8_absmax", comm=args.comm, fp8_div=args.fp8_div)
-    if parity.startswith("differs") and opt.comm == "multimem":
+    if parity.startswith("differs") and opt.comm in ("multimem", "p2p"):
         # never time a transport whose result is wrong: fall back to NCCL and say so
         del opt
         torch.cuda.empty_cache()
@@ -138,27 +140,23 @@ def run_sharded(args, rank, world, local_rank, config, metric):
 
     ms_compute, _, _ = _timed_max(compute_only, args.steps, 1, dev)
 
-    def comm_only_multimem():
+    def comm_only_own_kernels():
         main = torch.cuda.current_stream()
         s_red, s_bc = opt._streams
-        esz = 2
         opt._fence()
         s_red.wait_stream(main)
         s_bc.wait_stream(main)
         lib = _lib.load()
-        for k, ch in enumerate(opt.plan.chunks):
-            lo = ch.offset + rank * ch.shard_elems
-            lib.mmb_multimem_reduce_bf16(opt._mc_g + lo * esz, opt.g_own[opt.own_offset[k]:].data_ptr(), ch.shard_elems * esz,
-                                         opt.comm_ctas, s_red.cuda_stream)
-            lib.mmb_multimem_broadcast(opt.w_arena[lo:].data_ptr(), opt._mc_w + lo * esz, ch.shard_elems * esz,
-                                       opt.comm_ctas, s_bc.cuda_stream)
+        for k in range(len(opt.plan.chunks)):
+            opt._launch_reduce(lib, k, s_red.cuda_stream)
+            opt._launch_broadcast(lib, k, s_bc.cuda_stream)
         main.wait_stream(s_red)
         main.wait_stream(s_bc)
         opt._fence()
 
     def comm_only():
-        if opt.comm == "multimem":
-            return comm_only_multimem()
+        if opt.comm in ("multimem", "p2p"):
+            return comm_only_own_kernels()
         works = []
         for k in range(len(opt.plan.chunks)):
             g_whole, g_mine, w_whole, w_mine = opt.chunk_views(k)
@@ -203,6 +201,13 @@ def run_sharded(args, rank, world, local_rank, config, metric):
             nvlink = {"transport": "multimem", "bytes_per_direction_per_gpu_per_step": per_dir,
                       "achieved_gbs_per_direction_per_gpu": per_dir / (ms_comm * 1e-3) / 1e9, "reference_gbs": 770.0,
                       "note": "reduce (outbound) and broadcast (inbound) of all chunks timed together, no compute"}
+        elif opt.comm == "p2p":
+            # reduce: (N-1)/N of the arena comes in (the peers' copies of the own shard) and as much goes out
+            # (the peers reading theirs); broadcast: the same amounts the other way round
+            per_dir = 2 * (world - 1) / world * arena_bytes
+            nvlink = {"transport": "p2p", "bytes_per_direction_per_gpu_per_step": per_dir,
+                      "achieved_gbs_per_direction_per_gpu": per_dir / (ms_comm * 1e-3) / 1e9, "reference_gbs": 770.0,
+                      "note": "peer-load reduce and peer-store broadcast of all chunks timed together, no compute"}
         else:
             per_dir = 2 * (world - 1) / world * arena_bytes      # both ring collectives load both directions
             nvlink = {"transport": "nccl", "bytes_per_direction_per_gpu_per_step": per_dir,
@@ -214,7 +219,7 @@ def run_sharded(args, rank, world, local_rank, config, metric):
                 "vs_baseline": ms / bench.H100_PUBLISHED_MS, "dtype": "bf16", "data": "synthetic",
                 "config": dict(config, parallelism=f"owner-computes dp{world}: bf16 grad reduce-scatter, local "
                                                    "momentum/Newton-Schulz/update/AdamW, weight all-gather over "
-                                                   f"{'NVSwitch multicast kernels of this library' if opt.comm == 'multimem' else 'NCCL'}; "
+                                                   f"{ {'multimem': 'NVSwitch multicast kernels of this library', 'p2p': 'peer load/store kernels of this library'}.get(opt.comm, 'NCCL') }; "
                                                    f"{args.chunks} chunks pipelined, {opt.comm_sms} SMs left to communication, "
                                                    f"{'dynamic' if args.dynamic_schedule != 0 else 'static'} GEMM tile schedule"),
                 "phases_ms": {"step": ms, "compute_only": ms_compute, "communication_only": ms_comm,

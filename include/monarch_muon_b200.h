@@ -361,8 +361,10 @@ int mmb_set_device_grad_scale(const float* scale_dev);
  *                             rank owns, this is its share of a reduce-scatter;
  *   mmb_multimem_broadcast    every copy of dst[i] = src[i] (multimem.st) - called
  *                             on the range a rank owns, its share of an all-gather.
- * `ctas` CTAs of 512 threads are launched (16 saturate the links; few on purpose,
- * the kernels run beside the GEMMs).  The kernels wait on nothing and hold no
+ * `ctas` CTAs of 128 threads are launched.  They are small on purpose (no shared
+ * memory, at most 64 registers): one such CTA fits on an SM beside a Newton-Schulz
+ * GEMM CTA, so the transfer shares SMs with the GEMMs instead of taking SMs from
+ * them; use at most one CTA per SM.  The kernels wait on nothing and hold no
  * flags: the caller orders them against the other ranks (all copies written before
  * the first reduce; a group-wide collective after the last broadcast before any
  * copy is read).  On a GPU or buffer without multicast support the calls must not
@@ -370,6 +372,16 @@ int mmb_set_device_grad_scale(const float* scale_dev);
  * ---------------------------------------------------------------------- */
 int mmb_multimem_reduce_bf16(const void* multicast_src, void* dst_dev, int64_t nbytes, int ctas, void* stream);
 int mmb_multimem_broadcast(const void* src_dev, void* multicast_dst, int64_t nbytes, int ctas, void* stream);
+/* The same two pieces over plain peer addresses (no multicast object needed; no counterpart in the
+ * reference).  `copies` is a HOST array of device addresses, each 16-byte aligned, that this GPU can
+ * reach (its own memory or a peer mapping, e.g. symmetric memory's per-rank buffer pointers):
+ *   mmb_peer_reduce_bf16  dst[i] = bf16(copies[0][i] + copies[1][i] + ... ), bf16 elements, fp32
+ *                         accumulation in the order given, one rounding; `world` in 1..16;
+ *   mmb_peer_broadcast    copies[r][i] = src[i] for r < count (leave this GPU's own copy out when src
+ *                         already is it); `count` in 0..16.
+ * Same CTA shape, same ordering contract as the multicast calls. */
+int mmb_peer_reduce_bf16(const void* const* copies, int world, void* dst_dev, int64_t nbytes, int ctas, void* stream);
+int mmb_peer_broadcast(const void* src_dev, void* const* copies, int count, int64_t nbytes, int ctas, void* stream);
 
 /* ------------------------------------------------------------------------
  * Device status word.  Kernels never trap: a bounded wait that expires or a

@@ -100,6 +100,8 @@ SYMBOLS = {
     "mmb_set_device_grad_scale": (_i, [_vp]),
     "mmb_multimem_reduce_bf16": (_i, [_vp, _vp, _i64, _i, _vp]),
     "mmb_multimem_broadcast": (_i, [_vp, _vp, _i64, _i, _vp]),
+    "mmb_peer_reduce_bf16": (_i, [C.POINTER(_vp), _i, _vp, _i64, _i, _vp]),
+    "mmb_peer_broadcast": (_i, [_vp, C.POINTER(_vp), _i, _i64, _i, _vp]),
     "mmb_device_status_create": (_i, [C.POINTER(_vp)]),
     "mmb_device_status_destroy": (_i, [_vp]),
     "mmb_device_status_read": (_i, [_vp, C.POINTER(C.c_int32), _i, _vp]),

@@ -79,13 +79,21 @@ enum : int32_t {
 };
 
 #ifdef __CUDACC__
-// Launch of a bandwidth-bound kernel (no dynamic shared memory) with the carve-out that fits the mode.
+// Threads per CTA of a bandwidth-bound kernel.  While mmb_set_stream_ctas_per_sm() is in force they are meant
+// to sit on an SM beside a Newton-Schulz GEMM CTA (13 warps of 112 registers and nearly all shared memory).
+// What that leaves per SM sub-partition is 2048 registers on the one that holds four GEMM warps, so a guest
+// CTA fits if it puts one warp of at most 64 registers on each sub-partition: 128 threads.  Kernels launched
+// through launch_stream_kernel index by blockDim, not by a constant.
+inline int stream_threads(int normal) { return stream_kernels_share_sms() ? 128 : normal; }
+
+// Launch of a bandwidth-bound kernel (no dynamic shared memory) with the carve-out and CTA size that fit the
+// mode; `grid` must have been sized for stream_threads(threads) threads per CTA.
 template <typename... KArgs, typename... Args>
 inline void launch_stream_kernel(void (*kernel)(KArgs...), int grid, int threads, cudaStream_t st, Args... args) {
   cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel), cudaFuncAttributePreferredSharedMemoryCarveout,
                        stream_kernels_share_sms() ? static_cast<int>(cudaSharedmemCarveoutMaxShared)
                                                   : static_cast<int>(cudaSharedmemCarveoutDefault));
-  kernel<<<grid, threads, 0, st>>>(args...);
+  kernel<<<grid, stream_threads(threads), 0, st>>>(args...);
 }
 #endif
 

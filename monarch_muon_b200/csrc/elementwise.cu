@@ -111,8 +111,8 @@ template <typename WT>
 __global__ void __launch_bounds__(THREADS)
 muon_update_kernel(const __grid_constant__ UpdTable tab, float alpha) {
   const long long total = tab.vec_start[tab.nseg];
-  const long long stride = static_cast<long long>(gridDim.x) * THREADS;
-  for (long long v = static_cast<long long>(blockIdx.x) * THREADS + threadIdx.x; v < total; v += stride) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < total; v += stride) {
     const int s = find_segment(tab, v);
     const UpdSeg& sg = tab.seg[s];
     const long long at = (v - tab.vec_start[s]) * VEC;
@@ -155,8 +155,8 @@ adamw_kernel(const __grid_constant__ AdamTable tab, float decay, float beta1, fl
              float one_m_beta2, float eps, const float* __restrict__ grad_scale_dev) {
   const float gscale = grad_scale_dev != nullptr ? *grad_scale_dev : 1.0f;
   const long long total = tab.vec_start[tab.nseg];
-  const long long stride = static_cast<long long>(gridDim.x) * THREADS;
-  for (long long v = static_cast<long long>(blockIdx.x) * THREADS + threadIdx.x; v < total; v += stride) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < total; v += stride) {
     const int s = find_segment(tab, v);
     const AdamSeg& sg = tab.seg[s];
     const long long at = (v - tab.vec_start[s]) * VEC;
@@ -278,7 +278,8 @@ clip_coef_kernel(const float* __restrict__ partials, int n, float max_norm, floa
 }
 
 int grid_for(long long total_vecs, int sms) {
-  long long want = (total_vecs + THREADS - 1) / THREADS;
+  const int threads = stream_threads(THREADS);
+  long long want = (total_vecs + threads - 1) / threads;
   long long cap = stream_grid_cap(sms);
   long long g = want < cap ? want : cap;
   return static_cast<int>(g < 1 ? 1 : g);

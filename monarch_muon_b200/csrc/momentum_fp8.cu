@@ -328,8 +328,8 @@ momentum_kernel(const __grid_constant__ SegTable tab, float beta, float grad_sca
   const int lane = threadIdx.x & 31;
   const int sub = lane & (LANES_PER_GROUP - 1);
   const int grp_in_warp = lane >> 3;
-  const long long warp_global = static_cast<long long>(blockIdx.x) * (THREADS / 32) + (threadIdx.x >> 5);
-  const long long nwarps = static_cast<long long>(gridDim.x) * (THREADS / 32);
+  const long long warp_global = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
   const long long total_units = tab.unit_start[tab.nseg];
 
   for (long long u = warp_global; u < total_units; u += nwarps) {
@@ -582,8 +582,8 @@ __global__ void __launch_bounds__(THREADS)
 block_sumsq_kernel(const __grid_constant__ SegTable tab, const float* __restrict__ partials,
                    float* __restrict__ block_sumsq) {
   const int lane = threadIdx.x & 31;
-  const long long warp_global = static_cast<long long>(blockIdx.x) * (THREADS / 32) + (threadIdx.x >> 5);
-  const long long nwarps = static_cast<long long>(gridDim.x) * (THREADS / 32);
+  const long long warp_global = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
   const long long total = tab.block_start[tab.nseg];
   for (long long gb = warp_global; gb < total; gb += nwarps) {
     int lo = 0, hi = tab.nseg;
@@ -799,7 +799,7 @@ int momentum_step_impl(const char* who, const mmb_momentum_seg* segs, int nseg, 
     }
     tab.unit_start[tab.nseg] = units;
     tab.block_start[tab.nseg] = blocks;
-    const long long warps_per_cta = THREADS / 32;
+    const long long warps_per_cta = stream_threads(THREADS) / 32;
     long long want = (units + warps_per_cta - 1) / warps_per_cta;
     long long cap = stream_grid_cap(sms);  // a few waves of 8 resident CTAs per SM unless capped
     int grid = static_cast<int>(want < cap ? want : cap);

@@ -428,16 +428,20 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
     def _muon_slices_overlapped(self, group, lr: float, plan, slices) -> None:
         """Two streams: Newton-Schulz (with its fused update) of slice k on the caller's stream; momentum
         of slice k+1 and (once) the AdamW groups on a side stream.  Newton-Schulz is tensor bound and the
-        others are bandwidth bound, so they can share the chip; the GEMMs draw their tiles dynamically
-        meanwhile.  On a B200 at its power cap the gain is small (the two kinds of work share one power
-        budget), which is why this is not the default.  The bf16 stacks of consecutive slices alternate
+        others are bandwidth bound, so they share the chip: the side-stream kernels are launched as one
+        small CTA per SM (128 threads, at most 64 registers, no shared memory), which fits on an SM beside
+        a GEMM CTA, so the GEMMs keep every SM.  The side stream has high priority: the GEMMs are launched
+        ahead of time (programmatic serialisation), and a pending GEMM grid that cannot be placed yet would
+        otherwise hold up the placement of a kernel queued behind it.  The first slice's momentum has
+        nothing to hide behind and runs with full grids.  The bf16 stacks of consecutive slices alternate
         between two scratch buffers."""
         dev = plan["device"]
         main = torch.cuda.current_stream()
         side = self._side_streams.get(dev)
         if side is None:
-            side = self._side_streams[dev] = torch.cuda.Stream(device=dev)
-        with _lib.launch_options(dynamic_schedule=True):   # pairs that find their SMs taken draw fewer tiles
+            side = self._side_streams[dev] = torch.cuda.Stream(device=dev, priority=-1)
+        shared = _lib.launch_options(stream_ctas_per_sm=1)
+        with _lib.launch_options(dynamic_schedule=True):   # pairs that share their SMs draw fewer tiles
             side.wait_stream(main)                      # gradients and last step's weights are ready
             n = len(slices)
             mom_done = [torch.cuda.Event() for _ in range(n)]
@@ -453,7 +457,7 @@ class MonarchMuonOptimizer(torch.optim.Optimizer):
                 self._mark("momentum")
                 mom_done[0].record(side)
             for k, sl in enumerate(slices):
-                with torch.cuda.stream(side):
+                with torch.cuda.stream(side), shared:
                     if k + 1 < n:
                         if k >= 1:
                             side.wait_event(ns_done[k - 1])    # the buffer of slice k+1 was slice k-1's

@@ -15,7 +15,7 @@ Weights and gradients live in two flat arenas laid out by `partition.make_plan`
 weight arena and given gradient views of the gradient arena, so backward
 accumulates straight into the buffer that is reduced.  Chunks are pipelined.
 
-Two transports (`comm=`):
+Three transports (`comm=`):
 
   "nccl"      NCCL reduce-scatter / all-gather through torch.distributed: all
               reduce-scatters are queued up front on one communicator, each
@@ -35,8 +35,14 @@ Two transports (`comm=`):
               step and one after the last broadcast; the kernels themselves never
               wait on a peer.  Pays from four GPUs on (with two, a ring moves
               fewer bytes per link).
-  "auto"      "multimem" where the group has four or more ranks on one node and
-              the arenas could be mapped for multicast, else "nccl".
+  "p2p"       the same pipeline with plain peer loads and stores (symmetric
+              memory's per-rank pointers, no multicast object): a rank sums its
+              shard from every rank's gradient arena in rank order and writes its
+              updated shard into every rank's weight arena.  Ring-equal bytes per
+              link, one hop, and - like the multicast kernels - CTAs small enough
+              to share an SM with a GEMM CTA.
+  "auto"      what measured fastest on B200s: "p2p" for two ranks (where the arenas
+              can be mapped as symmetric memory), "nccl" otherwise.
 """
 from __future__ import annotations
 
@@ -72,7 +78,9 @@ class ShardedMonarchMuon:
         for the communication kernels (default 0: NCCL's kernels take SMs from the
         GEMMs as they come, the multicast kernels are small enough to share an SM
         with a GEMM CTA).
-    comm_ctas : CTAs of each multicast kernel (default: one per SM).
+    comm_ctas : CTAs of each multicast or peer kernel (default: one per SM).
+    chunk_edge : size of the first and the last Muon chunk relative to the inner ones
+        (their transfers are the ones no computation hides).
     dynamic_schedule : let the Newton-Schulz GEMMs draw their tiles from a counter
         during the step, so that SMs taken by a communication kernel cost those
         SMs' share of the work instead of stalling a whole launch.
@@ -82,11 +90,11 @@ class ShardedMonarchMuon:
                  adamw_betas=(0.9, 0.95), adamw_weight_decay: float = 0.1, adamw_eps: float = 1e-8,
                  n_chunks: int = 4, average: bool = True, local_factory=None, second_group: bool = True,
                  comm: str = "nccl", comm_sms: int | None = None, comm_ctas: int | None = None,
-                 dynamic_schedule: bool = True, **local_kwargs):
+                 dynamic_schedule: bool = True, chunk_edge: float = 0.5, **local_kwargs):
         if not dist.is_initialized():
             raise RuntimeError("ShardedMonarchMuon needs an initialised torch.distributed process group")
-        if comm not in ("nccl", "multimem", "auto"):
-            raise ValueError("comm must be 'nccl', 'multimem' or 'auto'")
+        if comm not in ("nccl", "multimem", "p2p", "auto"):
+            raise ValueError("comm must be 'nccl', 'multimem', 'p2p' or 'auto'")
         self.group = process_group
         self.world = dist.get_world_size(process_group)
         self.rank = dist.get_rank(process_group)
@@ -104,7 +112,7 @@ class ShardedMonarchMuon:
             if p.dim() != 3:
                 raise ValueError("Muon parameters must be 3-D (nblocks, rows, cols)")
         self.plan = partition.make_plan([tuple(p.shape) for p in self.muon_params],
-                                        [p.numel() for p in self.adamw_params], self.world, n_chunks)
+                                        [p.numel() for p in self.adamw_params], self.world, n_chunks, edge=chunk_edge)
         self._check_same_plan_everywhere()
         self.ag_group = dist.new_group(ranks=list(range(dist.get_world_size())), backend=self.backend) \
             if (second_group and process_group is None) else process_group
@@ -116,14 +124,19 @@ class ShardedMonarchMuon:
         # ---- arenas: symmetric memory when this library's multicast kernels move the data
         self.comm = "nccl"
         self._mc_g = self._mc_w = 0
-        want_mc = comm == "multimem" or (comm == "auto" and self.world >= 4)
-        if want_mc and self.backend == "nccl" and self.dtype == torch.bfloat16:
-            arenas = self._symmetric_arenas(n)
+        self._peer_g = self._peer_w = None             # per-rank base addresses of the arenas (symmetric memory)
+        want_mc = comm == "multimem"
+        want_p2p = comm == "p2p" or (comm == "auto" and self.world == 2)
+        if (want_mc or want_p2p) and self.backend == "nccl" and self.dtype == torch.bfloat16:
+            arenas = self._symmetric_arenas(n, need_multicast=want_mc)
             if arenas is not None:
-                self.w_arena, self.g_arena, self._mc_w, self._mc_g = arenas
-                self.comm = "multimem"
-            elif comm == "multimem":
-                raise RuntimeError("comm='multimem': the arenas could not be mapped for NVSwitch multicast on this group")
+                self.w_arena, self.g_arena, self._mc_w, self._mc_g, self._peer_w, self._peer_g = arenas
+                self.comm = "multimem" if want_mc else "p2p"
+            elif comm in ("multimem", "p2p"):
+                raise RuntimeError(f"comm='{comm}': the arenas could not be mapped as symmetric memory"
+                                   + (" with NVSwitch multicast" if want_mc else "") + " on this group")
+        elif comm == "p2p":
+            raise RuntimeError("comm='p2p' needs the NCCL backend and bf16 parameters")
         if self.comm == "nccl":
             self.w_arena = torch.zeros(n, dtype=self.dtype, device=self.device)
             self.g_arena = torch.zeros(n, dtype=self.dtype, device=self.device)
@@ -190,9 +203,10 @@ class ShardedMonarchMuon:
             raise ValueError("ShardedMonarchMuon: the ranks built different ownership plans (different parameter "
                              "lists, chunk counts or dtypes); every rank must pass the same parameters in the same order")
 
-    def _symmetric_arenas(self, n: int):
-        """Weight and gradient arenas in symmetric memory with their multicast addresses, or None when the
-        group cannot provide them (no NVSwitch multicast, allocation refused).  All ranks decide together."""
+    def _symmetric_arenas(self, n: int, need_multicast: bool = True):
+        """Weight and gradient arenas in symmetric memory with their multicast addresses and per-rank
+        addresses, or None when the group cannot provide them (no peer access or, where asked for, no
+        NVSwitch multicast; allocation refused).  All ranks decide together."""
         ok, out = 1, None
         try:
             import torch.distributed._symmetric_memory as symm_mem
@@ -201,13 +215,14 @@ class ShardedMonarchMuon:
             g = symm_mem.empty(n, dtype=self.dtype, device=self.device)
             hw = symm_mem.rendezvous(w, group)
             hg = symm_mem.rendezvous(g, group)
-            mw, mg = int(hw.multicast_ptr), int(hg.multicast_ptr)
-            if not mw or not mg:
+            mw, mg = int(hw.multicast_ptr or 0), int(hg.multicast_ptr or 0)
+            pw, pg = [int(a) for a in hw.buffer_ptrs], [int(a) for a in hg.buffer_ptrs]
+            if (need_multicast and (not mw or not mg)) or len(pw) != self.world or not all(pw) or not all(pg):
                 ok = 0
             else:
                 w.zero_()
                 g.zero_()
-                out = (w, g, mw, mg)
+                out = (w, g, mw, mg, pw, pg)
                 self._symm_handles = (hw, hg)        # keep the mappings alive
         except Exception:                            # no symmetric memory in this build / on this fabric
             ok = 0
@@ -305,8 +320,8 @@ class ShardedMonarchMuon:
         else:
             options = contextlib.nullcontext()
         with options:                                  # launch options are put back even if a local step raises
-            if self.comm == "multimem":
-                self._step_chunks_multimem()
+            if self.comm in ("multimem", "p2p"):
+                self._step_chunks_own_kernels()
             else:
                 self._step_chunks()
 
@@ -366,16 +381,51 @@ class ShardedMonarchMuon:
         for w in ag:
             w.wait()
 
-    def _step_chunks_multimem(self):
-        """The chunk pipeline over this library's multicast kernels: all reductions are queued on one side
-        stream, each chunk's local step waits for its own reduction on the caller's stream, and its
-        broadcast goes to a second side stream; reductions (outbound on the links) and broadcasts (inbound)
-        overlap each other and the GEMMs."""
+    def _launch_reduce(self, lib, k: int, stream) -> None:
+        """This rank's share of chunk k's reduce-scatter: g_own[chunk k] = sum over ranks of the shard."""
+        from . import _lib
+        ch = self.plan.chunks[k]
+        esz = self.g_arena.element_size()
+        lo = (ch.offset + self.rank * ch.shard_elems) * esz
+        dst = self.g_own[self.own_offset[k]:].data_ptr()
+        if self.comm == "multimem":
+            _lib.check(lib.mmb_multimem_reduce_bf16(self._mc_g + lo, dst, ch.shard_elems * esz, self.comm_ctas, stream),
+                       "multimem_reduce_bf16")
+        else:
+            copies = (_lib.C.c_void_p * self.world)(*[base + lo for base in self._peer_g])
+            _lib.check(lib.mmb_peer_reduce_bf16(copies, self.world, dst, ch.shard_elems * esz, self.comm_ctas, stream),
+                       "peer_reduce_bf16")
+
+    def _launch_broadcast(self, lib, k: int, stream) -> None:
+        """This rank's share of chunk k's all-gather: its updated shard goes into every rank's weight arena."""
+        from . import _lib
+        ch = self.plan.chunks[k]
+        esz = self.w_arena.element_size()
+        lo = ch.offset + self.rank * ch.shard_elems
+        src = self.w_arena[lo:].data_ptr()
+        if self.comm == "multimem":
+            _lib.check(lib.mmb_multimem_broadcast(src, self._mc_w + lo * esz, ch.shard_elems * esz, self.comm_ctas, stream),
+                       "multimem_broadcast")
+        else:
+            others = [base + lo * esz for r, base in enumerate(self._peer_w) if r != self.rank]
+            copies = (_lib.C.c_void_p * max(1, len(others)))(*others)
+            _lib.check(lib.mmb_peer_broadcast(src, copies, len(others), ch.shard_elems * esz, self.comm_ctas, stream),
+                       "peer_broadcast")
+
+    def _step_chunks_own_kernels(self):
+        """The chunk pipeline over this library's own transfer kernels (multicast or peer loads/stores): all
+        reductions are queued on one side stream, each chunk's local step waits for its own reduction on the
+        caller's stream, and its broadcast goes to a second side stream; reductions and broadcasts overlap
+        each other and the GEMMs."""
         from . import _lib
         lib = _lib.load()
         main = torch.cuda.current_stream(self.device)
         if self._streams is None:
-            self._streams = (torch.cuda.Stream(device=self.device), torch.cuda.Stream(device=self.device))
+            # High priority: the transfer kernels' CTAs are small and meant to sit beside the GEMM CTAs, but the
+            # GEMMs are launched ahead of time (programmatic serialisation) and a pending GEMM grid that cannot
+            # be placed yet would otherwise hold up the placement of a transfer kernel queued behind it.
+            self._streams = (torch.cuda.Stream(device=self.device, priority=-1),
+                             torch.cuda.Stream(device=self.device, priority=-1))
         s_red, s_bc = self._streams
         esz = self.g_arena.element_size()
         nchunks = len(self.plan.chunks)
@@ -391,11 +441,7 @@ class ShardedMonarchMuon:
                     # chunk has landed - one more fence per chunk, on the reduction stream
                     s_red.wait_event(self._copied[k])
                     self._fence()
-                lo = ch.offset + self.rank * ch.shard_elems
-                _lib.check(lib.mmb_multimem_reduce_bf16(self._mc_g + lo * esz,
-                                                        self.g_own[self.own_offset[k]:].data_ptr(),
-                                                        ch.shard_elems * esz, self.comm_ctas, s_red.cuda_stream),
-                           "multimem_reduce_bf16")
+                self._launch_reduce(lib, k, s_red.cuda_stream)
                 ev = torch.cuda.Event()
                 ev.record(s_red)
                 reduced.append(ev)
@@ -405,12 +451,9 @@ class ShardedMonarchMuon:
             self._local_step(k)
             done = torch.cuda.Event()
             done.record(main)
-            lo = ch.offset + self.rank * ch.shard_elems
             with torch.cuda.stream(s_bc):
                 s_bc.wait_event(done)
-                _lib.check(lib.mmb_multimem_broadcast(self.w_arena[lo:].data_ptr(), self._mc_w + lo * esz,
-                                                      ch.shard_elems * esz, self.comm_ctas, s_bc.cuda_stream),
-                           "multimem_broadcast")
+                self._launch_broadcast(lib, k, s_bc.cuda_stream)
         main.wait_stream(s_bc)
         main.wait_stream(s_red)
         self._fence()                                  # every rank's broadcasts have landed everywhere

@@ -60,11 +60,12 @@ dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("comm", ["nccl", "multimem"])
+@pytest.mark.parametrize("comm", ["nccl", "multimem", "p2p"])
 def test_sharded_step_is_bitwise_the_serial_step(tmp_path, comm):
     """Two GPUs, three steps (the last one fed from pinned host memory), gradients whose sums over the ranks
     are exact in bf16: the sharded weights must equal, bit for bit, those of the serial step on the summed
-    gradient - with NCCL collectives and with this library's NVSwitch multicast kernels.  Ranks live in
+    gradient - with NCCL collectives, with this library's NVSwitch multicast kernels and with its peer
+    load/store kernels.  Ranks live in
     child processes and leave only after their last step; NCCL's own in-switch algorithms are off here."""
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
