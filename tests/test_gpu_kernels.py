@@ -505,3 +505,53 @@ def test_onchip_newton_schulz_matches_the_multi_launch_path_and_the_oracle(mm, s
         mm["ns"].newton_schulz_update(xd, ptrs, wdtype, alpha, backend=L.NS_TCGEN05)
         assert L.read_status(xd.device) == 0
         assert torch.equal(w, want), wdtype
+
+
+# ------------------------------------------------ transfer kernels of the sharded step, on one GPU
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8, 16])
+def test_peer_reduce_sums_the_copies_in_rank_order(mm, world):
+    """mmb_peer_reduce_bf16 over `world` buffers (here all on one GPU; between GPUs the addresses are peer
+    mappings): dst = bf16(fp32 sum of the copies in the order given), bit for bit, for sizes with and
+    without a remainder for the unrolled loop."""
+    L = mm["lib"]
+    C = L.C
+    g = torch.Generator().manual_seed(100 + world)
+    for n in (8 * 1000, 8 * (128 * 148 * 8 * 2 + 37)):
+        copies = [torch.randn(n, generator=g).to(torch.bfloat16).cuda() for _ in range(world)]
+        want = torch.zeros(n, dtype=torch.float32, device="cuda")
+        for c in copies:
+            want += c.float()                                 # fp32 accumulation in rank order
+        want = want.to(torch.bfloat16)
+        got = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+        ptrs = (C.c_void_p * world)(*[c.data_ptr() for c in copies])
+        L.check(L.load().mmb_peer_reduce_bf16(ptrs, world, got.data_ptr(), n * 2, 148, L.stream_ptr()), "peer_reduce")
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("count", [0, 1, 3, 7])
+def test_peer_broadcast_writes_every_copy(mm, count):
+    L = mm["lib"]
+    C = L.C
+    n = 8 * (128 * 148 * 8 + 11)
+    src = torch.randn(n, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).cuda()
+    dsts = [torch.zeros(n, dtype=torch.bfloat16, device="cuda") for _ in range(count)]
+    ptrs = (C.c_void_p * max(1, count))(*[d.data_ptr() for d in dsts])
+    L.check(L.load().mmb_peer_broadcast(src.data_ptr(), ptrs, count, n * 2, 148, L.stream_ptr()), "peer_broadcast")
+    torch.cuda.synchronize()
+    assert all(torch.equal(d, src) for d in dsts)
+
+
+def test_transfer_kernels_refuse_bad_arguments(mm):
+    L = mm["lib"]
+    C = L.C
+    lib = L.load()
+    a = torch.zeros(64, dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros(64, dtype=torch.bfloat16, device="cuda")
+    one = (C.c_void_p * 1)(a.data_ptr())
+    assert lib.mmb_peer_reduce_bf16(one, 17, b.data_ptr(), 128, 1, None) == -1          # too many copies
+    assert lib.mmb_peer_reduce_bf16(one, 1, b.data_ptr(), 100, 1, None) == -1           # not a multiple of 16 bytes
+    assert lib.mmb_peer_reduce_bf16(one, 1, b.data_ptr() + 2, 96, 1, None) == -1        # misaligned
+    assert lib.mmb_peer_broadcast(a.data_ptr(), one, 1, 128, 1, None) == -1             # destination is the source
+    assert lib.mmb_peer_broadcast(a.data_ptr(), one, 0, 128, 1, None) == 0              # nothing to do
+    assert lib.mmb_multimem_reduce_bf16(None, b.data_ptr(), 128, 1, None) == -1

@@ -176,7 +176,15 @@ def _state_worker(rank, world, port, path, mode):
     try:
         from monarch_muon_b200.sharded import ShardedMonarchMuon
         muon, adamw = _make()
-        opt = ShardedMonarchMuon(muon, adamw, lr=0.02, n_chunks=2, local_factory=_MomentumLocal)
+        # comm="auto": on CPU ranks (gloo) there is no symmetric memory, so the choice must fall back to the
+        # torch.distributed collectives; an explicit "p2p" must be refused
+        opt = ShardedMonarchMuon(muon, adamw, lr=0.02, n_chunks=2, local_factory=_MomentumLocal, comm="auto")
+        assert opt.comm == "nccl"
+        try:
+            ShardedMonarchMuon(muon, adamw, lr=0.02, n_chunks=2, local_factory=_MomentumLocal, comm="p2p")
+            raise AssertionError("comm='p2p' accepted on gloo ranks")
+        except RuntimeError as exc:
+            assert "p2p" in str(exc)
         if mode == "save":
             for step in range(2):
                 if step == 1:
