@@ -78,9 +78,12 @@ const char* mmb_last_error(void);
  * Size every kernel's grid for at most n SMs (0 = all).  Leaving a few SMs
  * free lets communication kernels (NCCL) run beside the persistent GEMMs. */
 int mmb_set_sm_limit(int n);
-/* Cap the grids of the bandwidth-bound kernels (momentum, update, AdamW) at n CTAs of 256 threads per SM
- * (0 = default, 32; values outside 0..32 are refused with MMB_ERR_INVALID).  With n = 1 they fit beside the persistent GEMM CTAs, so work issued on a second stream
- * overlaps Newton-Schulz.  No counterpart in the reference. */
+/* Cap the grids of the bandwidth-bound kernels (momentum, update, AdamW) at n CTAs per SM (0 = default: up to
+ * 32 CTAs of 256 threads; values outside 0..32 are refused with MMB_ERR_INVALID).  With n > 0 the CTAs have
+ * 128 threads and ask for the largest shared-memory carve-out, the shape that fits on an SM beside a
+ * persistent GEMM CTA (one warp of at most 64 registers per sub-partition, no shared memory); with n = 1,
+ * work issued on a second stream runs beside Newton-Schulz without taking SMs from it.  No counterpart in the
+ * reference. */
 int mmb_set_stream_ctas_per_sm(int n);
 /* Tile schedule of the Newton-Schulz GEMMs (no counterpart in the reference).  0 (default): every CTA pair
  * takes tiles round-robin, fixed at launch.  1: pairs draw tile numbers from a counter in the workspace, so
