@@ -222,7 +222,7 @@ __device__ __forceinline__ float f32_state_unit(const SegDev& sg, long long e0, 
   return ss;
 }
 
-// FP8 absmax state, aligned pointers, full groups: the judged kernel.  Two groups of loads in flight per
+// FP8 absmax state, aligned pointers, full groups: the path the full-size step runs.  Two groups of loads in flight per
 // lane; the arithmetic works on pairs of elements with the packed fp32 instructions (same bits as the
 // scalar ones, half the issue slots).  m = rn(beta * rn(code * scale)) + g, quantised with
 // scale' = (absmax + 1e-20) / 448 and code' = cvt.rn.satfinite.e4m3(m / scale').  Returns this lane's
