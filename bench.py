@@ -483,6 +483,7 @@ def main():
         torch.cuda.empty_cache()
         sub["isolated_ns"] = measure_isolated_ns(dev, 4, 128, 10, 3)
         sub["small_block_ns"] = measure_small_block_ns(dev, 20, 5)
+        sub["small_block_ns_256"] = measure_small_block_ns(dev, 20, 5, sets=[(128, 256, 256)])
         sub["isolated_fp8_1.6e9"] = measure_isolated_fp8(dev, 1_600_000_000, "fp8_absmax", args.fp8_div, 20, 3)
         sub["isolated_fp8_2558525440"] = measure_isolated_fp8(dev, 2_558_525_440, "fp8_absmax", args.fp8_div, 20, 3)
         release_workspaces()
@@ -672,13 +673,14 @@ def measure_isolated_ns(dev, nblocks: int, ns_blocks: int, steps: int, warmup: i
             "clocks": sampler.stop(tb, te)}
 
 
-def measure_small_block_ns(dev, steps: int, warmup: int) -> dict:
+def measure_small_block_ns(dev, steps: int, warmup: int, sets=None) -> dict:
     """Newton-Schulz on the block set of the small plumbing model (d_model 256, 4 layers, 2-block Monarch:
-    88 blocks of 128x128, 16 of 344x128, 8 of 128x344), where every block fits one SM: the one-launch
-    on-chip kernel beside the fifteen-launch path on the same inputs."""
+    88 blocks of 128x128, 16 of 344x128, 8 of 128x344), or on `sets` (e.g. the 256 x 256 attention blocks of
+    a 1024-wide, 4-block model), where every block fits one SM: the one-launch on-chip kernel beside the
+    fifteen-launch path on the same inputs."""
     from monarch_muon_b200 import _lib, newton_schulz_batched
     gen = torch.Generator(device=dev).manual_seed(7)
-    sets = [(88, 128, 128), (16, 344, 128), (8, 128, 344)]
+    sets = sets or [(88, 128, 128), (16, 344, 128), (8, 128, 344)]
     xs = [torch.empty(s, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=gen) for s in sets]
     outs = [torch.empty_like(x) for x in xs]
     res = {"workload": "Newton-Schulz on " + ", ".join(f"{s[0]}x{s[1]}x{s[2]}" for s in sets) + " bf16 blocks"}

@@ -63,9 +63,10 @@ extern "C" {
 
 /* Newton-Schulz GEMM back ends */
 #define MMB_NS_TCGEN05 0 /* tcgen05.mma + TMEM + TMA (the product).  Blocks with 64 < min(rows, cols) <= 128
-                            and max(rows, cols) <= 384 run all five iterations in ONE launch, one CTA per
-                            block, operands resident in shared and tensor memory; larger blocks run
-                            fifteen batched GEMM launches                                            */
+                            and max(rows, cols) <= 384, and wide or square blocks with 128 < rows <= 256,
+                            rows <= cols <= 256, run all five iterations in ONE launch, one CTA per block,
+                            operands resident in shared and tensor memory; larger blocks run fifteen
+                            batched GEMM launches                                                    */
 #define MMB_NS_SIMT 1    /* plain CUDA-core tiles; slow, for cross-checking    */
 #define MMB_NS_TCGEN05_MULTI 2 /* the fifteen-launch tensor-core path for every shape (for comparison) */
 

@@ -459,13 +459,15 @@ def test_reciprocal_quotient_equals_the_division_instruction_on_many_elements(mm
 
 
 ONCHIP_SHAPES = [(3, 128, 128), (2, 344, 128), (2, 128, 344), (300, 128, 128), (5, 96, 200), (4, 128, 384),
-                 (3, 384, 128), (7, 200, 72)]
+                 (3, 384, 128), (7, 200, 72),
+                 # two row blocks: 128 < rows <= 256, rows <= cols <= 256
+                 (2, 256, 256), (3, 192, 256), (5, 136, 200), (160, 256, 256), (2, 200, 200)]
 
 
 @pytest.mark.parametrize("shape", ONCHIP_SHAPES, ids=lambda s: "x".join(map(str, s)))
 def test_onchip_newton_schulz_matches_the_multi_launch_path_and_the_oracle(mm, shape):
-    """Blocks whose short side is at most 128 (and long side at most 384) run all five iterations in one
-    launch with X, Ah and Pp resident in shared and tensor memory.  Same operands, same roundings as the
+    """Blocks whose short side is at most 128 (and long side at most 384), and wide or square blocks of up to
+    256 x 256, run all five iterations in one launch with X, Ah and Pp resident in shared and tensor memory.  Same operands, same roundings as the
     fifteen-launch path: the results must agree to bf16 rounding noise (the order of the K = 16 partial
     products inside an accumulator may differ) and meet the same bounds against the CPU oracle; one launch
     instead of seventeen; repeated calls and more blocks than SMs give identical bits; the fused weight
