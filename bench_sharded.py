@@ -235,6 +235,11 @@ def run_sharded(args, rank, world, local_rank, config, metric):
                 "cpu_baseline": None, "e2e": e2e, "gpu_launches": launches_per_step * args.steps * world,
                 "clocks": clocks, "device_status": int(status.item())}
         print(json.dumps(line))
+    # no rank leaves while another may still use the arenas it shares (symmetric memory mappings)
+    torch.cuda.synchronize()
+    dist.barrier()
+    del opt
+    torch.cuda.synchronize()
     dist.barrier()
     dist.destroy_process_group()
     return 0
