@@ -251,7 +251,12 @@ int mmb_muon_update(const mmb_update_seg* segs, int nseg, int weight_dtype, floa
  * Replaces _adamw_step, monarch_muon.py:171-201 (membench :176-208): weight
  * decay multiplies the parameter first; eps is added after sqrt(v)/sqrt(bc2);
  * every intermediate is rounded to the tensor dtype like the reference's
- * separate torch ops.  `step` is the already-incremented count.
+ * separate torch ops.  `step` is the already-incremented count.  The
+ * hyper-parameters of this and the two other AdamW entries are doubles, the
+ * reference's Python floats: 1 - lr*wd, 1 - beta, sqrt(1 - beta2^step) and
+ * lr / (1 - beta1^step) are formed in double as the reference forms them and
+ * narrowed once to fp32, as torch narrows a Python scalar (1 - 0.9 taken from
+ * a float 0.9 would be three ulps away from torch's alpha).
  * ---------------------------------------------------------------------- */
 typedef struct mmb_adamw_seg {
   void* param;        /* device, dtype */
@@ -263,8 +268,8 @@ typedef struct mmb_adamw_seg {
   int32_t pad_;
 } mmb_adamw_seg;
 
-int mmb_adamw_step(const mmb_adamw_seg* segs, int nseg, int dtype, float lr, float beta1, float beta2,
-                   float weight_decay, float eps, void* stream);
+int mmb_adamw_step(const mmb_adamw_seg* segs, int nseg, int dtype, double lr, double beta1, double beta2,
+                   double weight_decay, double eps, void* stream);
 
 /* ------------------------------------------------------------------------
  * AdamW with both moments stored as E4M3 codes + per-128-group side arrays,
@@ -292,8 +297,8 @@ typedef struct mmb_adamw_fp8_seg {
   int32_t pad_;
 } mmb_adamw_fp8_seg;
 
-int mmb_adamw_fp8_step(const mmb_adamw_fp8_seg* segs, int nseg, int dtype, int state_format, int div_mode, float lr,
-                       float beta1, float beta2, float weight_decay, float eps, int expand_min, void* stream);
+int mmb_adamw_fp8_step(const mmb_adamw_fp8_seg* segs, int nseg, int dtype, int state_format, int div_mode, double lr,
+                       double beta1, double beta2, double weight_decay, double eps, int expand_min, void* stream);
 
 /* ------------------------------------------------------------------------
  * Steps on fp32 master weights with a bf16 copy for the model, as the
@@ -325,8 +330,8 @@ typedef struct mmb_master_adamw_seg {
   int32_t pad_;
 } mmb_master_adamw_seg;
 
-int mmb_adamw_master_step(const mmb_master_adamw_seg* segs, int nseg, int grad_dtype, float lr, float beta1,
-                          float beta2, float weight_decay, float eps, void* stream);
+int mmb_adamw_master_step(const mmb_master_adamw_seg* segs, int nseg, int grad_dtype, double lr, double beta1,
+                          double beta2, double weight_decay, double eps, void* stream);
 
 /* ------------------------------------------------------------------------
  * Global gradient norm and clip coefficient, computed on the device with no

@@ -69,7 +69,7 @@ class MasterAdamWSeg(C.Structure):
 
 
 # every symbol include/monarch_muon_b200.h declares: name -> (restype, argtypes)
-_vp, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
+_vp, _i, _i64, _f, _d = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_double
 SYMBOLS = {
     "mmb_version": (_i, []),
     "mmb_last_error": (C.c_char_p, []),
@@ -91,10 +91,10 @@ SYMBOLS = {
     "mmb_gemm_occupancy": (_i, [_i, C.POINTER(C.c_int)]),
     "mmb_gemm_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _i, _i, _vp, _vp]),
     "mmb_muon_update": (_i, [C.POINTER(UpdateSeg), _i, _i, _f, _vp]),
-    "mmb_adamw_step": (_i, [C.POINTER(AdamWSeg), _i, _i, _f, _f, _f, _f, _f, _vp]),
-    "mmb_adamw_fp8_step": (_i, [C.POINTER(AdamWFp8Seg), _i, _i, _i, _i, _f, _f, _f, _f, _f, _i, _vp]),
+    "mmb_adamw_step": (_i, [C.POINTER(AdamWSeg), _i, _i, _d, _d, _d, _d, _d, _vp]),
+    "mmb_adamw_fp8_step": (_i, [C.POINTER(AdamWFp8Seg), _i, _i, _i, _i, _d, _d, _d, _d, _d, _i, _vp]),
     "mmb_muon_update_master": (_i, [C.POINTER(MasterUpdateSeg), _i, _f, _vp]),
-    "mmb_adamw_master_step": (_i, [C.POINTER(MasterAdamWSeg), _i, _i, _f, _f, _f, _f, _f, _vp]),
+    "mmb_adamw_master_step": (_i, [C.POINTER(MasterAdamWSeg), _i, _i, _d, _d, _d, _d, _d, _vp]),
     "mmb_grad_norm_scratch_floats": (_i64, []),
     "mmb_grad_norm_clip": (_i, [C.POINTER(GradSeg), _i, _f, _vp, _vp, _i64, _vp]),
     "mmb_set_device_grad_scale": (_i, [_vp]),

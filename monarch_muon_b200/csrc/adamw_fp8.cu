@@ -33,7 +33,7 @@ struct Seg {
   float* m_scale; float* m_expand; float* m_sqrt;
   float* v_scale; float* v_expand; float* v_sqrt;
   long long numel;
-  float bc2_sqrt, step_size;
+  float inv_bc2_sqrt, step_size;   // 1 / sqrt(1 - beta2^step) formed in double (torch multiplies by the reciprocal)
   int vec_ok;
   int pad_;
 };
@@ -177,8 +177,8 @@ adamw_fp8_kernel(const __grid_constant__ Table tab, float decay, float beta1, fl
         float pi = p[i];
         if (decay != 1.0f) pi = round_to<T>(__fmul_rn(pi, decay));                   // p.mul_(1 - lr*wd)
         const float mi = fmaf(one_m_beta1, gi_f, __fmul_rn(m[i], beta1));            // exp_avg.mul_(b1).add_(g, alpha=1-b1)
-        const float vi = fmaf(__fmul_rn(one_m_beta2, gi_f), gi_f, __fmul_rn(v[i], beta2));  // .mul_(b2).addcmul_(g, g, 1-b2)
-        const float d = __fadd_rn(__fdiv_rn(__fsqrt_rn(vi), sg.bc2_sqrt), eps);      // sqrt(v)/sqrt(bc2) + eps
+        const float vi = fmaf(one_m_beta2, __fmul_rn(gi_f, gi_f), __fmul_rn(v[i], beta2));  // .mul_(b2).addcmul_(g, g, 1-b2): a + value*(b*c)
+        const float d = __fadd_rn(__fmul_rn(__fsqrt_rn(vi), sg.inv_bc2_sqrt), eps);  // sqrt(v)/sqrt(bc2) + eps, the division as torch does it
         pi = round_to<T>(fmaf(-sg.step_size, __fdiv_rn(mi, d), pi));                 // p.addcdiv_(m, denom, value=-lr/bc1)
         const bool valid = i < n;
         p[i] = pi;
@@ -214,8 +214,8 @@ adamw_fp8_kernel(const __grid_constant__ Table tab, float decay, float beta1, fl
 
 extern "C" {
 
-int mmb_adamw_fp8_step(const mmb_adamw_fp8_seg* segs, int nseg, int dtype, int state_format, int div_mode, float lr,
-                       float beta1, float beta2, float weight_decay, float eps, int expand_min, void* stream) {
+int mmb_adamw_fp8_step(const mmb_adamw_fp8_seg* segs, int nseg, int dtype, int state_format, int div_mode, double lr_in,
+                       double beta1_in, double beta2_in, double weight_decay_in, double eps_in, int expand_min, void* stream) {
   using namespace mmb;
   MMB_REQUIRE(nseg >= 0 && (nseg == 0 || segs != nullptr), "mmb_adamw_fp8_step: bad segment table");
   MMB_REQUIRE(dtype == MMB_BF16 || dtype == MMB_F32, "mmb_adamw_fp8_step: dtype %d", dtype);
@@ -227,8 +227,10 @@ int mmb_adamw_fp8_step(const mmb_adamw_fp8_seg* segs, int nseg, int dtype, int s
   const int sms = sm_count();
   if (sms <= 0) return fail(MMB_ERR_CUDA, "mmb_adamw_fp8_step: no CUDA device");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const double b1 = beta1, b2 = beta2, lrd = lr, wd = weight_decay;
-  const float decay = weight_decay > 0.0f ? static_cast<float>(1.0 - lrd * wd) : 1.0f;
+  // doubles in, as the reference's Python floats; derived scalars formed in double, narrowed once
+  const double b1 = beta1_in, b2 = beta2_in, lrd = lr_in, wd = weight_decay_in;
+  const float beta1 = static_cast<float>(b1), beta2 = static_cast<float>(b2), eps = static_cast<float>(eps_in);
+  const float decay = wd > 0.0 ? static_cast<float>(1.0 - lrd * wd) : 1.0f;
   const float omb1 = static_cast<float>(1.0 - b1), omb2 = static_cast<float>(1.0 - b2);
   const uintptr_t amask = dtype == MMB_F32 ? 31u : 15u;
   for (int base = 0; base < nseg; base += MAX_SEG) {
@@ -253,7 +255,7 @@ int mmb_adamw_fp8_step(const mmb_adamw_fp8_seg* segs, int nseg, int dtype, int s
       d.numel = s.numel;
       const double bc1 = 1.0 - std::pow(b1, static_cast<double>(s.step));
       const double bc2 = 1.0 - std::pow(b2, static_cast<double>(s.step));
-      d.bc2_sqrt = static_cast<float>(std::sqrt(bc2));
+      d.inv_bc2_sqrt = static_cast<float>(1.0 / std::sqrt(bc2));
       d.step_size = static_cast<float>(lrd / bc1);
       d.vec_ok = (((reinterpret_cast<uintptr_t>(s.param) | reinterpret_cast<uintptr_t>(s.grad)) & amask) == 0) &&
                  aligned16(s.exp_avg) && aligned16(s.exp_avg_sq);

@@ -135,7 +135,8 @@ struct AdamSeg {
   void* exp_avg;
   void* exp_avg_sq;
   long long numel;
-  float bc2_sqrt;    // sqrt(1 - beta2^step)
+  float inv_bc2_sqrt;  // 1 / sqrt(1 - beta2^step), formed in double: torch divides a CUDA tensor by a Python scalar
+                       // by multiplying with the scalar's reciprocal
   float step_size;   // lr / (1 - beta1^step)
   int vec_ok;
   int pad_;
@@ -193,12 +194,12 @@ adamw_kernel(const __grid_constant__ AdamTable tab, float decay, float beta1, fl
       rd2<T>(m0, m1);
       float v0 = __fmul_rn(q[i], beta2), v1 = __fmul_rn(q[i + 1], beta2);       // exp_avg_sq.mul_(beta2)
       rd2<T>(v0, v1);
-      v0 = fmaf(__fmul_rn(one_m_beta2, g[i]), g[i], v0);                        // .addcmul_(grad, grad, value=1-beta2)
-      v1 = fmaf(__fmul_rn(one_m_beta2, g[i + 1]), g[i + 1], v1);
+      v0 = fmaf(one_m_beta2, __fmul_rn(g[i], g[i]), v0);                        // .addcmul_(grad, grad, value=1-beta2):
+      v1 = fmaf(one_m_beta2, __fmul_rn(g[i + 1], g[i + 1]), v1);                //  a + value * (b * c), one fused multiply-add
       rd2<T>(v0, v1);
       float d0 = __fsqrt_rn(v0), d1 = __fsqrt_rn(v1);                           // exp_avg_sq.sqrt()
       rd2<T>(d0, d1);
-      d0 = __fdiv_rn(d0, sg.bc2_sqrt); d1 = __fdiv_rn(d1, sg.bc2_sqrt);         // / sqrt(bc2)
+      d0 = __fmul_rn(d0, sg.inv_bc2_sqrt); d1 = __fmul_rn(d1, sg.inv_bc2_sqrt); // / sqrt(bc2): times the reciprocal
       rd2<T>(d0, d1);
       d0 = __fadd_rn(d0, eps); d1 = __fadd_rn(d1, eps);                         // .add_(eps)
       rd2<T>(d0, d1);
@@ -377,8 +378,8 @@ int mmb_grad_norm_clip(const mmb_grad_seg* segs, int nseg, float max_norm, float
   return MMB_OK;
 }
 
-int mmb_adamw_step(const mmb_adamw_seg* segs, int nseg, int dtype, float lr, float beta1, float beta2,
-                   float weight_decay, float eps, void* stream) {
+int mmb_adamw_step(const mmb_adamw_seg* segs, int nseg, int dtype, double lr_in, double beta1_in, double beta2_in,
+                   double weight_decay_in, double eps_in, void* stream) {
   using namespace mmb;
   MMB_REQUIRE(nseg >= 0 && (nseg == 0 || segs != nullptr), "mmb_adamw_step: bad segment table");
   MMB_REQUIRE(dtype == MMB_BF16 || dtype == MMB_F32, "mmb_adamw_step: dtype %d", dtype);
@@ -386,10 +387,12 @@ int mmb_adamw_step(const mmb_adamw_seg* segs, int nseg, int dtype, float lr, flo
   const int sms = sm_count();
   if (sms <= 0) return fail(MMB_ERR_CUDA, "mmb_adamw_step: no CUDA device");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // scalars are formed in double like the reference's Python floats, then
-  // narrowed once to the fp32 the element-wise arithmetic runs in
-  const double b1 = beta1, b2 = beta2, lrd = lr, wd = weight_decay;
-  const float decay = weight_decay > 0.0f ? static_cast<float>(1.0 - lrd * wd) : 1.0f;
+  // Hyper-parameters arrive as doubles, the reference's Python floats; every derived scalar (1 - lr*wd,
+  // 1 - beta, sqrt(1 - beta2^t), lr / (1 - beta1^t)) is formed in double as the reference forms it and
+  // narrowed once to the fp32 the element-wise arithmetic runs in, as torch narrows a Python scalar.
+  const double b1 = beta1_in, b2 = beta2_in, lrd = lr_in, wd = weight_decay_in;
+  const float beta1 = static_cast<float>(b1), beta2 = static_cast<float>(b2), eps = static_cast<float>(eps_in);
+  const float decay = wd > 0.0 ? static_cast<float>(1.0 - lrd * wd) : 1.0f;
   const uintptr_t amask = dtype == MMB_F32 ? 31u : 15u;
   for (int base = 0; base < nseg; base += MAX_SEG) {
     AdamTable tab;
@@ -408,7 +411,7 @@ int mmb_adamw_step(const mmb_adamw_seg* segs, int nseg, int dtype, float lr, flo
       d.numel = s.numel;
       double bc1 = 1.0 - pow(b1, static_cast<double>(s.step));
       double bc2 = 1.0 - pow(b2, static_cast<double>(s.step));
-      d.bc2_sqrt = static_cast<float>(sqrt(bc2));
+      d.inv_bc2_sqrt = static_cast<float>(1.0 / sqrt(bc2));
       d.step_size = static_cast<float>(lrd / bc1);
       d.vec_ok = (((reinterpret_cast<uintptr_t>(s.param) | reinterpret_cast<uintptr_t>(s.grad) |
                     reinterpret_cast<uintptr_t>(s.exp_avg) | reinterpret_cast<uintptr_t>(s.exp_avg_sq)) & amask) == 0);

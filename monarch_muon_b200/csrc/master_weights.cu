@@ -196,8 +196,8 @@ int mmb_muon_update_master(const mmb_master_update_seg* segs, int nseg, float al
   return MMB_OK;
 }
 
-int mmb_adamw_master_step(const mmb_master_adamw_seg* segs, int nseg, int grad_dtype, float lr, float beta1,
-                          float beta2, float weight_decay, float eps, void* stream) {
+int mmb_adamw_master_step(const mmb_master_adamw_seg* segs, int nseg, int grad_dtype, double lr, double beta1_in,
+                          double beta2_in, double weight_decay, double eps_in, void* stream) {
   using namespace mmb;
   MMB_REQUIRE(nseg >= 0 && (nseg == 0 || segs != nullptr), "mmb_adamw_master_step: bad segment table");
   MMB_REQUIRE(grad_dtype == MMB_BF16 || grad_dtype == MMB_F32, "mmb_adamw_master_step: grad_dtype %d", grad_dtype);
@@ -205,10 +205,12 @@ int mmb_adamw_master_step(const mmb_master_adamw_seg* segs, int nseg, int grad_d
   const int sms = sm_count();
   if (sms <= 0) return fail(MMB_ERR_CUDA, "mmb_adamw_master_step: no CUDA device");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // scalars formed in double like the Python floats of torch.optim
-  const float decay = static_cast<float>(1.0 - static_cast<double>(lr) * static_cast<double>(weight_decay));
-  const float one_m_beta1 = static_cast<float>(1.0 - static_cast<double>(beta1));
-  const float one_m_beta2 = static_cast<float>(1.0 - static_cast<double>(beta2));
+  // hyper-parameters arrive as doubles, the Python floats of torch.optim; derived scalars are formed in
+  // double and narrowed once
+  const float beta2 = static_cast<float>(beta2_in), eps = static_cast<float>(eps_in);
+  const float decay = static_cast<float>(1.0 - lr * weight_decay);
+  const float one_m_beta1 = static_cast<float>(1.0 - beta1_in);
+  const float one_m_beta2 = static_cast<float>(1.0 - beta2_in);
   for (int base = 0; base < nseg; base += MAX_SEG) {
     Table tab;
     tab.nseg = (nseg - base) < MAX_SEG ? (nseg - base) : MAX_SEG;
@@ -226,10 +228,10 @@ int mmb_adamw_master_step(const mmb_master_adamw_seg* segs, int nseg, int grad_d
       d.exp_avg = static_cast<float*>(s.exp_avg);
       d.exp_avg_sq = static_cast<float*>(s.exp_avg_sq);
       d.numel = s.numel;
-      const double bc1 = 1.0 - std::pow(static_cast<double>(beta1), static_cast<double>(s.step));
-      const double bc2 = 1.0 - std::pow(static_cast<double>(beta2), static_cast<double>(s.step));
+      const double bc1 = 1.0 - std::pow(beta1_in, static_cast<double>(s.step));
+      const double bc2 = 1.0 - std::pow(beta2_in, static_cast<double>(s.step));
       d.bc2_sqrt = static_cast<float>(std::sqrt(bc2));
-      d.step_size = static_cast<float>(static_cast<double>(lr) / bc1);
+      d.step_size = static_cast<float>(lr / bc1);
       d.vec_ok = aligned32(s.master) && aligned32(s.exp_avg) && aligned32(s.exp_avg_sq) &&
                  (grad_dtype == MMB_F32 ? aligned32(s.grad) : aligned16(s.grad)) &&
                  (s.shadow == nullptr || aligned16(s.shadow));
