@@ -150,26 +150,69 @@ struct AdamTable {
 // The reference issues one torch op per line (pretrain/src/models/monarch/
 // monarch_muon.py:191-201); each op rounds to the tensor dtype, so `rd` is
 // applied after every one of them.
+__device__ __forceinline__ void unpack_bf16x8(const uint4& v, float* out) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
+  }
+}
+
+// bf16 tensors, aligned full vectors: the four 16-byte loads of a thread's NEXT vector are issued before the
+// current one is computed, so loads stay in flight during the ~70 instructions per element of arithmetic.
 template <typename T>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 4)
 adamw_kernel(const __grid_constant__ AdamTable tab, float decay, float beta1, float one_m_beta1, float beta2,
              float one_m_beta2, float eps, const float* __restrict__ grad_scale_dev) {
+  constexpr bool PREFETCH = sizeof(T) == 2;
   const float gscale = grad_scale_dev != nullptr ? *grad_scale_dev : 1.0f;
   const long long total = tab.vec_start[tab.nseg];
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < total; v += stride) {
-    const int s = find_segment(tab, v);
+  long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // where vector v lives, and (PREFETCH) its raw contents
+  int s = 0, n = 0;
+  long long at = 0;
+  bool vec = false;
+  uint4 rp = {}, rg = {}, rm = {}, rq = {};
+  auto locate_and_fetch = [&](long long vv) {
+    s = find_segment(tab, vv);
     const AdamSeg& sg = tab.seg[s];
-    const long long at = (v - tab.vec_start[s]) * VEC;
+    at = (vv - tab.vec_start[s]) * VEC;
     const long long rem = sg.numel - at;
-    const int n = rem >= VEC ? VEC : static_cast<int>(rem);
-    const bool vec = sg.vec_ok && n == VEC;
+    n = rem >= VEC ? VEC : static_cast<int>(rem);
+    vec = sg.vec_ok && n == VEC;
+    if (PREFETCH && vec) {
+      rp = *reinterpret_cast<const uint4*>(static_cast<const T*>(sg.param) + at);
+      rg = *reinterpret_cast<const uint4*>(static_cast<const T*>(sg.grad) + at);
+      rm = *reinterpret_cast<const uint4*>(static_cast<const T*>(sg.exp_avg) + at);
+      rq = *reinterpret_cast<const uint4*>(static_cast<const T*>(sg.exp_avg_sq) + at);
+    }
+  };
+  if (v < total) locate_and_fetch(v);
+  while (v < total) {
+    const AdamSeg& sg = tab.seg[s];
+    const bool cur_vec = vec;
+    const int cur_n = n;
+    const float inv_bc2_sqrt = sg.inv_bc2_sqrt, step_size = sg.step_size;
     T* pp = static_cast<T*>(sg.param) + at;
     T* mp = static_cast<T*>(sg.exp_avg) + at;
     T* vp = static_cast<T*>(sg.exp_avg_sq) + at;
     float p[VEC], g[VEC], m[VEC], q[VEC];
-    load_vec<T>(pp, vec, n, p);
-    load_vec<T>(static_cast<const T*>(sg.grad) + at, vec, n, g);
+    if (PREFETCH && cur_vec) {
+      unpack_bf16x8(rp, p);
+      unpack_bf16x8(rg, g);
+      unpack_bf16x8(rm, m);
+      unpack_bf16x8(rq, q);
+    } else {
+      load_vec<T>(pp, cur_vec, cur_n, p);
+      load_vec<T>(static_cast<const T*>(sg.grad) + at, cur_vec, cur_n, g);
+      load_vec<T>(mp, cur_vec, cur_n, m);
+      load_vec<T>(vp, cur_vec, cur_n, q);
+    }
+    v += stride;
+    if (v < total) locate_and_fetch(v);   // from here on s, at, n, vec and the raw vectors describe the NEXT vector
     if (gscale != 1.0f) {
 #pragma unroll
       for (int i = 0; i < VEC; i += 2) {  // like grad.mul_(coef) on the stored type
@@ -178,8 +221,6 @@ adamw_kernel(const __grid_constant__ AdamTable tab, float decay, float beta1, fl
         rd2<T>(g[i], g[i + 1]);
       }
     }
-    load_vec<T>(mp, vec, n, m);
-    load_vec<T>(vp, vec, n, q);
     // two elements at a time so that every rounding to the tensor dtype is one packed conversion
 #pragma unroll
     for (int i = 0; i < VEC; i += 2) {
@@ -199,18 +240,18 @@ adamw_kernel(const __grid_constant__ AdamTable tab, float decay, float beta1, fl
       rd2<T>(v0, v1);
       float d0 = __fsqrt_rn(v0), d1 = __fsqrt_rn(v1);                           // exp_avg_sq.sqrt()
       rd2<T>(d0, d1);
-      d0 = __fmul_rn(d0, sg.inv_bc2_sqrt); d1 = __fmul_rn(d1, sg.inv_bc2_sqrt); // / sqrt(bc2): times the reciprocal
+      d0 = __fmul_rn(d0, inv_bc2_sqrt); d1 = __fmul_rn(d1, inv_bc2_sqrt);       // / sqrt(bc2): times the reciprocal
       rd2<T>(d0, d1);
       d0 = __fadd_rn(d0, eps); d1 = __fadd_rn(d1, eps);                         // .add_(eps)
       rd2<T>(d0, d1);
-      p0 = fmaf(-sg.step_size, __fdiv_rn(m0, d0), p0);                          // p.addcdiv_(m, denom, value=-lr/bc1)
-      p1 = fmaf(-sg.step_size, __fdiv_rn(m1, d1), p1);
+      p0 = fmaf(-step_size, __fdiv_rn(m0, d0), p0);                             // p.addcdiv_(m, denom, value=-lr/bc1)
+      p1 = fmaf(-step_size, __fdiv_rn(m1, d1), p1);
       rd2<T>(p0, p1);
       p[i] = p0; p[i + 1] = p1; m[i] = m0; m[i + 1] = m1; q[i] = v0; q[i + 1] = v1;
     }
-    store_vec<T>(pp, vec, n, p);
-    store_vec<T>(mp, vec, n, m);
-    store_vec<T>(vp, vec, n, q);
+    store_vec<T>(pp, cur_vec, cur_n, p);
+    store_vec<T>(mp, cur_vec, cur_n, m);
+    store_vec<T>(vp, cur_vec, cur_n, q);
   }
 }
 
