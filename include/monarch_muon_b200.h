@@ -306,9 +306,12 @@ int mmb_adamw_fp8_step(const mmb_adamw_fp8_seg* segs, int nseg, int dtype, int s
  * state["master"] is updated, then `p.copy_(master)`).  Update and down-cast
  * are one pass.  `shadow` may be NULL (no copy written).
  *   mmb_muon_update_master: master <- master + alpha*O       (:48-49)
- *   mmb_adamw_master_step : torch.optim AdamW on the master  (:51-55); moments
- *     are fp32, the gradient is read in its own dtype (`p.grad.float()`, :44),
- *     `step` is the already-incremented count.
+ *   mmb_adamw_master_step : torch.optim AdamW on the master  (:51-55), in the
+ *     arithmetic of torch's fused CUDA kernel, which is what that call runs on
+ *     a GPU (fp32 hyper-parameters, 1 - beta from the float beta, bias
+ *     corrections by the float power function): bit-exact with the reference
+ *     class on the GPU; moments are fp32, the gradient is read in its own dtype
+ *     (`p.grad.float()`, :44), `step` is the already-incremented count.
  * ---------------------------------------------------------------------- */
 typedef struct mmb_master_update_seg {
   void* master;       /* device, fp32, [numel]              */

@@ -73,9 +73,8 @@ struct Seg {
   float* exp_avg;          // AdamW only
   float* exp_avg_sq;
   long long numel;
-  float bc2_sqrt, step_size;
+  int step;                // AdamW: the already incremented step count
   int vec_ok;
-  int pad_;
 };
 struct Table {
   Seg seg[MAX_SEG];
@@ -113,17 +112,30 @@ update_master_kernel(const __grid_constant__ Table tab, float alpha) {
   }
 }
 
-// torch.optim.AdamW's single-tensor update in fp32 (decoupled decay, lerp for
-// the first moment, eps added after sqrt(v)/sqrt(bc2)).
+// The AdamW update the reference's fine-tuning optimizer runs on a GPU: torch.optim's FUSED kernel
+// (finetune/sft_optimizer.py:52-55 passes fused=p.is_cuda), on the fp32 master.  That kernel works in fp32
+// throughout, hyper-parameters included: 1 - beta is formed from the float beta, the bias corrections
+// 1 - beta^step by the float power function, and its multiply-adds contract as below (each line checked
+// against torch._fused_adamw_ on 2^20 elements: equal bit for bit).
 template <typename GradT>
 __global__ void __launch_bounds__(THREADS)
-adamw_master_kernel(const __grid_constant__ Table tab, float decay, float one_m_beta1, float beta2,
-                    float one_m_beta2, float eps) {
+adamw_master_kernel(const __grid_constant__ Table tab, float lr, float weight_decay, float beta1, float beta2, float eps) {
   const long long total = tab.vec_start[tab.nseg];
   const long long stride = static_cast<long long>(gridDim.x) * THREADS;
+  const float a1 = __fsub_rn(1.0f, beta1), a2 = __fsub_rn(1.0f, beta2);
+  const float lw = __fmul_rn(lr, weight_decay);
+  int cached_step = -1;
+  float bc2_sqrt = 1.0f, step_size = 0.0f;
   for (long long v = static_cast<long long>(blockIdx.x) * THREADS + threadIdx.x; v < total; v += stride) {
     const int s = find_segment(tab, v);
     const Seg& sg = tab.seg[s];
+    if (sg.step != cached_step) {   // bias corrections as the fused kernel forms them, on the device, in fp32
+      cached_step = sg.step;
+      const float t = static_cast<float>(sg.step);
+      const float bc1 = __fsub_rn(1.0f, powf(beta1, t));
+      bc2_sqrt = __fsqrt_rn(__fsub_rn(1.0f, powf(beta2, t)));
+      step_size = __fdiv_rn(lr, bc1);
+    }
     const long long at = (v - tab.vec_start[s]) * VEC;
     const long long rem = sg.numel - at;
     const int n = rem >= VEC ? VEC : static_cast<int>(rem);
@@ -135,11 +147,11 @@ adamw_master_kernel(const __grid_constant__ Table tab, float decay, float one_m_
     load8(sg.exp_avg_sq + at, vec, n, q);
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
-      float pi = decay != 1.0f ? __fmul_rn(p[i], decay) : p[i];                   // param.mul_(1 - lr*wd)
-      const float mi = fmaf(one_m_beta1, __fsub_rn(g[i], m[i]), m[i]);            // exp_avg.lerp_(grad, 1 - beta1)
-      const float vi = fmaf(__fmul_rn(one_m_beta2, g[i]), g[i], __fmul_rn(q[i], beta2));  // mul_(beta2).addcmul_(g, g, 1 - beta2)
-      const float d = __fadd_rn(__fdiv_rn(__fsqrt_rn(vi), sg.bc2_sqrt), eps);     // sqrt(v)/sqrt(bc2) + eps
-      pi = fmaf(-sg.step_size, __fdiv_rn(mi, d), pi);                             // param.addcdiv_(m, denom, value=-lr/bc1)
+      float pi = weight_decay != 0.0f ? fmaf(-lw, p[i], p[i]) : p[i];            // param -= lr * weight_decay * param
+      const float mi = fmaf(beta1, m[i], __fmul_rn(a1, g[i]));                   // exp_avg = beta1 * exp_avg + (1 - beta1) * grad
+      const float vi = fmaf(beta2, q[i], __fmul_rn(a2, __fmul_rn(g[i], g[i])));  // exp_avg_sq = beta2 * exp_avg_sq + (1 - beta2) * grad * grad
+      const float d = __fadd_rn(__fdiv_rn(__fsqrt_rn(vi), bc2_sqrt), eps);       // denom = sqrt(exp_avg_sq) / bias_correction2_sqrt + eps
+      pi = __fsub_rn(pi, __fdiv_rn(__fmul_rn(step_size, mi), d));                // param -= step_size * exp_avg / denom
       p[i] = pi; m[i] = mi; q[i] = vi;
     }
     store8(sg.master + at, vec, n, p);
@@ -183,7 +195,7 @@ int mmb_muon_update_master(const mmb_master_update_seg* segs, int nseg, float al
       d.a = s.ortho;
       d.exp_avg = d.exp_avg_sq = nullptr;
       d.numel = s.numel;
-      d.bc2_sqrt = d.step_size = 0.0f;
+      d.step = 0;
       d.vec_ok = aligned32(s.master) && aligned16(s.ortho) && (s.shadow == nullptr || aligned16(s.shadow));
       tab.vec_start[i] = vecs;
       vecs += (s.numel + VEC - 1) / VEC;
@@ -205,12 +217,10 @@ int mmb_adamw_master_step(const mmb_master_adamw_seg* segs, int nseg, int grad_d
   const int sms = sm_count();
   if (sms <= 0) return fail(MMB_ERR_CUDA, "mmb_adamw_master_step: no CUDA device");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // hyper-parameters arrive as doubles, the Python floats of torch.optim; derived scalars are formed in
-  // double and narrowed once
-  const float beta2 = static_cast<float>(beta2_in), eps = static_cast<float>(eps_in);
-  const float decay = static_cast<float>(1.0 - lr * weight_decay);
-  const float one_m_beta1 = static_cast<float>(1.0 - beta1_in);
-  const float one_m_beta2 = static_cast<float>(1.0 - beta2_in);
+  // hyper-parameters arrive as doubles, the Python floats of torch.optim, and are narrowed to fp32 here, as
+  // torch's fused kernel narrows them; everything derived from them is formed in fp32 on the device
+  const float lr_f = static_cast<float>(lr), wd_f = static_cast<float>(weight_decay);
+  const float beta1 = static_cast<float>(beta1_in), beta2 = static_cast<float>(beta2_in), eps = static_cast<float>(eps_in);
   for (int base = 0; base < nseg; base += MAX_SEG) {
     Table tab;
     tab.nseg = (nseg - base) < MAX_SEG ? (nseg - base) : MAX_SEG;
@@ -228,10 +238,7 @@ int mmb_adamw_master_step(const mmb_master_adamw_seg* segs, int nseg, int grad_d
       d.exp_avg = static_cast<float*>(s.exp_avg);
       d.exp_avg_sq = static_cast<float*>(s.exp_avg_sq);
       d.numel = s.numel;
-      const double bc1 = 1.0 - std::pow(beta1_in, static_cast<double>(s.step));
-      const double bc2 = 1.0 - std::pow(beta2_in, static_cast<double>(s.step));
-      d.bc2_sqrt = static_cast<float>(std::sqrt(bc2));
-      d.step_size = static_cast<float>(lr / bc1);
+      d.step = s.step;
       d.vec_ok = aligned32(s.master) && aligned32(s.exp_avg) && aligned32(s.exp_avg_sq) &&
                  (grad_dtype == MMB_F32 ? aligned32(s.grad) : aligned16(s.grad)) &&
                  (s.shadow == nullptr || aligned16(s.shadow));
@@ -241,9 +248,9 @@ int mmb_adamw_master_step(const mmb_master_adamw_seg* segs, int nseg, int grad_d
     tab.vec_start[tab.nseg] = vecs;
     const int grid = grid_for(vecs, sms);
     if (grad_dtype == MMB_BF16)
-      adamw_master_kernel<__nv_bfloat16><<<grid, THREADS, 0, st>>>(tab, decay, one_m_beta1, beta2, one_m_beta2, eps);
+      adamw_master_kernel<__nv_bfloat16><<<grid, THREADS, 0, st>>>(tab, lr_f, wd_f, beta1, beta2, eps);
     else
-      adamw_master_kernel<float><<<grid, THREADS, 0, st>>>(tab, decay, one_m_beta1, beta2, one_m_beta2, eps);
+      adamw_master_kernel<float><<<grid, THREADS, 0, st>>>(tab, lr_f, wd_f, beta1, beta2, eps);
     MMB_CUDA_CHECK(cudaGetLastError());
     count_launch();
   }

@@ -210,3 +210,46 @@ def test_strided_gradients_are_read_through_a_copy_that_outlives_the_launch():
         results.append([p.data.clone() for p in params])
     for a, b in zip(*results):
         assert torch.equal(a, b)
+
+
+def test_adamw_groups_are_bit_exact_with_the_reference_class_on_the_gpu():
+    """The reference's SFTOptimizer (finetune/sft_optimizer.py:17-59, staged unmodified) run on the GPU, where its
+    AdamW branch calls torch.optim's fused kernel, against this library's class: master weights, both moments
+    and the bf16 parameters equal bit for bit after each of six steps, then again from a late step count (the
+    bias corrections are float powers of the float betas there)."""
+    from oracle import ref_loader
+    if not ref_loader.available():
+        pytest.skip("oracle/_ref/ not staged (python oracle/make_ref.py <reference checkout>)")
+    from monarch_muon_b200.sft import SFTOptimizer
+    ref = ref_loader.sft()
+    gen = torch.Generator().manual_seed(5)
+    shapes = [(1000, 64), (64,), (333, 77)]
+    w = [(0.05 * torch.randn(s, generator=gen)).bfloat16() for s in shapes]
+    a = [torch.nn.Parameter(t.clone().cuda()) for t in w]
+    b = [torch.nn.Parameter(t.clone().cuda()) for t in w]
+    theirs = ref.SFTOptimizer([{"params": a, "algorithm": "adamw"}], lr=3e-5)
+    ours = SFTOptimizer([{"params": b, "algorithm": "adamw"}], lr=3e-5)
+
+    def bits(t):
+        return t.contiguous().view(torch.int32 if t.dtype == torch.float32 else torch.int16).reshape(-1)
+
+    def one_step(tag):
+        for pa, pb, sh in zip(a, b, shapes):
+            g = (1e-2 * torch.randn(sh, generator=gen)).bfloat16()
+            pa.grad, pb.grad = g.clone().cuda(), g.clone().cuda()
+        theirs.step()
+        ours.step()
+        for pa, pb in zip(a, b):
+            sa, sb = theirs.state[pa], ours.state[pb]
+            for name in ("master", "momentum", "variance"):
+                assert torch.equal(bits(sa[name]), bits(sb[name])), (tag, name, tuple(pa.shape))
+            assert torch.equal(bits(pa.data), bits(pb.data)), (tag, tuple(pa.shape))
+
+    for step in range(6):
+        one_step(step)
+    for pa, pb in zip(a, b):                                  # jump both sides to a late step
+        theirs.state[pa]["adam_step"].fill_(997.0)
+        ours.state[pb]["adam_step"].fill_(997.0)
+    ours._adam_steps.clear()                                  # host copies of the step counts are re-read from the state
+    for step in range(3):
+        one_step(997 + step)
