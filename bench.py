@@ -300,7 +300,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--nblocks", type=int, default=4, choices=[2, 4])
-    ap.add_argument("--case", default="step", choices=["step", "ns", "fp8", "gemm", "adamw"],
+    ap.add_argument("--case", default="step", choices=["step", "ns", "fp8", "gemm", "adamw", "guest"],
                     help="step: the full optimizer step (headline); ns: isolated batched Newton-Schulz on the "
                          "128+64+64 block set; fp8: isolated FP8 momentum kernel on a flat buffer; gemm: the library's "
                          "batched GEMM beside cuBLAS (torch.bmm) on the Newton-Schulz shapes, each run back to "
@@ -385,6 +385,8 @@ def main():
         return run_gemm_comparison(args, dev)
     if args.case == "adamw":
         return run_adamw_isolated(args, dev)
+    if args.case == "guest":
+        return run_guest_probe(args, dev)
     if args.case != "step":
         return run_isolated(args, dev)
 
@@ -584,6 +586,66 @@ def run_adamw_isolated(args, dev):
             "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "dtype": "bf16", "data": "synthetic",
             "scaling": "strong", "vs_baseline": None, "gpu_launches": _lib.launch_count() - l0,
             "clocks": sampler.stop(tb, te), "device_status": _lib.read_status(dev)}
+    print(json.dumps(line))
+    return 0
+
+
+def run_guest_probe(args, dev):
+    """Do the small transfer kernels share SMs with the Newton-Schulz GEMMs?  Newton-Schulz on 128 blocks of
+    1024 x 1024 (four calls, ~11 ms) is timed alone, and again while this library's peer-store kernel
+    (mmb_peer_broadcast, here onto buffers of the same GPU: a copy of 512 MB per launch) runs on a second,
+    high-priority stream with one CTA per SM, with one per two SMs, and with two per SM.  CTAs of 128 threads
+    without shared memory fit beside a GEMM CTA once per SM; a second one per SM does not, and the GEMM
+    launches then wait for SMs."""
+    import ctypes as C
+    from monarch_muon_b200 import _lib, newton_schulz_batched
+    lib = _lib.load()
+    gen = torch.Generator(device=dev).manual_seed(11)
+    x = torch.empty(128, 1024, 1024, dtype=torch.bfloat16, device=dev).normal_(0, 1, generator=gen)
+    nbytes = 512 << 20
+    src = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    dst = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    side = torch.cuda.Stream(device=dev, priority=-1)
+    reps = 4
+
+    def ns():
+        for _ in range(reps):
+            newton_schulz_batched(x, backend=_lib.NS_TCGEN05_MULTI)
+
+    for _ in range(2):
+        ns()
+    torch.cuda.synchronize()
+
+    def timed(ctas, copies):
+        torch.cuda.synchronize()
+        e0, e1, s0, s1 = (torch.cuda.Event(enable_timing=True) for _ in range(4))
+        if ctas:
+            ptr = (C.c_void_p * 1)(dst.data_ptr())
+            with torch.cuda.stream(side):
+                s0.record(side)
+                for _ in range(copies):
+                    _lib.check(lib.mmb_peer_broadcast(src.data_ptr(), ptr, 1, nbytes, ctas, side.cuda_stream), "peer_broadcast")
+                s1.record(side)
+            time.sleep(0.002)                         # the copy is under way before the first GEMM is queued
+        e0.record()
+        ns()
+        e1.record()
+        torch.cuda.synchronize()
+        out = {"newton_schulz_ms": e0.elapsed_time(e1)}
+        if ctas:
+            ms = s0.elapsed_time(s1)
+            out.update(guest_ctas=ctas, guest_ms=ms, guest_gbs=2.0 * nbytes * copies / ms / 1e6)
+        return out
+
+    rows = {"alone": timed(0, 0), "alone_again": timed(0, 0)}
+    for name, ctas, copies in (("one_guest_per_sm", sms, 40), ("one_guest_per_two_sms", sms // 2, 24),
+                               ("two_guests_per_sm", 2 * sms, 40)):
+        rows[name] = timed(ctas, copies)
+    line = {"metric": "newton_schulz_ms_beside_guest_kernel", "unit": "ms", "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{reps} x Newton-Schulz on 128 blocks of 1024x1024 beside mmb_peer_broadcast copying "
+                                   "512 MB per launch on a high-priority stream"},
+            "rows": rows, "device_status": _lib.read_status(dev)}
     print(json.dumps(line))
     return 0
 
