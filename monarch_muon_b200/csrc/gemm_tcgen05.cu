@@ -410,7 +410,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a_k, const __grid_constant__
     const int ew = warp - 2;
     const int quarter = warp & 3;
     const int half = ew >> 2;
-    const int row_in_tile = quarter * 32 + lane;
     uint8_t* my_buf = epi_ptr + ew * EPI_WARP_BYTES;
     const uint32_t my_buf_addr = epi_addr + ew * EPI_WARP_BYTES;
     uint32_t local = 0;
